@@ -1,0 +1,584 @@
+// Implicit-GEMM convolution / dense on tcgen05 tensor cores with TMEM accumulators and TMA operand
+// loads (see conv_tc.cuh for the GEMM view). Persistent, warp-specialised CTAs, one per SM:
+//
+//   warp 0      TMA producer   one lane issues cp.async.bulk.tensor loads into a ring of swizzled
+//                              shared-memory stages, each guarded by a full/empty mbarrier pair
+//   warp 1      MMA issuer     one lane issues tcgen05.mma (M = 128, N = BN, K = 32 bytes per
+//                              instruction) into one of two TMEM accumulators; tcgen05.commit
+//                              releases stages and publishes finished accumulators; owns TMEM alloc
+//   warps 2..5  epilogue       tcgen05.ld the accumulator (each warp its own 32-lane quadrant),
+//                              +bias -> +residual -> ReLU (or int8 requantize), store; overlaps the
+//                              next tile's main loop through the second accumulator
+//
+// Every wait is bounded (sm100::mbar_wait_bounded); a wait that runs out sets the CTA's abort flag
+// and the global status word, every role leaves its loop, TMEM is released and the kernel returns.
+#include "conv_tc.cuh"
+
+#include <cuda_bf16.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace kxc_b200 {
+namespace {
+
+using namespace sm100;
+
+constexpr int kTcThreads = 192;
+constexpr int kSmemLimit = 227 * 1024;
+
+template <int KB_BYTES, int BN>
+struct StageGeom {
+    static constexpr int kABytes = 128 * KB_BYTES;
+    static constexpr int kBBytes = BN * KB_BYTES;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStagesRaw = (kSmemLimit - 2048) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align the ring to 1024 B
+};
+
+__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Epilogue for one 32-column chunk held by one thread (= one output pixel, 32 consecutive channels).
+template <int kOutMode>
+__device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t (&v)[32], int c0, bool valid, int n,
+                                               int oh, int ow) {
+    if (!valid || c0 >= p.Cout) return;
+    const int nch = (p.Cout - c0) < 32 ? (p.Cout - c0) : 32;
+    const size_t pix = ((size_t)n * p.OH + oh) * p.OW + ow;
+
+    if constexpr (kOutMode == kOutNHWC_S8 || kOutMode == kOutNCHW_S8) {
+        int8_t q[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int c = c0 + j;
+            if (j < nch) {
+                const int32_t acc = (int32_t)v[j] + __ldg(p.bias_i32 + c);
+                q[j] = requantize_s8(acc, __ldg(p.multiplier + c), __ldg(p.shift + c), p.relu);
+            } else {
+                q[j] = 0;
+            }
+        }
+        int8_t* out = static_cast<int8_t*>(p.out);
+        if constexpr (kOutMode == kOutNHWC_S8) {
+            int8_t* dst = out + pix * p.Cout + c0;
+            if (nch == 32 && (p.Cout & 15) == 0 && p.vec_ok) {
+                const uint4* src = reinterpret_cast<const uint4*>(q);
+                reinterpret_cast<uint4*>(dst)[0] = src[0];
+                reinterpret_cast<uint4*>(dst)[1] = src[1];
+            } else {
+                for (int j = 0; j < nch; ++j) dst[j] = q[j];
+            }
+        } else {
+            const size_t plane = (size_t)p.OH * p.OW;
+            int8_t* dst = out + ((size_t)n * p.Cout + c0) * plane + (size_t)oh * p.OW + ow;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < nch) dst[(size_t)j * plane] = q[j];
+        }
+        return;
+    } else {
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        if (p.bias != nullptr) {
+            if (nch == 32 && p.vec_ok) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + j));
+                    f[j] = __fadd_rn(f[j], b.x);
+                    f[j + 1] = __fadd_rn(f[j + 1], b.y);
+                    f[j + 2] = __fadd_rn(f[j + 2], b.z);
+                    f[j + 3] = __fadd_rn(f[j + 3], b.w);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < nch) f[j] = __fadd_rn(f[j], __ldg(p.bias + c0 + j));
+            }
+        }
+        if constexpr (kOutMode == kOutNHWC_BF16) {
+            const bool vec = (nch == 32) && ((p.Cout & 7) == 0) && p.vec_ok;
+            __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + pix * p.Cout + c0;
+            if (p.residual != nullptr) {
+                const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(p.residual) + pix * p.Cout + c0;
+                if (vec) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const uint4 r = __ldg(reinterpret_cast<const uint4*>(res) + g);
+                        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            f[g * 8 + 2 * k] = __fadd_rn(f[g * 8 + 2 * k], bf16_lo(w[k]));
+                            f[g * 8 + 2 * k + 1] = __fadd_rn(f[g * 8 + 2 * k + 1], bf16_hi(w[k]));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (j < nch) f[j] = __fadd_rn(f[j], __bfloat162float(res[j]));
+                }
+            }
+            if (p.relu) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) f[j] = f[j] > 0.0f ? f[j] : 0.0f;
+            }
+            if (vec) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    uint4 o;
+                    o.x = pack_bf16(f[g * 8 + 0], f[g * 8 + 1]);
+                    o.y = pack_bf16(f[g * 8 + 2], f[g * 8 + 3]);
+                    o.z = pack_bf16(f[g * 8 + 4], f[g * 8 + 5]);
+                    o.w = pack_bf16(f[g * 8 + 6], f[g * 8 + 7]);
+                    reinterpret_cast<uint4*>(out)[g] = o;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < nch) out[j] = __float2bfloat16_rn(f[j]);
+            }
+        } else if constexpr (kOutMode == kOutNHWC_F32) {
+            const bool vec = (nch == 32) && ((p.Cout & 3) == 0) && p.vec_ok;
+            float* out = static_cast<float*>(p.out) + pix * p.Cout + c0;
+            if (p.residual != nullptr) {
+                const float* res = static_cast<const float*>(p.residual) + pix * p.Cout + c0;
+                if (vec) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 r = __ldg(reinterpret_cast<const float4*>(res + j));
+                        f[j] = __fadd_rn(f[j], r.x);
+                        f[j + 1] = __fadd_rn(f[j + 1], r.y);
+                        f[j + 2] = __fadd_rn(f[j + 2], r.z);
+                        f[j + 3] = __fadd_rn(f[j + 3], r.w);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (j < nch) f[j] = __fadd_rn(f[j], __ldg(res + j));
+                }
+            }
+            if (p.relu) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) f[j] = f[j] > 0.0f ? f[j] : 0.0f;
+            }
+            if (vec) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(out + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < nch) out[j] = f[j];
+            }
+        } else {  // kOutNCHW_F32: lanes are consecutive pixels, so each channel's store is contiguous
+            const size_t plane = (size_t)p.OH * p.OW;
+            const size_t off = ((size_t)n * p.Cout + c0) * plane + (size_t)oh * p.OW + ow;
+            float* out = static_cast<float*>(p.out) + off;
+            const float* res = p.residual ? static_cast<const float*>(p.residual) + off : nullptr;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (j < nch) {
+                    float x = f[j];
+                    if (res) x = __fadd_rn(x, __ldg(res + (size_t)j * plane));
+                    if (p.relu) x = x > 0.0f ? x : 0.0f;
+                    out[(size_t)j * plane] = x;
+                }
+            }
+        }
+    }
+}
+
+template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode>
+__global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_constant__ TcParams p) {
+    using G = StageGeom<KB_BYTES, BN>;
+    constexpr int kStages = G::kStages;
+    constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators; 128, 256 or 512: a power of two
+    constexpr uint32_t kIdesc =
+        make_instr_desc(kKind == MmaKind::F16 ? kFmtBF16 : (kKind == MmaKind::TF32 ? kFmtTF32 : kFmtS8),
+                        kKind == MmaKind::I8 ? kAccS32 : kAccF32, BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[kStages];
+    __shared__ __align__(8) uint64_t bar_empty[kStages];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bar_acc_full[a]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[a]), 4);  // one arrival per epilogue warp
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort_ptr = &abort_flag;
+
+    const int num_kb = p.taps_h * p.taps_w * p.cblocks;
+    const int total_tiles = p.tiles_c * p.tiles_w * p.tiles_h * p.tiles_n;
+    const int rows_used = p.BW * p.BH * p.BNI;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&p.tmB);
+            tma_prefetch_desc(&p.tmA[0]);
+            const uint32_t tx_bytes = (uint32_t)(rows_used * KB_BYTES + G::kBBytes);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                int r = tile;
+                const int ct = r % p.tiles_c; r /= p.tiles_c;
+                const int tw = r % p.tiles_w; r /= p.tiles_w;
+                const int th = r % p.tiles_h;
+                const int tn = r / p.tiles_h;
+                const int ow0 = tw * p.BW, oh0 = th * p.BH, n0 = tn * p.BNI, co0 = ct * BN;
+                int kb = 0;
+                for (int kh = 0; ok && kh < p.taps_h; ++kh) {
+                    for (int kw = 0; ok && kw < p.taps_w; ++kw) {
+                        const int dh = kh * p.dil_h - p.pad_h;
+                        const int dw = kw * p.dil_w - p.pad_w;
+                        int map = 0, ch = oh0 + dh, cw = ow0 + dw;
+                        if (p.stride == 2) {
+                            const int hp = dh & 1, wp = dw & 1;
+                            map = hp * 2 + wp;
+                            ch = oh0 + ((dh - hp) >> 1);
+                            cw = ow0 + ((dw - wp) >> 1);
+                        }
+                        for (int cb = 0; cb < p.cblocks; ++cb, ++kb) {
+                            if (!mbar_wait_bounded(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr)) {
+                                ok = false;
+                                break;
+                            }
+                            const uint32_t full = smem_u32(&bar_full[stage]);
+                            const uint32_t a_dst = ring + (uint32_t)stage * G::kStageBytes;
+                            mbar_arrive_expect_tx(full, tx_bytes);
+                            tma_load_4d(a_dst, &p.tmA[map], full, cb * p.kb_elems, cw, ch, n0);
+                            tma_load_2d(a_dst + G::kABytes, &p.tmB, full, kb * p.kb_elems, co0);
+                            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr)) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_bounded(smem_u32(&bar_full[stage]), phase, abort_ptr)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = ring + (uint32_t)stage * G::kStageBytes;
+                    const uint64_t a_desc = make_smem_desc(a_addr, KB_BYTES);
+                    const uint64_t b_desc = make_smem_desc(a_addr + G::kABytes, KB_BYTES);
+#pragma unroll
+                    for (int k = 0; k < KB_BYTES / 32; ++k) {
+                        // advancing 32 bytes along K inside the swizzle span = +2 in the (addr >> 4) field
+                        umma<kKind>(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), kIdesc,
+                                    (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&bar_empty[stage]));
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&bar_acc_full[acc]));
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+        const int row = quad * 32 + lane;
+        const int box_hw = p.BH * p.BW;
+        const int n_l = row / box_hw;
+        const int rem = row - n_l * box_hw;
+        const int h_l = rem / p.BW;
+        const int w_l = rem - h_l * p.BW;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            int r = tile;
+            const int ct = r % p.tiles_c; r /= p.tiles_c;
+            const int tw = r % p.tiles_w; r /= p.tiles_w;
+            const int th = r % p.tiles_h;
+            const int tn = r / p.tiles_h;
+            const int n = tn * p.BNI + n_l, oh = th * p.BH + h_l, ow = tw * p.BW + w_l;
+            const bool valid = (row < rows_used) && (n < p.N) && (oh < p.OH) && (ow < p.OW);
+            bool ok = mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                uint32_t v[32];
+                tmem_ld_32x32(t_addr + (uint32_t)(chunk * 32), v);
+                tmem_ld_wait();
+                epilogue_chunk<kOutMode>(p, v, ct * BN + chunk * 32, valid, n, oh, ow);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    // ------------------------------ teardown ------------------------------
+    if (*abort_ptr) {
+        // Loads that were already issued may still be landing in shared memory: give them time
+        // (bounded) before the CTA's shared memory is released.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_ptr && p.status != nullptr) atomicExch(p.status, KXC_B200_ERR_DEVICE_WAIT);
+}
+
+template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode>
+int32_t launch_one(const TcParams& p, cudaStream_t stream) {
+    using G = StageGeom<KB_BYTES, BN>;
+    auto kernel = conv_igemm_kernel<kKind, KB_BYTES, BN, kOutMode>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes);
+    });
+    if (attr_err != cudaSuccess)
+        return fail(KXC_B200_ERR_CUDA, "cudaFuncSetAttribute(smem=%d): %s", G::kSmemBytes, cudaGetErrorString(attr_err));
+    const long long tiles = (long long)p.tiles_c * p.tiles_w * p.tiles_h * p.tiles_n;
+    if (tiles <= 0) return KXC_B200_OK;
+    const int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
+    kernel<<<grid, kTcThreads, G::kSmemBytes, stream>>>(p);
+    return check_launch("conv_igemm_kernel");
+}
+
+template <MmaKind kKind, int KB_BYTES, int BN>
+int32_t launch_by_out(const TcConfig& cfg, const TcParams& p, cudaStream_t s) {
+    if constexpr (kKind == MmaKind::I8) {
+        switch (cfg.out_mode) {
+            case kOutNHWC_S8: return launch_one<kKind, KB_BYTES, BN, kOutNHWC_S8>(p, s);
+            case kOutNCHW_S8: return launch_one<kKind, KB_BYTES, BN, kOutNCHW_S8>(p, s);
+            default: break;
+        }
+    } else {
+        switch (cfg.out_mode) {
+            case kOutNHWC_BF16: return launch_one<kKind, KB_BYTES, BN, kOutNHWC_BF16>(p, s);
+            case kOutNHWC_F32: return launch_one<kKind, KB_BYTES, BN, kOutNHWC_F32>(p, s);
+            case kOutNCHW_F32: return launch_one<kKind, KB_BYTES, BN, kOutNCHW_F32>(p, s);
+            default: break;
+        }
+    }
+    return fail(KXC_B200_ERR_INVALID, "tensor-core conv: output mode %d does not fit dtype %d", (int)cfg.out_mode, (int)cfg.dtype);
+}
+
+template <MmaKind kKind, int KB_BYTES>
+int32_t launch_by_bn(const TcConfig& cfg, const TcParams& p, cudaStream_t s) {
+    switch (cfg.bn) {
+        case 64: return launch_by_out<kKind, KB_BYTES, 64>(cfg, p, s);
+        case 128: return launch_by_out<kKind, KB_BYTES, 128>(cfg, p, s);
+        case 256: return launch_by_out<kKind, KB_BYTES, 256>(cfg, p, s);
+        default: return fail(KXC_B200_ERR_INVALID, "tensor-core conv: unsupported N tile %d", cfg.bn);
+    }
+}
+
+template <MmaKind kKind>
+int32_t launch_by_kb(const TcConfig& cfg, const TcParams& p, cudaStream_t s) {
+    switch (cfg.kb_bytes) {
+        case 32: return launch_by_bn<kKind, 32>(cfg, p, s);
+        case 64: return launch_by_bn<kKind, 64>(cfg, p, s);
+        case 128: return launch_by_bn<kKind, 128>(cfg, p, s);
+        default: return fail(KXC_B200_ERR_INVALID, "tensor-core conv: unsupported K block of %d bytes", cfg.kb_bytes);
+    }
+}
+
+}  // namespace
+
+int32_t tc_launch(const TcConfig& cfg, const TcParams& p, cudaStream_t stream) {
+    switch (cfg.dtype) {
+        case kTcBF16: return launch_by_kb<MmaKind::F16>(cfg, p, stream);
+        case kTcTF32: return launch_by_kb<MmaKind::TF32>(cfg, p, stream);
+        case kTcS8: return launch_by_kb<MmaKind::I8>(cfg, p, stream);
+    }
+    return fail(KXC_B200_ERR_INVALID, "tensor-core conv: unknown dtype");
+}
+
+void tc_pick_tile(int N, int OH, int OW, int* BW, int* BH, int* BNI) {
+    double best = -1.0;
+    int bw_best = 1, bh_best = 1, bn_best = 1;
+    for (int bw = 1; bw <= OW && bw <= 128; ++bw) {
+        for (int bh = 1; bh <= OH && bw * bh <= 128; ++bh) {
+            int bn = 128 / (bw * bh);
+            if (bn > N) bn = N;
+            if (bn > 128) bn = 128;
+            if (bn < 1) bn = 1;
+            const long long tiles = (long long)((OW + bw - 1) / bw) * ((OH + bh - 1) / bh) * ((N + bn - 1) / bn);
+            const double eff = (double)N * OH * OW / ((double)tiles * 128.0);
+            // prefer higher efficiency; on ties a wider box (longer contiguous runs for TMA and stores)
+            if (eff > best + 1e-9 || (eff > best - 1e-9 && bw > bw_best)) {
+                best = eff;
+                bw_best = bw; bh_best = bh; bn_best = bn;
+            }
+        }
+    }
+    *BW = bw_best; *BH = bh_best; *BNI = bn_best;
+}
+
+int32_t tc_make_tmap(CUtensorMap* out, TcDType dtype, int rank, void* base, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
+    static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    });
+    if (!encode) return fail(KXC_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const CUtensorMapDataType dt = dtype == kTcBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                    : (dtype == kTcTF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
+    const CUtensorMapSwizzle sw = swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                                       : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    cuuint64_t gdims[5];
+    cuuint64_t gstrides[4];
+    cuuint32_t gbox[5];
+    cuuint32_t estr[5];
+    for (int i = 0; i < rank; ++i) {
+        gdims[i] = dims[i];
+        gbox[i] = box[i];
+        estr[i] = 1;
+        if (i + 1 < rank) gstrides[i] = strides_bytes[i];
+    }
+    const CUresult r = encode(out, dt, (cuuint32_t)rank, base, gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return fail(KXC_B200_ERR_CUDA,
+                    "cuTensorMapEncodeTiled failed (%d): rank %d dims [%llu,%llu,%llu,%llu] box [%u,%u,%u,%u] stride0 %llu", (int)r,
+                    rank, (unsigned long long)dims[0], (unsigned long long)(rank > 1 ? dims[1] : 0),
+                    (unsigned long long)(rank > 2 ? dims[2] : 0), (unsigned long long)(rank > 3 ? dims[3] : 0), box[0],
+                    rank > 1 ? box[1] : 0, rank > 2 ? box[2] : 0, rank > 3 ? box[3] : 0,
+                    (unsigned long long)(rank > 1 ? strides_bytes[0] : 0));
+    }
+    return KXC_B200_OK;
+}
+
+int32_t tc_status_word(int** out) {
+    static std::mutex mu;
+    static int* words[64] = {nullptr};
+    int dev = 0;
+    KXC_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(KXC_B200_ERR_INVALID, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!words[dev]) {
+        KXC_CUDA_TRY(cudaMalloc(&words[dev], sizeof(int)));
+        KXC_CUDA_TRY(cudaMemset(words[dev], 0, sizeof(int)));
+    }
+    *out = words[dev];
+    return KXC_B200_OK;
+}
+
+int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_mode, const void* act_nhwc,
+                      const void* w_packed, int N, int H, int W, int cpad, int Cout, int KH, int KW, int stride, int pad_h,
+                      int pad_w, int dil_h, int dil_w) {
+    const int eb = tc_elem_bytes(dtype);
+    if (stride != 1 && stride != 2) return fail(KXC_B200_ERR_UNSUPPORTED, "tensor-core conv: stride %d", stride);
+    const int row_bytes = cpad * eb;
+    int kb_bytes;
+    if (row_bytes == 32 || row_bytes == 64) kb_bytes = row_bytes;
+    else if (row_bytes % 128 == 0) kb_bytes = 128;
+    else return fail(KXC_B200_ERR_INVALID, "tensor-core conv: %d padded channels x %d bytes is not a K-block multiple", cpad, eb);
+    const int OH = (int)conv_out_dim(H, KH, stride, pad_h, dil_h);
+    const int OW = (int)conv_out_dim(W, KW, stride, pad_w, dil_w);
+    if (OH <= 0 || OW <= 0) return fail(KXC_B200_ERR_INVALID, "tensor-core conv: empty output");
+
+    p->N = N; p->OH = OH; p->OW = OW; p->Cout = Cout;
+    p->taps_h = KH; p->taps_w = KW; p->stride = stride;
+    p->pad_h = pad_h; p->pad_w = pad_w; p->dil_h = dil_h; p->dil_w = dil_w;
+    p->kb_elems = kb_bytes / eb;
+    p->cblocks = row_bytes / kb_bytes;
+    tc_pick_tile(N, OH, OW, &p->BW, &p->BH, &p->BNI);
+    p->tiles_w = (OW + p->BW - 1) / p->BW;
+    p->tiles_h = (OH + p->BH - 1) / p->BH;
+    p->tiles_n = (N + p->BNI - 1) / p->BNI;
+
+    int bn = Cout <= 64 ? 64 : 128;
+    cfg->dtype = dtype; cfg->kb_bytes = kb_bytes; cfg->bn = bn; cfg->out_mode = out_mode;
+    p->tiles_c = (Cout + bn - 1) / bn;
+
+    const uint32_t box[4] = {(uint32_t)p->kb_elems, (uint32_t)p->BW, (uint32_t)p->BH, (uint32_t)p->BNI};
+    uint8_t* base = const_cast<uint8_t*>(static_cast<const uint8_t*>(act_nhwc));
+    if (stride == 1) {
+        const uint64_t dims[4] = {(uint64_t)cpad, (uint64_t)W, (uint64_t)H, (uint64_t)N};
+        const uint64_t strides[3] = {(uint64_t)row_bytes, (uint64_t)W * row_bytes, (uint64_t)H * W * row_bytes};
+        KXC_TRY(tc_make_tmap(&p->tmA[0], dtype, 4, base, dims, strides, box, kb_bytes));
+        for (int i = 1; i < 4; ++i) p->tmA[i] = p->tmA[0];
+    } else {
+        // One map per (row parity, column parity): the stride-2 walk over the input becomes a unit-stride
+        // walk over the pixels of one parity class.
+        for (int hp = 0; hp < 2; ++hp)
+            for (int wp = 0; wp < 2; ++wp) {
+                const int hc = (H - hp + 1) / 2, wc = (W - wp + 1) / 2;
+                CUtensorMap* m = &p->tmA[hp * 2 + wp];
+                if (hc <= 0 || wc <= 0)
+                    return fail(KXC_B200_ERR_UNSUPPORTED, "tensor-core conv: stride 2 over a %dx%d input", H, W);
+                const uint64_t dims[4] = {(uint64_t)cpad, (uint64_t)wc, (uint64_t)hc, (uint64_t)N};
+                const uint64_t strides[3] = {(uint64_t)2 * row_bytes, (uint64_t)2 * W * row_bytes, (uint64_t)H * W * row_bytes};
+                KXC_TRY(tc_make_tmap(m, dtype, 4, base + ((size_t)hp * W + wp) * row_bytes, dims, strides, box, kb_bytes));
+            }
+    }
+    const uint64_t ktot = (uint64_t)KH * KW * cpad;
+    const uint64_t bdims[2] = {ktot, (uint64_t)Cout};
+    const uint64_t bstrides[1] = {ktot * eb};
+    const uint32_t bbox[2] = {(uint32_t)p->kb_elems, (uint32_t)bn};
+    KXC_TRY(tc_make_tmap(&p->tmB, dtype, 2, const_cast<void*>(w_packed), bdims, bstrides, bbox, kb_bytes));
+    KXC_TRY(tc_status_word(&p->status));
+    return KXC_B200_OK;
+}
+
+}  // namespace kxc_b200

@@ -1,0 +1,142 @@
+// Per-operator glue between the reference-layout entry points (NCHW fp32 / int8 tensors) and the
+// tensor-core implicit-GEMM kernel: operand conversion into a stream-ordered workspace, parameter
+// set-up, launch. Shapes the tensor-core path does not take fall back to the CUDA-core kernels
+// (still on the GPU; there is no CPU path).
+#include "common.cuh"
+#include "conv_common.cuh"
+#include "conv_tc.cuh"
+#include "layout.cuh"
+
+namespace kxc_b200 {
+
+namespace {
+
+// Stream-ordered scratch: allocated and freed on the caller's stream, so the call stays asynchronous.
+struct StreamScratch {
+    void* ptr = nullptr;
+    cudaStream_t stream;
+    explicit StreamScratch(cudaStream_t s) : stream(s) {}
+    int32_t alloc(size_t bytes) {
+        cudaError_t e = cudaMallocAsync(&ptr, bytes, stream);
+        if (e != cudaSuccess) {
+            ptr = nullptr;
+            return fail(KXC_B200_ERR_NOMEM, "workspace of %zu bytes: %s", bytes, cudaGetErrorString(e));
+        }
+        return KXC_B200_OK;
+    }
+    ~StreamScratch() {
+        if (ptr) cudaFreeAsync(ptr, stream);
+    }
+};
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+bool tc_shape_ok(const ConvDims& d) {
+    return d.SH == d.SW && (d.SH == 1 || d.SH == 2) && !(d.SH == 2 && (d.H < 2 || d.W < 2)) && d.N <= 65535;
+}
+
+}  // namespace
+
+int32_t conv2d_tensor_core(const float* data, const float* weight, const float* bias, const float* residual, float* out,
+                           const ConvDims& d, int relu, int precision, cudaStream_t s) {
+    if (!tc_shape_ok(d)) return conv2d_fp32_exact(data, weight, bias, residual, out, d, relu, s);
+    const TcDType dt = precision == KXC_B200_PREC_BF16 ? kTcBF16 : kTcTF32;
+    const int eb = tc_elem_bytes(dt);
+    const int cpad = tc_channel_pad(dt, d.C);
+    const size_t act_bytes = align_up((size_t)d.N * d.H * d.W * cpad * eb, 1024);
+    const size_t w_bytes = align_up((size_t)d.O * d.KH * d.KW * cpad * eb, 1024);
+    StreamScratch ws(s);
+    KXC_TRY(ws.alloc(act_bytes + w_bytes));
+    uint8_t* act = static_cast<uint8_t*>(ws.ptr);
+    uint8_t* wp = act + act_bytes;
+    KXC_TRY(nchw_to_nhwc(data, act, dt, d.N, d.C, d.H * d.W, cpad, s));
+    KXC_TRY(pack_weights_ohwi(weight, wp, dt, d.O, d.C, d.KH, d.KW, cpad, s));
+    TcParams p{};
+    TcConfig cfg{};
+    KXC_TRY(tc_setup_conv(&p, &cfg, dt, kOutNCHW_F32, act, wp, d.N, d.H, d.W, cpad, d.O, d.KH, d.KW, d.SH, d.PH, d.PW, d.DH,
+                          d.DW));
+    p.bias = bias;
+    p.residual = residual;
+    p.out = out;
+    p.relu = relu;
+    tc_finish_params(&p);
+    return tc_launch(cfg, p, s);
+}
+
+int32_t conv2d_s8_dispatch(const int8_t* data, const int8_t* weight, const int32_t* bias, const int32_t* multiplier,
+                           const int32_t* shift, int8_t* out, const ConvDims& d, int relu, int force_simt, cudaStream_t s) {
+    if (force_simt || !tc_shape_ok(d)) return conv2d_s8_exact(data, weight, bias, multiplier, shift, out, d, relu, s);
+    const TcDType dt = kTcS8;
+    const int cpad = tc_channel_pad(dt, d.C);
+    const size_t act_bytes = align_up((size_t)d.N * d.H * d.W * cpad, 1024);
+    const size_t w_bytes = align_up((size_t)d.O * d.KH * d.KW * cpad, 1024);
+    StreamScratch ws(s);
+    KXC_TRY(ws.alloc(act_bytes + w_bytes));
+    uint8_t* act = static_cast<uint8_t*>(ws.ptr);
+    uint8_t* wp = act + act_bytes;
+    KXC_TRY(nchw_to_nhwc(data, act, dt, d.N, d.C, d.H * d.W, cpad, s));
+    KXC_TRY(pack_weights_ohwi(weight, wp, dt, d.O, d.C, d.KH, d.KW, cpad, s));
+    TcParams p{};
+    TcConfig cfg{};
+    KXC_TRY(tc_setup_conv(&p, &cfg, dt, kOutNCHW_S8, act, wp, d.N, d.H, d.W, cpad, d.O, d.KH, d.KW, d.SH, d.PH, d.PW, d.DH,
+                          d.DW));
+    p.bias_i32 = bias;
+    p.multiplier = multiplier;
+    p.shift = shift;
+    p.out = out;
+    p.relu = relu;
+    tc_finish_params(&p);
+    return tc_launch(cfg, p, s);
+}
+
+int32_t gemm_tensor_core(const float* a, const float* b, const float* c, float* out, const kxc_b200_gemm_desc& g,
+                         cudaStream_t s) {
+    // alpha/beta scaling is a separately rounded multiply in the reference; only the common
+    // alpha = beta = 1 form is fused into the tensor-core epilogue.
+    if ((g.has_c && ((double)g.alpha != 1.0 || (double)g.beta != 1.0)) || g.m > 65535 * 128)
+        return gemm_fp32_exact(a, b, c, out, g, s);
+    const TcDType dt = g.precision == KXC_B200_PREC_BF16 ? kTcBF16 : kTcTF32;
+    const int eb = tc_elem_bytes(dt);
+    const int kpad = tc_channel_pad(dt, g.k);
+    const size_t a_bytes = align_up((size_t)g.m * kpad * eb, 1024);
+    const size_t b_bytes = align_up((size_t)g.n * kpad * eb, 1024);
+    StreamScratch ws(s);
+    KXC_TRY(ws.alloc(a_bytes + b_bytes));
+    uint8_t* ap = static_cast<uint8_t*>(ws.ptr);
+    uint8_t* bp = ap + a_bytes;
+    KXC_TRY(convert_rows(a, ap, dt, g.m, g.k, kpad, s));
+    if (g.transB || !g.has_c) {
+        KXC_TRY(convert_rows(b, bp, dt, g.n, g.k, kpad, s));  // b is [N, K]
+    } else {
+        KXC_TRY(nchw_to_nhwc(b, bp, dt, 1, g.k, g.n, kpad, s));  // b is [K, N] -> [N, Kpad]
+    }
+    TcParams p{};
+    TcConfig cfg{};
+    // A dense layer is a 1x1 convolution over an M x 1 x 1 "image" batch.
+    KXC_TRY(tc_setup_conv(&p, &cfg, dt, kOutNHWC_F32, ap, bp, g.m, 1, 1, kpad, g.n, 1, 1, 1, 0, 0, 1, 1));
+    p.bias = g.has_c ? c : nullptr;
+    p.out = out;
+    p.relu = 0;
+    tc_finish_params(&p);
+    return tc_launch(cfg, p, s);
+}
+
+}  // namespace kxc_b200
+
+using namespace kxc_b200;
+
+// Reads (and clears) the device status word written by a tensor-core kernel whose bounded wait ran
+// out. Synchronises the stream. 0 = every kernel so far completed its protocol.
+extern "C" int32_t kxc_b200_device_status(void* stream, int32_t* status_out) {
+    KXC_TRY(require_device());
+    int* word = nullptr;
+    KXC_TRY(tc_status_word(&word));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int host = 0;
+    KXC_CUDA_TRY(cudaMemcpyAsync(&host, word, sizeof(int), cudaMemcpyDeviceToHost, s));
+    KXC_CUDA_TRY(cudaStreamSynchronize(s));
+    if (host != 0) KXC_CUDA_TRY(cudaMemsetAsync(word, 0, sizeof(int), s));
+    if (status_out) *status_out = host;
+    if (host != 0) return fail(KXC_B200_ERR_DEVICE_WAIT, "a tensor-core kernel gave up a bounded wait (status %d)", host);
+    return KXC_B200_OK;
+}

@@ -1,0 +1,202 @@
+// Standalone elementwise operators: nn_relu and add (+ optional fused relu).
+// HBM-bound streaming kernels: 16-byte vector accesses, four independent vectors in flight per
+// thread, persistent grid sized as a multiple of the SM count.
+//
+// Bit-exactness against the reference lowering:
+//   relu : `x > 0 ? x : 0`  (NaN -> 0, -0 -> +0)            include/te/topi/nn.h:19-30
+//   add  : one IEEE fp32 add per element (__fadd_rn, never contracted)   include/te/topi/broadcast.h:90-109
+#include "common.cuh"
+
+namespace kxc_b200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+constexpr int kBlocksPerSM = 8;
+
+__device__ __forceinline__ float relu1(float v) { return v > 0.0f ? v : 0.0f; }
+__device__ __forceinline__ float4 relu4(float4 v) {
+    return make_float4(relu1(v.x), relu1(v.y), relu1(v.z), relu1(v.w));
+}
+__device__ __forceinline__ float4 add4(float4 a, float4 b) {
+    return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
+}
+
+// Streaming loads/stores: every element is touched once, keep it out of L1.
+__device__ __forceinline__ float4 ldg_stream(const float4* p) { return __ldcs(p); }
+__device__ __forceinline__ void stg_stream(float4* p, float4 v) { __stcs(p, v); }
+
+template <bool kRelu>
+__global__ void __launch_bounds__(kThreads) relu_vec_kernel(const float4* __restrict__ x, float4* __restrict__ out,
+                                                            int64_t nvec) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+        float4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) v[u] = ldg_stream(x + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) stg_stream(out + i + u * stride, relu4(v[u]));
+    }
+    for (; i < nvec; i += stride) stg_stream(out + i, relu4(ldg_stream(x + i)));
+}
+
+__global__ void relu_scalar_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t begin, int64_t n) {
+    for (int64_t i = begin + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = relu1(x[i]);
+}
+
+template <bool kRelu>
+__global__ void __launch_bounds__(kThreads) add_vec_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
+                                                           float4* __restrict__ out, int64_t nvec) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+        float4 va[kUnroll], vb[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            va[u] = ldg_stream(a + i + u * stride);
+            vb[u] = ldg_stream(b + i + u * stride);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            float4 s = add4(va[u], vb[u]);
+            stg_stream(out + i + u * stride, kRelu ? relu4(s) : s);
+        }
+    }
+    for (; i < nvec; i += stride) {
+        float4 s = add4(ldg_stream(a + i), ldg_stream(b + i));
+        stg_stream(out + i, kRelu ? relu4(s) : s);
+    }
+}
+
+struct BroadcastDims {
+    int rank;
+    int64_t out_shape[6];
+    int64_t a_stride[6];  // 0 where the input dim is 1 (broadcast reads index 0)
+    int64_t b_stride[6];
+};
+
+// General broadcast path (also the unaligned / tail path): one element per thread-iteration.
+template <bool kRelu>
+__global__ void add_broadcast_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+                                     BroadcastDims d, int64_t begin, int64_t total) {
+    for (int64_t lin = begin + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; lin < total;
+         lin += (int64_t)gridDim.x * blockDim.x) {
+        int64_t rem = lin, ai = 0, bi = 0;
+#pragma unroll
+        for (int i = 5; i >= 0; --i) {
+            if (i < d.rank) {
+                const int64_t idx = rem % d.out_shape[i];
+                rem /= d.out_shape[i];
+                ai += idx * d.a_stride[i];
+                bi += idx * d.b_stride[i];
+            }
+        }
+        const float s = __fadd_rn(a[ai], b[bi]);
+        out[lin] = kRelu ? relu1(s) : s;
+    }
+}
+
+int grid_for(int64_t work_items) {
+    int64_t blocks = (work_items + kThreads - 1) / kThreads;
+    const int64_t cap = (int64_t)kNumSMs * kBlocksPerSM;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+}  // namespace
+}  // namespace kxc_b200
+
+using namespace kxc_b200;
+
+extern "C" int32_t kxc_b200_nn_relu(void** packed_args, int64_t numel, void* stream) {
+    KXC_TRY(require_device());
+    if (!packed_args || numel < 0) return fail(KXC_B200_ERR_INVALID, "nn_relu: bad arguments");
+    const float* x = static_cast<const float*>(packed_args[0]);
+    float* out = static_cast<float*>(packed_args[1]);
+    if (numel == 0) return KXC_B200_OK;
+    if (!x || !out) return fail(KXC_B200_ERR_INVALID, "nn_relu: null tensor pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int64_t vec_elems = 0;
+    if (aligned16(x) && aligned16(out)) {
+        const int64_t nvec = numel / 4;
+        vec_elems = nvec * 4;
+        if (nvec > 0)
+            relu_vec_kernel<true><<<grid_for(nvec), kThreads, 0, s>>>(reinterpret_cast<const float4*>(x),
+                                                                        reinterpret_cast<float4*>(out), nvec);
+    }
+    if (vec_elems < numel)
+        relu_scalar_kernel<<<grid_for(numel - vec_elems), kThreads, 0, s>>>(x, out, vec_elems, numel);
+    return check_launch("nn_relu");
+}
+
+extern "C" int32_t kxc_b200_nn_flatten(void** packed_args, int64_t numel, void* stream) {
+    KXC_TRY(require_device());
+    if (!packed_args || numel < 0) return fail(KXC_B200_ERR_INVALID, "nn_flatten: bad arguments");
+    if (numel == 0 || packed_args[0] == packed_args[1]) return KXC_B200_OK;
+    if (!packed_args[0] || !packed_args[1]) return fail(KXC_B200_ERR_INVALID, "nn_flatten: null tensor pointer");
+    KXC_CUDA_TRY(cudaMemcpyAsync(packed_args[1], packed_args[0], (size_t)numel * sizeof(float),
+                                 cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+    return KXC_B200_OK;
+}
+
+extern "C" int32_t kxc_b200_add(void** packed_args, const kxc_b200_add_desc* desc, void* stream) {
+    KXC_TRY(require_device());
+    if (!packed_args || !desc) return fail(KXC_B200_ERR_INVALID, "add: bad arguments");
+    if (desc->rank_a < 0 || desc->rank_a > 6 || desc->rank_b < 0 || desc->rank_b > 6)
+        return fail(KXC_B200_ERR_INVALID, "add: rank must be in [0,6]");
+    BroadcastDims d{};
+    d.rank = desc->rank_a > desc->rank_b ? desc->rank_a : desc->rank_b;
+    if (d.rank == 0) d.rank = 1;
+    int64_t ash[6], bsh[6];
+    for (int i = 0; i < d.rank; ++i) {
+        const int ia = i - (d.rank - desc->rank_a), ib = i - (d.rank - desc->rank_b);
+        ash[i] = ia >= 0 ? desc->shape_a[ia] : 1;
+        bsh[i] = ib >= 0 ? desc->shape_b[ib] : 1;
+        if (ash[i] < 0 || bsh[i] < 0) return fail(KXC_B200_ERR_INVALID, "add: negative extent");
+        if (ash[i] != bsh[i] && ash[i] != 1 && bsh[i] != 1)
+            return fail(KXC_B200_ERR_INVALID, "add: shapes do not broadcast (dim %d: %lld vs %lld)", i,
+                        (long long)ash[i], (long long)bsh[i]);
+        d.out_shape[i] = ash[i] == 1 ? bsh[i] : ash[i];
+    }
+    int64_t total = 1, sa = 1, sb = 1;
+    bool same = true;
+    for (int i = d.rank - 1; i >= 0; --i) {
+        d.a_stride[i] = ash[i] == 1 ? 0 : sa;
+        d.b_stride[i] = bsh[i] == 1 ? 0 : sb;
+        sa *= ash[i];
+        sb *= bsh[i];
+        total *= d.out_shape[i];
+        same = same && (ash[i] == bsh[i]);
+    }
+    if (total == 0) return KXC_B200_OK;
+    const float* a = static_cast<const float*>(packed_args[0]);
+    const float* b = static_cast<const float*>(packed_args[1]);
+    float* out = static_cast<float*>(packed_args[2]);
+    if (!a || !b || !out) return fail(KXC_B200_ERR_INVALID, "add: null tensor pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool relu = desc->relu != 0;
+    int64_t done = 0;
+    if (same && aligned16(a) && aligned16(b) && aligned16(out)) {
+        const int64_t nvec = total / 4;
+        done = nvec * 4;
+        if (nvec > 0) {
+            auto* a4 = reinterpret_cast<const float4*>(a);
+            auto* b4 = reinterpret_cast<const float4*>(b);
+            auto* o4 = reinterpret_cast<float4*>(out);
+            if (relu)
+                add_vec_kernel<true><<<grid_for(nvec), kThreads, 0, s>>>(a4, b4, o4, nvec);
+            else
+                add_vec_kernel<false><<<grid_for(nvec), kThreads, 0, s>>>(a4, b4, o4, nvec);
+        }
+    }
+    if (done < total) {
+        if (relu)
+            add_broadcast_kernel<true><<<grid_for(total - done), kThreads, 0, s>>>(a, b, out, d, done, total);
+        else
+            add_broadcast_kernel<false><<<grid_for(total - done), kThreads, 0, s>>>(a, b, out, d, done, total);
+    }
+    return check_launch("add");
+}

@@ -1,0 +1,132 @@
+// Layout / precision conversion kernels (HBM-bound, coalesced on both sides through a shared-memory
+// transpose tile).
+#include "layout.cuh"
+
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace kxc_b200 {
+namespace {
+
+__device__ __forceinline__ float round_tf32_rne(float x) {
+    uint32_t u = __float_as_uint(x);
+    if ((u & 0x7f800000u) != 0x7f800000u) u = (u + 0xfffu + ((u >> 13) & 1u)) & 0xffffe000u;
+    return __uint_as_float(u);
+}
+
+template <typename TOut>
+__device__ __forceinline__ TOut convert_to(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 convert_to<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ float convert_to<float>(float v) { return round_tf32_rne(v); }
+
+template <typename TIn, typename TOut>
+__device__ __forceinline__ TOut convert_elem(TIn v) { return convert_to<TOut>((float)v); }
+template <>
+__device__ __forceinline__ int8_t convert_elem<int8_t, int8_t>(int8_t v) { return v; }
+
+// grid (ceil(HW/32), ceil(cpad/32), N), block (32, 8)
+template <typename TIn, typename TOut>
+__global__ void nchw_to_nhwc_kernel(const TIn* __restrict__ in, TOut* __restrict__ out, int C, int HW, int cpad) {
+    __shared__ TIn tile[32][33];
+    const int n = blockIdx.z;
+    const int hw0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const TIn* src = in + (size_t)n * C * HW;
+    TOut* dst = out + (size_t)n * HW * cpad;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int c = c0 + threadIdx.y + 8 * k, hw = hw0 + threadIdx.x;
+        tile[threadIdx.y + 8 * k][threadIdx.x] = (c < C && hw < HW) ? src[(size_t)c * HW + hw] : (TIn)0;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int hw = hw0 + threadIdx.y + 8 * k, c = c0 + threadIdx.x;
+        if (hw < HW && c < cpad) dst[(size_t)hw * cpad + c] = convert_elem<TIn, TOut>(tile[threadIdx.x][threadIdx.y + 8 * k]);
+    }
+}
+
+template <typename TIn, typename TOut>
+__global__ void pack_weights_kernel(const TIn* __restrict__ w, TOut* __restrict__ out, int O, int C, int KH, int KW, int cpad) {
+    const int64_t total = (int64_t)O * KH * KW * cpad;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % cpad);
+        int64_t t = i / cpad;
+        const int kw = (int)(t % KW); t /= KW;
+        const int kh = (int)(t % KH);
+        const int o = (int)(t / KH);
+        out[i] = c < C ? convert_elem<TIn, TOut>(w[(((int64_t)o * C + c) * KH + kh) * KW + kw]) : convert_elem<TIn, TOut>((TIn)0);
+    }
+}
+
+template <typename TOut>
+__global__ void convert_rows_kernel(const float* __restrict__ in, TOut* __restrict__ out, int64_t rows, int cols, int cpad) {
+    const int64_t total = rows * cpad;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % cpad);
+        const int64_t r = i / cpad;
+        out[i] = convert_to<TOut>(c < cols ? in[r * cols + c] : 0.0f);
+    }
+}
+
+int grid_1d(int64_t items, int threads) {
+    int64_t b = (items + threads - 1) / threads;
+    const int64_t cap = (int64_t)kNumSMs * 16;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+}  // namespace
+
+int32_t nchw_to_nhwc(const void* in, void* out, TcDType dtype, int N, int C, int HW, int cpad, cudaStream_t s) {
+    if (N == 0) return KXC_B200_OK;
+    if (N > 65535) return fail(KXC_B200_ERR_UNSUPPORTED, "layout transform: batch %d exceeds the grid limit", N);
+    const dim3 grid((HW + 31) / 32, (cpad + 31) / 32, N), block(32, 8);
+    switch (dtype) {
+        case kTcBF16:
+            nchw_to_nhwc_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>(static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out), C, HW, cpad);
+            break;
+        case kTcTF32:
+            nchw_to_nhwc_kernel<float, float><<<grid, block, 0, s>>>(static_cast<const float*>(in), static_cast<float*>(out), C, HW, cpad);
+            break;
+        case kTcS8:
+            nchw_to_nhwc_kernel<int8_t, int8_t><<<grid, block, 0, s>>>(static_cast<const int8_t*>(in), static_cast<int8_t*>(out), C, HW, cpad);
+            break;
+    }
+    return check_launch("nchw_to_nhwc");
+}
+
+int32_t pack_weights_ohwi(const void* w, void* out, TcDType dtype, int O, int C, int KH, int KW, int cpad, cudaStream_t s) {
+    const int64_t total = (int64_t)O * KH * KW * cpad;
+    const int grid = grid_1d(total, 256);
+    switch (dtype) {
+        case kTcBF16:
+            pack_weights_kernel<float, __nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const float*>(w), static_cast<__nv_bfloat16*>(out), O, C, KH, KW, cpad);
+            break;
+        case kTcTF32:
+            pack_weights_kernel<float, float><<<grid, 256, 0, s>>>(static_cast<const float*>(w), static_cast<float*>(out), O, C, KH, KW, cpad);
+            break;
+        case kTcS8:
+            pack_weights_kernel<int8_t, int8_t><<<grid, 256, 0, s>>>(static_cast<const int8_t*>(w), static_cast<int8_t*>(out), O, C, KH, KW, cpad);
+            break;
+    }
+    return check_launch("pack_weights");
+}
+
+int32_t convert_rows(const float* in, void* out, TcDType dtype, int64_t rows, int cols, int cpad, cudaStream_t s) {
+    const int64_t total = rows * cpad;
+    if (total == 0) return KXC_B200_OK;
+    const int grid = grid_1d(total, 256);
+    if (dtype == kTcBF16)
+        convert_rows_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(in, static_cast<__nv_bfloat16*>(out), rows, cols, cpad);
+    else if (dtype == kTcTF32)
+        convert_rows_kernel<float><<<grid, 256, 0, s>>>(in, static_cast<float*>(out), rows, cols, cpad);
+    else
+        return fail(KXC_B200_ERR_INVALID, "convert_rows: dtype");
+    return check_launch("convert_rows");
+}
+
+}  // namespace kxc_b200

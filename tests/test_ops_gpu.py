@@ -1,0 +1,271 @@
+"""GPU parity tests, per operator, through the C ABI (ctypes) against the CPU oracle.
+
+Bit-exact: relu, add, max/avg pool, global avg pool, the fused pool chain, fp32-mode conv/gemm,
+int8 conv + requantize. Tolerance (the reference's own metric, test/onnx_importer_test.cpp:161-177):
+1e-3 for tf32, 1e-2 for bf16, measured against the oracle run on identically rounded operands.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_bit_exact, assert_close, ref_metric
+from oracle import port
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from hdkx_aicompiler_b200 import ops as _ops
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    return _ops
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    torch.cuda.synchronize()
+    return t.cpu().numpy()
+
+
+SPECIALS = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1e-45, -1e-45, 3.4e38, -3.4e38], dtype=f32)
+
+
+# ---------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("n", [0, 1, 3, 4, 5, 1023, 4096, 1 << 20, (1 << 20) + 7])
+def test_relu_bit_exact(ops, rng, n):
+    x = rng.normal(size=n).astype(f32)
+    x[: min(n, SPECIALS.size)] = SPECIALS[: min(n, SPECIALS.size)]
+    assert_bit_exact(host(ops.nn_relu(dev(x))), port.relu(x), f"relu n={n}")
+
+
+def test_relu_unaligned_view(ops, rng):
+    x = rng.normal(size=10001).astype(f32)
+    t = dev(x)[1:]  # 4-byte aligned only
+    assert_bit_exact(host(ops.nn_relu(t)), port.relu(x[1:]), "relu unaligned")
+
+
+@pytest.mark.parametrize("sa,sb", [((2, 3), (3,)), ((4, 8, 14, 14), (4, 8, 14, 14)), ((2, 5, 7, 9), (5, 1, 1)),
+                                   ((2, 5, 7, 9), (1, 5, 1, 9)), ((1,), (3, 2)), ((2, 1, 4), (1, 3, 1)),
+                                   ((32, 64, 8, 8), (32, 64, 8, 8)), ((0, 4), (4,)), ((7,), (7,))])
+@pytest.mark.parametrize("relu", [False, True])
+def test_add_bit_exact(ops, rng, sa, sb, relu):
+    a = rng.normal(size=sa).astype(f32)
+    b = rng.normal(size=sb).astype(f32)
+    if a.size > 8:
+        a.ravel()[:9] = SPECIALS
+    expect = port.add(a, b)
+    if relu:
+        expect = port.relu(expect)
+    assert_bit_exact(host(ops.add(dev(a), dev(b), relu=relu)), expect, f"add {sa}+{sb}")
+
+
+def test_add_rejects_bad_broadcast(ops):
+    from hdkx_aicompiler_b200 import KxcError
+    with pytest.raises((KxcError, RuntimeError)):
+        ops.add(torch.zeros(2, 3, device="cuda"), torch.zeros(2, 4, device="cuda"))
+
+
+# ---------------------------------------------------------------- pooling
+POOL_CASES = [
+    ((1, 1, 4, 4), (2, 2), (2, 2), (0, 0, 0, 0), False),       # the reference's TestMaxPool2D shape
+    ((2, 3, 16, 16), (3, 3), (2, 2), (1, 1, 1, 1), False),     # fast path (W % 8 == 0, H % 4 == 0)
+    ((2, 3, 12, 24), (3, 3), (2, 2), (1, 1, 1, 1), False),     # fast path, non-square
+    ((2, 3, 14, 14), (3, 3), (2, 2), (1, 1, 1, 1), False),     # generic path (W % 8 != 0)
+    ((1, 2, 9, 7), (3, 2), (2, 1), (1, 0, 0, 1), True),        # asymmetric padding, ceil mode
+    ((1, 2, 7, 7), (2, 2), (2, 2), (0, 0, 0, 0), True),
+    ((3, 5, 10, 10), (3, 3), (1, 1), (1, 1, 1, 1), False),
+    ((0, 4, 8, 8), (2, 2), (2, 2), (0, 0, 0, 0), False),       # empty batch
+]
+
+
+@pytest.mark.parametrize("shape,k,s,p,ceil", POOL_CASES)
+def test_max_pool_bit_exact(ops, rng, shape, k, s, p, ceil):
+    x = rng.uniform(-1, 1, shape).astype(f32)
+    if x.size > 16:
+        x.ravel()[3:12] = SPECIALS
+        x.ravel()[-1] = np.nan
+    assert_bit_exact(host(ops.nn_max_pool2d(dev(x), k, s, p, ceil)), port.max_pool2d(x, k, s, p, ceil), f"max_pool {shape}")
+
+
+@pytest.mark.parametrize("shape,k,s,p,ceil", POOL_CASES)
+def test_avg_pool_bit_exact(ops, rng, shape, k, s, p, ceil):
+    x = rng.uniform(-1, 1, shape).astype(f32)
+    assert_bit_exact(host(ops.nn_avg_pool2d(dev(x), k, s, p, ceil)), port.avg_pool2d(x, k, s, p, ceil), f"avg_pool {shape}")
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 16, 16), (1, 3, 14, 14), (4, 64, 112, 112)])
+def test_pool_add_relu_chain_bit_exact(ops, rng, shape):
+    x = rng.uniform(-1, 1, shape).astype(f32)
+    oh = port.pool_out_dim(shape[2], 3, 2, 1, 1)
+    ow = port.pool_out_dim(shape[3], 3, 2, 1, 1)
+    res = rng.uniform(-1, 1, shape[:2] + (oh, ow)).astype(f32)
+    expect = port.relu(port.add(port.max_pool2d(x, (3, 3), (2, 2), (1, 1, 1, 1)), res))
+    fused = host(ops.max_pool2d_add_relu(dev(x), dev(res), (3, 3), (2, 2), (1, 1, 1, 1)))
+    assert_bit_exact(fused, expect, "fused chain")
+    unfused = host(ops.nn_relu(ops.add(ops.nn_max_pool2d(dev(x), (3, 3), (2, 2), (1, 1, 1, 1)), dev(res))))
+    assert_bit_exact(unfused, expect, "unfused chain")
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 2, 2), (3, 512, 7, 7), (2, 5, 8, 8), (1, 3, 56, 56), (2, 2, 120, 120), (0, 3, 4, 4)])
+def test_global_avg_pool_bit_exact(ops, rng, shape):
+    x = rng.normal(size=shape).astype(f32)
+    assert_bit_exact(host(ops.nn_global_avg_pool2d(dev(x))), port.global_avg_pool2d(x), f"gap {shape}")
+
+
+def test_flatten(ops, rng):
+    x = rng.normal(size=(3, 4, 2, 5)).astype(f32)
+    assert_bit_exact(host(ops.nn_flatten(dev(x))), x.reshape(3, -1), "flatten")
+
+
+# ---------------------------------------------------------------- conv2d
+CONV_CASES = [
+    # (N, C, H, W, O, KH, KW, stride, pad, dil)
+    (1, 1, 3, 3, 1, 2, 2, 1, 0, 1),       # the reference's TestConv2D shape
+    (2, 64, 12, 12, 64, 3, 3, 1, 1, 1),
+    (2, 64, 16, 16, 128, 3, 3, 2, 1, 1),
+    (2, 64, 16, 16, 128, 1, 1, 2, 0, 1),
+    (3, 128, 14, 14, 256, 3, 3, 1, 1, 1),
+    (2, 3, 32, 32, 64, 7, 7, 2, 3, 1),
+    (3, 20, 9, 7, 10, 3, 3, 1, 1, 1),
+    (2, 40, 11, 13, 72, 3, 3, 1, 1, 2),   # dilation 2
+    (5, 512, 7, 7, 512, 3, 3, 1, 1, 1),
+    (2, 16, 10, 10, 24, 5, 5, 2, 2, 1),
+    (0, 8, 6, 6, 8, 3, 3, 1, 1, 1),       # empty batch
+]
+
+
+def conv_inputs(rng, N, C, H, W, O, KH, KW):
+    x = rng.uniform(-1, 1, (N, C, H, W)).astype(f32)
+    w = rng.normal(0, np.sqrt(2.0 / (C * KH * KW)), (O, C, KH, KW)).astype(f32)
+    b = rng.normal(0, 0.01, (O,)).astype(f32)
+    return x, w, b
+
+
+def conv_expect(x, w, b, res, relu, s, p, d, rounder=None):
+    if rounder is not None:
+        x, w = rounder(x), rounder(w)
+    y = port.conv2d(x, w, b, (s, s), (p, p), (d, d))
+    if res is not None:
+        y = port.add(y, res)
+    if relu:
+        y = port.relu(y)
+    return y
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv2d_fp32_mode_bit_exact(ops, rng, case):
+    N, C, H, W, O, KH, KW, s, p, d = case
+    x, w, b = conv_inputs(rng, N, C, H, W, O, KH, KW)
+    got = host(ops.nn_conv2d(dev(x), dev(w), dev(b), (s, s), (p, p), (d, d), relu=True, precision="fp32"))
+    assert_bit_exact(got, conv_expect(x, w, b, None, True, s, p, d), f"conv fp32 {case}")
+
+
+@pytest.mark.parametrize("precision,tol,rounder", [("tf32", 1e-3, port.round_tf32), ("bf16", 1e-2, port.round_bf16)])
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv2d_tensor_core(ops, rng, case, precision, tol, rounder):
+    N, C, H, W, O, KH, KW, s, p, d = case
+    x, w, b = conv_inputs(rng, N, C, H, W, O, KH, KW)
+    for with_bias, with_res, relu in [(True, False, True), (True, True, True), (False, False, False)]:
+        oh, ow = port.conv_out_dim(H, KH, s, p, d), port.conv_out_dim(W, KW, s, p, d)
+        res = rng.uniform(-1, 1, (N, O, oh, ow)).astype(f32) if with_res else None
+        got = host(ops.nn_conv2d(dev(x), dev(w), dev(b) if with_bias else None, (s, s), (p, p), (d, d),
+                                 residual=dev(res) if with_res else None, relu=relu, precision=precision))
+        assert ops.device_status() == 0
+        what = f"conv {precision} {case} bias={with_bias} res={with_res} relu={relu}"
+        # north-star tolerance against the fp32 reference arithmetic on the original operands
+        assert_close(got, conv_expect(x, w, b if with_bias else None, res, relu, s, p, d), tol, what)
+        # and the sharper check: same operands as the tensor cores see, only the summation order differs
+        exp_r = conv_expect(x, w, b if with_bias else None, res, relu, s, p, d, rounder)
+        max_abs, max_rel = ref_metric(got, exp_r)
+        assert min(max_abs, max_rel) <= 2e-5 * max(1.0, np.sqrt(C * KH * KW) / 8), f"{what}: {max_abs:.3e} {max_rel:.3e}"
+
+
+def test_conv2d_config1_shape(ops, rng):
+    """BASELINE config 1: conv 1x64x56x56 * 64x64x3x3 + bias + ReLU."""
+    x = rng.uniform(-1, 1, (1, 64, 56, 56)).astype(f32)
+    w = rng.normal(0, np.sqrt(2 / 576), (64, 64, 3, 3)).astype(f32)
+    b = rng.normal(0, 0.01, (64,)).astype(f32)
+    expect = port.relu(port.conv2d(x, w, b, (1, 1), (1, 1)))
+    assert_bit_exact(host(ops.nn_conv2d(dev(x), dev(w), dev(b), (1, 1), (1, 1), relu=True, precision="fp32")), expect, "cfg1 fp32")
+    assert_close(host(ops.nn_conv2d(dev(x), dev(w), dev(b), (1, 1), (1, 1), relu=True, precision="tf32")), expect, 1e-3, "cfg1 tf32")
+    assert_close(host(ops.nn_conv2d(dev(x), dev(w), dev(b), (1, 1), (1, 1), relu=True, precision="bf16")), expect, 1e-2, "cfg1 bf16")
+    assert ops.device_status() == 0
+
+
+def test_conv2d_argument_errors(ops):
+    from hdkx_aicompiler_b200 import KxcError
+    x = torch.zeros(1, 4, 3, 3, device="cuda")
+    w = torch.zeros(2, 4, 5, 5, device="cuda")
+    with pytest.raises(KxcError):  # empty output
+        ops.nn_conv2d(x, w, precision="fp32")
+    with pytest.raises(ValueError):
+        ops.nn_conv2d(x, torch.zeros(2, 3, 1, 1, device="cuda"))
+
+
+# ---------------------------------------------------------------- int8 conv + requantize
+def s8_inputs(rng, N, C, H, W, O, KH, KW):
+    x = np.clip(np.round(rng.normal(0, 32, (N, C, H, W))), -128, 127).astype(np.int8)
+    wf = rng.normal(0, np.sqrt(2.0 / (C * KH * KW)), (O, C, KH, KW))
+    scale = np.abs(wf).reshape(O, -1).max(axis=1) / 127.0
+    w = np.clip(np.round(wf / scale[:, None, None, None]), -127, 127).astype(np.int8)
+    b = rng.integers(-1024, 1025, (O,)).astype(np.int32)
+    m = rng.integers(2 ** 30, 2 ** 31, (O,)).astype(np.int64).astype(np.int32)
+    sh = rng.integers(8, 16, (O,)).astype(np.int32)
+    return x, w, b, m, sh
+
+
+@pytest.mark.parametrize("simt", [True, False])
+@pytest.mark.parametrize("case", [c for c in CONV_CASES if c[0] > 0])
+def test_conv2d_s8_bit_exact(ops, rng, case, simt):
+    N, C, H, W, O, KH, KW, s, p, d = case
+    x, w, b, m, sh = s8_inputs(rng, N, C, H, W, O, KH, KW)
+    for relu in (True, False):
+        got = host(ops.nn_conv2d_s8(dev(x), dev(w), dev(b), dev(m), dev(sh), (s, s), (p, p), (d, d), relu=relu, simt=simt))
+        assert ops.device_status() == 0
+        expect = port.conv2d_s8_requant(x, w, b, m, sh, relu, (s, s), (p, p), (d, d))
+        assert np.array_equal(got, expect), f"s8 conv {case} relu={relu} simt={simt}: {np.count_nonzero(got != expect)} differ"
+
+
+# ---------------------------------------------------------------- dense / gemm
+@pytest.mark.parametrize("M,N,K", [(2, 2, 3), (2, 4, 3), (5, 11, 37), (33, 1000, 512), (130, 72, 200), (0, 4, 8)])
+def test_gemm_fp32_mode_bit_exact(ops, rng, M, N, K):
+    a = rng.normal(size=(M, K)).astype(f32)
+    b = rng.normal(size=(N, K)).astype(f32)
+    c = rng.normal(size=(N,)).astype(f32)
+    assert_bit_exact(host(ops.nn_dense(dev(a), dev(b), precision="fp32")), port.dense(a, b), "dense fp32")
+    assert_bit_exact(host(ops.nn_gemm(dev(a), dev(b), dev(c), 1.0, 1.0, 0, 1, precision="fp32")), port.gemm(a, b, c), "gemm fp32")
+    assert_bit_exact(host(ops.nn_gemm(dev(a), dev(b), dev(c), 0.5, 2.0, 0, 1, precision="fp32")),
+                     port.gemm(a, b, c, 0.5, 2.0), "gemm alpha/beta fp32")
+    bt = np.ascontiguousarray(b.T)
+    assert_bit_exact(host(ops.nn_gemm(dev(a), dev(bt), dev(c), 1.0, 1.0, 0, 0, precision="fp32")),
+                     port.gemm(a, bt, c, 1.0, 1.0, 0, 0), "gemm transB=0 fp32")
+
+
+@pytest.mark.parametrize("precision,tol,rounder", [("tf32", 1e-3, port.round_tf32), ("bf16", 1e-2, port.round_bf16)])
+@pytest.mark.parametrize("M,N,K", [(2, 4, 3), (5, 11, 37), (33, 1000, 512), (130, 72, 200), (300, 256, 64)])
+def test_gemm_tensor_core(ops, rng, M, N, K, precision, tol, rounder):
+    a = (rng.normal(size=(M, K)) / np.sqrt(K)).astype(f32)
+    b = rng.normal(size=(N, K)).astype(f32)
+    c = rng.normal(size=(N,)).astype(f32)
+    got = host(ops.nn_gemm(dev(a), dev(b), dev(c), 1.0, 1.0, 0, 1, precision=precision))
+    assert ops.device_status() == 0
+    assert_close(got, port.gemm(a, b, c), tol, f"gemm {precision}")
+    max_abs, max_rel = ref_metric(got, port.gemm(rounder(a), rounder(b), c))
+    assert min(max_abs, max_rel) <= 2e-5 * max(1.0, np.sqrt(K) / 8)
+    got_d = host(ops.nn_dense(dev(a), dev(b), precision=precision))
+    assert_close(got_d, port.dense(a, b), tol, f"dense {precision}")
+    bt = np.ascontiguousarray(b.T)
+    got_t = host(ops.nn_gemm(dev(a), dev(bt), dev(c), 1.0, 1.0, 0, 0, precision=precision))
+    assert_close(got_t, port.gemm(a, bt, c, 1.0, 1.0, 0, 0), tol, f"gemm transB=0 {precision}")
+    assert ops.device_status() == 0
+
+
+def test_gemm_transA_rejected(ops):
+    from hdkx_aicompiler_b200 import KxcError
+    z = torch.zeros(2, 2, device="cuda")
+    with pytest.raises(KxcError):
+        ops.nn_gemm(z, z, torch.zeros(2, device="cuda"), transA=1, transB=1)
