@@ -11,3 +11,4 @@ a Blackwell GPU is missing.
 """
 from . import _lib  # noqa: F401
 from ._lib import KxcError, library_path, load  # noqa: F401
+from . import plan  # noqa: F401,E402  (registers the plan entry points with the binding table)

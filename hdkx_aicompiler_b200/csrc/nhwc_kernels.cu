@@ -1,0 +1,290 @@
+// Kernels of the whole-graph executor that work on its internal activation format: NHWC
+// (channel-innermost), bf16 or fp32 storage. All HBM-bound: 16-byte vector accesses along the
+// channel axis, grids sized as a multiple of the SM count.
+//
+// Semantics follow the reference ops exactly on the stored values:
+//   max pool  m = -inf; v = inb ? x : -1e30f; m = (m > v) ? m : v  (include/te/topi/nn.h:161-229)
+//   gap       s = 0; s = s + x over (h, w) in order; s / (float)(H*W)  (include/te/topi/nn.h:260-287)
+//   add/relu  one fp32 add, `x > 0 ? x : 0`  (include/te/topi/broadcast.h:90-109, nn.h:19-30)
+// with bf16 storage rounding (nearest even) applied when a result is written back as bf16.
+#include "nhwc_kernels.cuh"
+
+#include <cuda_bf16.h>
+
+#include <cmath>
+
+#include "common.cuh"
+
+namespace kxc_b200 {
+namespace {
+
+constexpr int kThreads = 256;
+
+// 16-byte vector of activations <-> fp32 lanes
+template <typename T>
+struct Vec;
+template <>
+struct Vec<__nv_bfloat16> {
+    static constexpr int kLanes = 8;
+    __device__ static void load(const __nv_bfloat16* p, float (&f)[8]) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            f[2 * k] = __uint_as_float(w[k] << 16);
+            f[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+        }
+    }
+    __device__ static void store(__nv_bfloat16* p, const float (&f)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+            w[k] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+template <>
+struct Vec<float> {
+    static constexpr int kLanes = 4;
+    __device__ static void load(const float* p, float (&f)[4]) {
+        const float4 u = __ldg(reinterpret_cast<const float4*>(p));
+        f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
+    }
+    __device__ static void store(float* p, const float (&f)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) maxpool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ out, int N, int H,
+                                                                int W, int C, int OH, int OW, int KH, int KW, int SH, int SW,
+                                                                int PT, int PL) {
+    constexpr int L = Vec<T>::kLanes;
+    const int cg = C / L;
+    const int64_t total = (int64_t)N * OH * OW * cg;
+    for (int64_t lin = (int64_t)blockIdx.x * kThreads + threadIdx.x; lin < total; lin += (int64_t)gridDim.x * kThreads) {
+        const int g = (int)(lin % cg);
+        int64_t t = lin / cg;
+        const int ow = (int)(t % OW); t /= OW;
+        const int oh = (int)(t % OH);
+        const int n = (int)(t / OH);
+        float m[L];
+#pragma unroll
+        for (int j = 0; j < L; ++j) m[j] = -INFINITY;
+        for (int rh = 0; rh < KH; ++rh) {
+            const int ih = oh * SH + rh - PT;
+            for (int rw = 0; rw < KW; ++rw) {
+                const int iw = ow * SW + rw - PL;
+                float v[L];
+                if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
+                    Vec<T>::load(x + (((int64_t)n * H + ih) * W + iw) * C + g * L, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < L; ++j) v[j] = -1e30f;
+                }
+#pragma unroll
+                for (int j = 0; j < L; ++j) m[j] = (m[j] > v[j]) ? m[j] : v[j];
+            }
+        }
+        Vec<T>::store(out + lin * L, m);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) gap_nhwc_kernel(const T* __restrict__ x, T* __restrict__ out, int N, int HW, int C) {
+    constexpr int L = Vec<T>::kLanes;
+    const int cg = C / L;
+    const int64_t total = (int64_t)N * cg;
+    const float div = (float)HW;
+    for (int64_t lin = (int64_t)blockIdx.x * kThreads + threadIdx.x; lin < total; lin += (int64_t)gridDim.x * kThreads) {
+        const int g = (int)(lin % cg);
+        const int n = (int)(lin / cg);
+        float s[L];
+#pragma unroll
+        for (int j = 0; j < L; ++j) s[j] = 0.0f;
+        const T* p = x + (int64_t)n * HW * C + g * L;
+        for (int i = 0; i < HW; ++i) {
+            float v[L];
+            Vec<T>::load(p + (int64_t)i * C, v);
+#pragma unroll
+            for (int j = 0; j < L; ++j) s[j] = __fadd_rn(s[j], v[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < L; ++j) s[j] = __fdiv_rn(s[j], div);
+        Vec<T>::store(out + lin * L, s);
+    }
+}
+
+// out = relu?(a (+ b)) on flat arrays of the same shape; b may be null (plain relu)
+template <typename T>
+__global__ void __launch_bounds__(kThreads) eltwise_nhwc_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                                T* __restrict__ out, int64_t nvec, int relu) {
+    constexpr int L = Vec<T>::kLanes;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * kThreads) {
+        float va[L];
+        Vec<T>::load(a + i * L, va);
+        if (b != nullptr) {
+            float vb[L];
+            Vec<T>::load(b + i * L, vb);
+#pragma unroll
+            for (int j = 0; j < L; ++j) va[j] = __fadd_rn(va[j], vb[j]);
+        }
+        if (relu) {
+#pragma unroll
+            for (int j = 0; j < L; ++j) va[j] = va[j] > 0.0f ? va[j] : 0.0f;
+        }
+        Vec<T>::store(out + i * L, va);
+    }
+}
+
+// NHWC (bf16/fp32) -> NCHW fp32 through a shared-memory transpose tile; grid (ceil(HW/32), ceil(C/32), N)
+template <typename T>
+__global__ void nhwc_to_nchw_kernel(const T* __restrict__ in, float* __restrict__ out, int C, int HW) {
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z, hw0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const T* src = in + (size_t)n * HW * C;
+    float* dst = out + (size_t)n * C * HW;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int hw = hw0 + threadIdx.y + 8 * k, c = c0 + threadIdx.x;
+        tile[threadIdx.y + 8 * k][threadIdx.x] = (hw < HW && c < C) ? (float)src[(size_t)hw * C + c] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int c = c0 + threadIdx.y + 8 * k, hw = hw0 + threadIdx.x;
+        if (c < C && hw < HW) dst[(size_t)c * HW + hw] = tile[threadIdx.x][threadIdx.y + 8 * k];
+    }
+}
+
+__device__ __forceinline__ float round_tf32_rne(float x) {
+    uint32_t u = __float_as_uint(x);
+    if ((u & 0x7f800000u) != 0x7f800000u) u = (u + 0xfffu + ((u >> 13) & 1u)) & 0xffffe000u;
+    return __uint_as_float(u);
+}
+template <typename T>
+__device__ __forceinline__ T to_operand(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 to_operand<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ float to_operand<float>(float v) { return round_tf32_rne(v); }
+
+// Stem input packing: NCHW fp32 [N,C<=4,H,W] -> [N][H+2*pad_h][Wp][4] operand type with a zero border,
+// so that the 8 consecutive pixels x 4 channels starting at an even column form one K block.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) stem_pack_kernel(const float* __restrict__ x, T* __restrict__ out, int N, int C,
+                                                             int H, int W, int Hp, int Wp, int pad_h, int pad_w) {
+    const int64_t total = (int64_t)N * Hp * Wp;
+    for (int64_t lin = (int64_t)blockIdx.x * kThreads + threadIdx.x; lin < total; lin += (int64_t)gridDim.x * kThreads) {
+        const int wp = (int)(lin % Wp);
+        int64_t t = lin / Wp;
+        const int hp = (int)(t % Hp);
+        const int n = (int)(t / Hp);
+        const int h = hp - pad_h, w = wp - pad_w;
+        T v[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float f = 0.0f;
+            if (c < C && h >= 0 && h < H && w >= 0 && w < W) f = __ldg(x + (((int64_t)n * C + c) * H + h) * W + w);
+            v[c] = to_operand<T>(f);
+        }
+        T* dst = out + lin * 4;
+        if constexpr (sizeof(T) == 2) {
+            *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(v);
+        } else {
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(v);
+        }
+    }
+}
+
+// Stem weights: OIHW fp32 [O,C<=4,KH,KW<=8] -> [O][KH][8][4] operand type, zero for kw >= KW or c >= C
+template <typename T>
+__global__ void stem_pack_weights_kernel(const float* __restrict__ w, T* __restrict__ out, int O, int C, int KH, int KW) {
+    const int total = O * KH * 32;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int c = i & 3, kw = (i >> 2) & 7;
+        const int kh = (i >> 5) % KH, o = (i >> 5) / KH;
+        float f = 0.0f;
+        if (c < C && kw < KW) f = w[((o * C + c) * KH + kh) * KW + kw];
+        out[i] = to_operand<T>(f);
+    }
+}
+
+int grid_for(int64_t items, int per_sm = 8) {
+    int64_t b = (items + kThreads - 1) / kThreads;
+    const int64_t cap = (int64_t)kNumSMs * per_sm;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+}  // namespace
+
+#define KXC_DISPATCH_ACT(dtype, ...)                         \
+    if ((dtype) == kTcBF16) {                                \
+        using T = __nv_bfloat16;                             \
+        __VA_ARGS__;                                         \
+    } else if ((dtype) == kTcTF32) {                         \
+        using T = float;                                     \
+        __VA_ARGS__;                                         \
+    } else {                                                 \
+        return fail(KXC_B200_ERR_INVALID, "activation dtype"); \
+    }
+
+int32_t maxpool_nhwc(const void* x, void* out, TcDType dt, int N, int H, int W, int C, int OH, int OW, int KH, int KW, int SH,
+                     int SW, int PT, int PL, cudaStream_t s) {
+    const int lanes = dt == kTcBF16 ? 8 : 4;
+    if (C % lanes != 0) return fail(KXC_B200_ERR_UNSUPPORTED, "NHWC max pool: %d channels is not a multiple of %d", C, lanes);
+    const int64_t items = (int64_t)N * OH * OW * (C / lanes);
+    if (items == 0) return KXC_B200_OK;
+    KXC_DISPATCH_ACT(dt, (maxpool_nhwc_kernel<T><<<grid_for(items, 16), kThreads, 0, s>>>(
+                             static_cast<const T*>(x), static_cast<T*>(out), N, H, W, C, OH, OW, KH, KW, SH, SW, PT, PL)));
+    return check_launch("maxpool_nhwc");
+}
+
+int32_t gap_nhwc(const void* x, void* out, TcDType dt, int N, int HW, int C, cudaStream_t s) {
+    const int lanes = dt == kTcBF16 ? 8 : 4;
+    if (C % lanes != 0) return fail(KXC_B200_ERR_UNSUPPORTED, "NHWC global pool: %d channels is not a multiple of %d", C, lanes);
+    const int64_t items = (int64_t)N * (C / lanes);
+    if (items == 0) return KXC_B200_OK;
+    KXC_DISPATCH_ACT(dt, (gap_nhwc_kernel<T><<<grid_for(items, 16), kThreads, 0, s>>>(static_cast<const T*>(x),
+                                                                                    static_cast<T*>(out), N, HW, C)));
+    return check_launch("gap_nhwc");
+}
+
+int32_t eltwise_nhwc(const void* a, const void* b, void* out, TcDType dt, int64_t numel, int relu, cudaStream_t s) {
+    const int lanes = dt == kTcBF16 ? 8 : 4;
+    if (numel % lanes != 0) return fail(KXC_B200_ERR_UNSUPPORTED, "NHWC elementwise: %lld elements is not a multiple of %d", (long long)numel, lanes);
+    const int64_t nvec = numel / lanes;
+    if (nvec == 0) return KXC_B200_OK;
+    KXC_DISPATCH_ACT(dt, (eltwise_nhwc_kernel<T><<<grid_for(nvec, 16), kThreads, 0, s>>>(
+                             static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), nvec, relu)));
+    return check_launch("eltwise_nhwc");
+}
+
+int32_t nhwc_to_nchw_f32(const void* in, float* out, TcDType dt, int N, int C, int HW, cudaStream_t s) {
+    if (N == 0) return KXC_B200_OK;
+    if (N > 65535) return fail(KXC_B200_ERR_UNSUPPORTED, "layout transform: batch %d exceeds the grid limit", N);
+    const dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
+    KXC_DISPATCH_ACT(dt, (nhwc_to_nchw_kernel<T><<<grid, block, 0, s>>>(static_cast<const T*>(in), out, C, HW)));
+    return check_launch("nhwc_to_nchw");
+}
+
+int32_t stem_pack(const float* x, void* out, TcDType dt, int N, int C, int H, int W, int Hp, int Wp, int pad_h, int pad_w,
+                  cudaStream_t s) {
+    const int64_t items = (int64_t)N * Hp * Wp;
+    if (items == 0) return KXC_B200_OK;
+    KXC_DISPATCH_ACT(dt, (stem_pack_kernel<T><<<grid_for(items, 16), kThreads, 0, s>>>(x, static_cast<T*>(out), N, C, H, W, Hp, Wp,
+                                                                                     pad_h, pad_w)));
+    return check_launch("stem_pack");
+}
+
+int32_t stem_pack_weights(const float* w, void* out, TcDType dt, int O, int C, int KH, int KW, cudaStream_t s) {
+    KXC_DISPATCH_ACT(dt, (stem_pack_weights_kernel<T><<<grid_for((int64_t)O * KH * 32), kThreads, 0, s>>>(w, static_cast<T*>(out), O,
+                                                                                                          C, KH, KW)));
+    return check_launch("stem_pack_weights");
+}
+
+}  // namespace kxc_b200

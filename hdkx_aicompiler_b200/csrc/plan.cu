@@ -1,0 +1,858 @@
+// Whole-graph executor behind kxc_b200_plan_* (include/kxc_b200_plan.h).
+//
+// The caller describes the graph the way the reference's ExecutionPlan does — one KernelExec node
+// per Relay call, values named by ids (include/base/execution_plan.h:42-50) — and finalize() turns
+// it into a short list of launches:
+//   * conv -> [add residual] -> [relu] chains become ONE tensor-core kernel (fused epilogue);
+//   * activations stay in the plan's arena, channel-innermost (NHWC), in the operand type of the
+//     chosen precision; arena blocks are reused once a value's last consumer has run;
+//   * graph inputs are converted once (a few-channel stride-2 first convolution gets the packed
+//     "stem" layout below), graph outputs are written in the reference's NCHW/row-major fp32 layout
+//     straight from the last kernel's epilogue;
+//   * constants are packed into the tensor-core weight layout on the first run.
+//
+// Stem layout. A 7x7 stride-2 convolution over 3 channels has K = 147, far too ragged for 64-channel
+// K blocks. The input is instead packed as [N][H+2p][Wp][4] with a zero border, and one K block is
+// "8 consecutive pixels x 4 channels" (32 elements) starting at column 2*ow: a TMA tensor map whose
+// column dimension has a stride of 2 pixels makes consecutive output columns overlapping 32-element
+// rows, so the A tile of filter row kh is again a single TMA box. Weights are packed to
+// [O][KH][8][4] with zeros in the unused slots; K = KH*32.
+#include "kxc_b200_plan.h"
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "conv_tc.cuh"
+#include "layout.cuh"
+#include "nhwc_kernels.cuh"
+
+using namespace kxc_b200;
+
+namespace {
+
+enum class VKind { Input, Constant, Intermediate };
+enum class SKind { InputNHWC, InputStem, Conv, Gemm, MaxPool, Gap, Eltwise, ToNCHW };
+
+struct Value {
+    int id = -1;
+    VKind kind = VKind::Intermediate;
+    std::vector<int64_t> shape;  // logical (NCHW / [M,K]) shape, the reference's view
+    int arg_index = -1;          // inputs/constants: position in packed_args
+    int producer = -1;           // node index
+    std::vector<int> consumers;  // node indices
+    int alias_of = -1;           // value id whose storage this one shares (flatten)
+    // storage of the internal (NHWC / row-major, operand dtype) copy
+    size_t offset = 0, bytes = 0;
+    bool has_storage = false;
+    int first_step = -1, last_step = -1;
+};
+
+struct Node {
+    std::string op;
+    std::vector<int> in;
+    int out = -1;
+    kxc_b200_conv2d_attrs conv{};
+    kxc_b200_pool2d_attrs pool{};
+    kxc_b200_gemm_attrs gemm{};
+    bool fused_into_other = false;
+};
+
+struct PackedWeight {
+    int const_id = -1;
+    void* ptr = nullptr;       // plan-owned, tensor-core layout
+    size_t bytes = 0;
+    const void* source = nullptr;  // user pointer it was packed from
+    int mode = 0;              // 0 conv OHWI, 1 stem, 2 dense [N,K], 3 dense from [K,N]
+    int O = 0, C = 0, KH = 0, KW = 0, cpad = 0;
+};
+
+struct Step {
+    SKind kind;
+    // generic references (value ids)
+    int in0 = -1, in1 = -1, out = -1;
+    int weight = -1;      // index into packed weights
+    int bias_const = -1;  // constant value id (fp32 user pointer), -1 = none
+    bool relu = false;
+    bool out_is_graph_output = false;
+    // conv / gemm
+    TcParams params{};
+    TcConfig cfg{};
+    // pooling / misc geometry
+    int N = 0, C = 0, H = 0, W = 0, OH = 0, OW = 0;
+    kxc_b200_pool2d_attrs pool{};
+    int Hp = 0, Wp = 0, pad_h = 0, pad_w = 0, cpad = 0;
+    int64_t numel = 0;
+};
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int64_t numel_of(const std::vector<int64_t>& s) {
+    int64_t n = 1;
+    for (auto d : s) n *= d;
+    return n;
+}
+
+}  // namespace
+
+struct kxc_b200_plan {
+    int precision = KXC_B200_PREC_BF16;
+    TcDType dtype = kTcBF16;
+    std::map<int, Value> values;
+    std::vector<int> inputs, constants;
+    std::vector<Node> nodes;
+    int output_id = -1;
+    bool finalized = false;
+    std::vector<Step> steps;
+    std::vector<PackedWeight> weights;
+    void* arena = nullptr;
+    size_t arena_bytes = 0;
+    void* weight_arena = nullptr;
+    int device = -1;
+
+    ~kxc_b200_plan() {
+        if (arena) cudaFree(arena);
+        if (weight_arena) cudaFree(weight_arena);
+    }
+
+    Value* find(int id) {
+        auto it = values.find(id);
+        return it == values.end() ? nullptr : &it->second;
+    }
+    int root_of(int id) {
+        Value* v = find(id);
+        while (v && v->alias_of >= 0) v = find(v->alias_of);
+        return v ? v->id : -1;
+    }
+    void* storage(int id) {
+        Value* v = find(root_of(id));
+        return static_cast<uint8_t*>(arena) + v->offset;
+    }
+    int eb() const { return tc_elem_bytes(dtype); }
+};
+
+namespace {
+
+int32_t infer_shapes(kxc_b200_plan* pl) {
+    for (size_t ni = 0; ni < pl->nodes.size(); ++ni) {
+        Node& n = pl->nodes[ni];
+        std::vector<Value*> in;
+        for (int id : n.in) {
+            Value* v = pl->find(id);
+            if (!v)
+                return fail(KXC_B200_ERR_INVALID, "plan: node %zu (%s) reads undefined value %d", ni, n.op.c_str(), id);
+            in.push_back(v);
+        }
+        Value* out = pl->find(n.out);
+        if (!out) return fail(KXC_B200_ERR_INVALID, "plan: node %zu has no output value", ni);
+        const std::string& op = n.op;
+        if (op == "nn_conv2d") {
+            // Conv2DInferType, src/relay/type_infer.cc:346-400
+            if (in.size() < 2 || in.size() > 3) return fail(KXC_B200_ERR_INVALID, "nn_conv2d expects 2 or 3 inputs (data, weight[, bias])");
+            if (in[0]->shape.size() != 4 || in[1]->shape.size() != 4)
+                return fail(KXC_B200_ERR_INVALID, "nn_conv2d currently expects NCHW/OIHW rank-4 tensors");
+            if (in.size() == 3 && in[2]->shape.size() != 1) return fail(KXC_B200_ERR_INVALID, "nn_conv2d bias must be rank-1");
+            if (n.conv.groups != 1) return fail(KXC_B200_ERR_UNSUPPORTED, "nn_conv2d: groups=%d", n.conv.groups);
+            if (in[0]->shape[1] != in[1]->shape[1]) return fail(KXC_B200_ERR_INVALID, "nn_conv2d: channel mismatch");
+            const int64_t OH = conv_out_dim(in[0]->shape[2], in[1]->shape[2], n.conv.strides[0], n.conv.padding[0], n.conv.dilation[0]);
+            const int64_t OW = conv_out_dim(in[0]->shape[3], in[1]->shape[3], n.conv.strides[1], n.conv.padding[1], n.conv.dilation[1]);
+            if (OH <= 0 || OW <= 0) return fail(KXC_B200_ERR_INVALID, "nn_conv2d: empty output");
+            out->shape = {in[0]->shape[0], in[1]->shape[0], OH, OW};
+        } else if (op == "nn_relu") {
+            if (in.size() != 1) return fail(KXC_B200_ERR_INVALID, "nn_relu expects exactly 1 input");
+            out->shape = in[0]->shape;
+        } else if (op == "add") {
+            if (in.size() != 2) return fail(KXC_B200_ERR_INVALID, "add expects exactly 2 inputs");
+            if (in[0]->shape != in[1]->shape)
+                return fail(KXC_B200_ERR_UNSUPPORTED, "plan: add with broadcasting is not supported inside a plan (use kxc_b200_add)");
+            out->shape = in[0]->shape;
+        } else if (op == "nn_max_pool2d") {
+            if (in.size() != 1 || in[0]->shape.size() != 4) return fail(KXC_B200_ERR_INVALID, "nn_max_pool2d expects NCHW rank-4 input");
+            const auto& a = n.pool;
+            const int64_t OH = pool_out_dim(in[0]->shape[2], a.pool_size[0], a.strides[0], a.padding[0], a.padding[2], a.ceil_mode != 0);
+            const int64_t OW = pool_out_dim(in[0]->shape[3], a.pool_size[1], a.strides[1], a.padding[1], a.padding[3], a.ceil_mode != 0);
+            if (OH <= 0 || OW <= 0) return fail(KXC_B200_ERR_INVALID, "nn_max_pool2d: empty output");
+            out->shape = {in[0]->shape[0], in[0]->shape[1], OH, OW};
+        } else if (op == "nn_global_avg_pool2d") {
+            if (in.size() != 1 || in[0]->shape.size() != 4) return fail(KXC_B200_ERR_INVALID, "nn_global_avg_pool2d expects NCHW rank-4 input");
+            out->shape = {in[0]->shape[0], in[0]->shape[1], 1, 1};
+        } else if (op == "nn_flatten") {
+            if (in.size() != 1 || in[0]->shape.empty()) return fail(KXC_B200_ERR_INVALID, "nn_flatten expects exactly 1 input");
+            int64_t rest = 1;
+            for (size_t i = 1; i < in[0]->shape.size(); ++i) rest *= in[0]->shape[i];
+            out->shape = {in[0]->shape[0], rest};
+        } else if (op == "nn_dense" || op == "nn_gemm") {
+            const bool gemm = op == "nn_gemm";
+            if ((int)in.size() != (gemm ? 3 : 2)) return fail(KXC_B200_ERR_INVALID, "%s expects exactly %d inputs", op.c_str(), gemm ? 3 : 2);
+            if (in[0]->shape.size() != 2 || in[1]->shape.size() != 2) return fail(KXC_B200_ERR_INVALID, "%s expects rank-2 operands", op.c_str());
+            if (gemm && n.gemm.transA != 0) return fail(KXC_B200_ERR_UNSUPPORTED, "nn_gemm currently does not support transA=1");
+            const bool transB = !gemm || n.gemm.transB == 1;
+            const int64_t K = in[0]->shape[1];
+            const int64_t Nn = transB ? in[1]->shape[0] : in[1]->shape[1];
+            if ((transB ? in[1]->shape[1] : in[1]->shape[0]) != K) return fail(KXC_B200_ERR_INVALID, "%s: inner dimensions differ", op.c_str());
+            out->shape = {in[0]->shape[0], Nn};
+        } else {
+            return fail(KXC_B200_ERR_UNSUPPORTED, "plan: op '%s' is not supported", op.c_str());
+        }
+    }
+    return KXC_B200_OK;
+}
+
+// The single consumer node of value `id`, or -1.
+int sole_consumer(kxc_b200_plan* pl, int id) {
+    Value* v = pl->find(id);
+    if (!v || v->consumers.size() != 1 || id == pl->output_id) return -1;
+    return v->consumers[0];
+}
+
+int32_t setup_stem(kxc_b200_plan* pl, Step& st, int N, int C, int H, int W, int O, int KH, int KW, int pad_h, int pad_w,
+                   const void* packed_in, const void* packed_w, TcOutMode out_mode) {
+    const TcDType dt = pl->dtype;
+    const int eb = tc_elem_bytes(dt);
+    TcParams& p = st.params;
+    const int OH = (int)conv_out_dim(H, KH, 2, pad_h, 1), OW = (int)conv_out_dim(W, KW, 2, pad_w, 1);
+    p.N = N; p.OH = OH; p.OW = OW; p.Cout = O;
+    p.taps_h = KH; p.taps_w = 1; p.stride = 2;
+    p.pad_h = 0; p.pad_w = 0; p.dil_h = 1; p.dil_w = 1;
+    p.cblocks = 1; p.kb_elems = 32;
+    tc_pick_tile(N, OH, OW, &p.BW, &p.BH, &p.BNI);
+    p.tiles_w = (OW + p.BW - 1) / p.BW;
+    p.tiles_h = (OH + p.BH - 1) / p.BH;
+    p.tiles_n = (N + p.BNI - 1) / p.BNI;
+    const int bn = O <= 64 ? 64 : 128;
+    p.tiles_c = (O + bn - 1) / bn;
+    st.cfg = TcConfig{dt, 32 * eb, bn, out_mode};
+    const size_t px = (size_t)4 * eb;  // bytes per packed pixel
+    const uint32_t box[4] = {32u, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BNI};
+    uint8_t* base = const_cast<uint8_t*>(static_cast<const uint8_t*>(packed_in));
+    for (int hp = 0; hp < 2; ++hp) {
+        const uint64_t dims[4] = {32, (uint64_t)OW, (uint64_t)((st.Hp - hp + 1) / 2), (uint64_t)N};
+        const uint64_t strides[3] = {2 * px, (uint64_t)2 * st.Wp * px, (uint64_t)st.Hp * st.Wp * px};
+        CUtensorMap m;
+        KXC_TRY(tc_make_tmap(&m, dt, 4, base + (size_t)hp * st.Wp * px, dims, strides, box, 32 * eb));
+        p.tmA[hp * 2] = m;
+        p.tmA[hp * 2 + 1] = m;
+    }
+    const uint64_t ktot = (uint64_t)KH * 32;
+    const uint64_t bdims[2] = {ktot, (uint64_t)O};
+    const uint64_t bstr[1] = {ktot * eb};
+    const uint32_t bbox[2] = {32u, (uint32_t)bn};
+    KXC_TRY(tc_make_tmap(&p.tmB, dt, 2, const_cast<void*>(packed_w), bdims, bstr, bbox, 32 * eb));
+    KXC_TRY(tc_status_word(&p.status));
+    return KXC_B200_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t kxc_b200_plan_create(int32_t precision, kxc_b200_plan** out) {
+    if (!out) return fail(KXC_B200_ERR_INVALID, "plan_create: null out pointer");
+    if (precision != KXC_B200_PREC_BF16 && precision != KXC_B200_PREC_TF32)
+        return fail(KXC_B200_ERR_UNSUPPORTED, "plan_create: precision must be KXC_B200_PREC_BF16 or KXC_B200_PREC_TF32");
+    auto* pl = new (std::nothrow) kxc_b200_plan();
+    if (!pl) return fail(KXC_B200_ERR_NOMEM, "plan_create: out of host memory");
+    pl->precision = precision;
+    pl->dtype = precision == KXC_B200_PREC_BF16 ? kTcBF16 : kTcTF32;
+    *out = pl;
+    return KXC_B200_OK;
+}
+
+extern "C" int32_t kxc_b200_plan_destroy(kxc_b200_plan* plan) {
+    delete plan;
+    return KXC_B200_OK;
+}
+
+static int32_t add_value(kxc_b200_plan* pl, int32_t id, VKind kind, int32_t rank, const int64_t* shape) {
+    if (!pl || pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan: null or already finalized");
+    if (id < 0 || rank < 0 || rank > 6 || (rank > 0 && !shape)) return fail(KXC_B200_ERR_INVALID, "plan: bad value declaration");
+    if (pl->find(id)) return fail(KXC_B200_ERR_INVALID, "plan: value %d declared twice", id);
+    Value v;
+    v.id = id;
+    v.kind = kind;
+    v.shape.assign(shape, shape + rank);
+    for (auto d : v.shape)
+        if (d < 0) return fail(KXC_B200_ERR_INVALID, "plan: negative extent");
+    v.arg_index = (int)(pl->inputs.size() + pl->constants.size());
+    pl->values[id] = v;
+    (kind == VKind::Input ? pl->inputs : pl->constants).push_back(id);
+    return KXC_B200_OK;
+}
+
+extern "C" int32_t kxc_b200_plan_add_input(kxc_b200_plan* plan, int32_t value_id, int32_t rank, const int64_t* shape) {
+    if (plan && !plan->constants.empty()) return fail(KXC_B200_ERR_INVALID, "plan: inputs must be added before constants");
+    return add_value(plan, value_id, VKind::Input, rank, shape);
+}
+extern "C" int32_t kxc_b200_plan_add_constant(kxc_b200_plan* plan, int32_t value_id, int32_t rank, const int64_t* shape) {
+    return add_value(plan, value_id, VKind::Constant, rank, shape);
+}
+
+extern "C" int32_t kxc_b200_plan_add_kernel(kxc_b200_plan* plan, const char* op_name, const void* attrs, int32_t num_inputs,
+                                            const int32_t* input_ids, int32_t output_id) {
+    if (!plan || plan->finalized || !op_name || num_inputs < 0 || (num_inputs > 0 && !input_ids) || output_id < 0)
+        return fail(KXC_B200_ERR_INVALID, "plan_add_kernel: bad arguments");
+    if (plan->find(output_id)) return fail(KXC_B200_ERR_INVALID, "plan: value %d already defined", output_id);
+    Node n;
+    n.op = op_name;
+    n.in.assign(input_ids, input_ids + num_inputs);
+    n.out = output_id;
+    if (n.op == "nn_conv2d") {
+        if (!attrs) return fail(KXC_B200_ERR_INVALID, "nn_conv2d expects Conv2DAttrs");
+        n.conv = *static_cast<const kxc_b200_conv2d_attrs*>(attrs);
+        if (n.conv.strides[0] <= 0 || n.conv.strides[1] <= 0 || n.conv.dilation[0] <= 0 || n.conv.dilation[1] <= 0 ||
+            n.conv.padding[0] < 0 || n.conv.padding[1] < 0)
+            return fail(KXC_B200_ERR_INVALID, "nn_conv2d: bad strides/padding/dilation");
+    } else if (n.op == "nn_max_pool2d") {
+        if (!attrs) return fail(KXC_B200_ERR_INVALID, "nn_max_pool2d expects MaxPool2DAttrs");
+        n.pool = *static_cast<const kxc_b200_pool2d_attrs*>(attrs);
+        if (n.pool.pool_size[0] <= 0 || n.pool.pool_size[1] <= 0 || n.pool.strides[0] <= 0 || n.pool.strides[1] <= 0)
+            return fail(KXC_B200_ERR_INVALID, "nn_max_pool2d: bad pool_size/strides");
+    } else if (n.op == "nn_gemm") {
+        if (!attrs) return fail(KXC_B200_ERR_INVALID, "nn_gemm expects GemmAttrs");
+        n.gemm = *static_cast<const kxc_b200_gemm_attrs*>(attrs);
+    }
+    for (int id : n.in)
+        if (!plan->find(id)) return fail(KXC_B200_ERR_INVALID, "plan: node '%s' reads undefined value %d", op_name, id);
+    Value v;
+    v.id = output_id;
+    v.kind = VKind::Intermediate;
+    v.producer = (int)plan->nodes.size();
+    plan->values[output_id] = v;
+    for (int id : n.in) plan->find(id)->consumers.push_back((int)plan->nodes.size());
+    plan->nodes.push_back(n);
+    return KXC_B200_OK;
+}
+
+extern "C" int32_t kxc_b200_plan_set_output(kxc_b200_plan* plan, int32_t value_id) {
+    if (!plan || plan->finalized) return fail(KXC_B200_ERR_INVALID, "plan_set_output: bad plan");
+    Value* v = plan->find(value_id);
+    if (!v || v->kind != VKind::Intermediate) return fail(KXC_B200_ERR_INVALID, "plan_set_output: value %d is not produced by a kernel", value_id);
+    plan->output_id = value_id;
+    return KXC_B200_OK;
+}
+
+extern "C" int32_t kxc_b200_plan_value_shape(kxc_b200_plan* plan, int32_t value_id, int64_t* shape_out) {
+    if (!plan || !plan->finalized) return -KXC_B200_ERR_INVALID;
+    Value* v = plan->find(value_id);
+    if (!v) return -KXC_B200_ERR_INVALID;
+    for (size_t i = 0; i < v->shape.size(); ++i) shape_out[i] = v->shape[i];
+    return (int32_t)v->shape.size();
+}
+
+extern "C" int32_t kxc_b200_plan_num_launches(kxc_b200_plan* plan) {
+    if (!plan || !plan->finalized) return -KXC_B200_ERR_INVALID;
+    return (int32_t)plan->steps.size();
+}
+
+extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
+    if (!pl || pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_finalize: null or already finalized");
+    KXC_TRY(require_device());
+    if (pl->output_id < 0) return fail(KXC_B200_ERR_INVALID, "plan_finalize: no output set");
+    if (pl->inputs.size() != 1) return fail(KXC_B200_ERR_UNSUPPORTED, "plan_finalize: exactly one graph input is supported");
+    KXC_TRY(infer_shapes(pl));
+    if (!pl->find(pl->output_id)->consumers.empty())
+        return fail(KXC_B200_ERR_UNSUPPORTED, "plan_finalize: the output value must not feed other kernels");
+    KXC_CUDA_TRY(cudaGetDevice(&pl->device));
+    const TcDType dt = pl->dtype;
+    const int eb = pl->eb();
+    const int lanes = 16 / eb;
+
+    auto is_const = [&](int id) { return pl->find(id)->kind == VKind::Constant; };
+    auto is_input = [&](int id) { return pl->find(id)->kind == VKind::Input; };
+
+    // ---- build steps (fusing conv -> [add] -> [relu] and add -> relu) ----
+    std::map<int, int> input_copy;  // (input value id * 2 + stem) -> step index producing the internal copy
+    std::vector<std::pair<int, Step>> pending;  // (emit position = node index, step)
+    for (size_t ni = 0; ni < pl->nodes.size(); ++ni) {
+        Node& n = pl->nodes[ni];
+        if (n.fused_into_other) continue;
+        Step st{};
+        int emit_at = (int)ni;
+        if (n.op == "nn_conv2d") {
+            Value* data = pl->find(n.in[0]);
+            Value* w = pl->find(n.in[1]);
+            if (!is_const(n.in[1]) || (n.in.size() == 3 && !is_const(n.in[2])))
+                return fail(KXC_B200_ERR_UNSUPPORTED, "plan: nn_conv2d weight and bias must be constants");
+            if (is_const(n.in[0])) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: nn_conv2d over a constant input");
+            st.kind = SKind::Conv;
+            st.in0 = n.in[0];
+            st.bias_const = n.in.size() == 3 ? n.in[2] : -1;
+            int cur = n.out;
+            int c = sole_consumer(pl, cur);
+            if (c >= 0 && pl->nodes[c].op == "add") {
+                Node& a = pl->nodes[c];
+                const int other = a.in[0] == cur ? a.in[1] : a.in[0];
+                Value* ov = pl->find(other);
+                if (other != cur && ov->kind == VKind::Intermediate && ov->producer < c && ov->shape == pl->find(cur)->shape) {
+                    st.in1 = other;
+                    a.fused_into_other = true;
+                    cur = a.out;
+                    emit_at = c;
+                    c = sole_consumer(pl, cur);
+                }
+            }
+            if (c >= 0 && pl->nodes[c].op == "nn_relu") {
+                st.relu = true;
+                pl->nodes[c].fused_into_other = true;
+                cur = pl->nodes[c].out;
+                emit_at = c;
+            }
+            st.out = cur;
+            st.N = (int)data->shape[0]; st.C = (int)data->shape[1]; st.H = (int)data->shape[2]; st.W = (int)data->shape[3];
+            st.pool = {};  // unused
+            // weight record
+            PackedWeight pw;
+            pw.const_id = n.in[1];
+            pw.O = (int)w->shape[0]; pw.C = (int)w->shape[1]; pw.KH = (int)w->shape[2]; pw.KW = (int)w->shape[3];
+            const bool stem = is_input(n.in[0]) && st.C <= 4 && n.conv.strides[0] == 2 && n.conv.strides[1] == 2 &&
+                              n.conv.dilation[0] == 1 && n.conv.dilation[1] == 1 && pw.KW <= 8 && st.W >= 8;
+            if (stem) {
+                pw.mode = 1;
+                pw.cpad = 4;
+                pw.bytes = (size_t)pw.O * pw.KH * 32 * eb;
+            } else {
+                pw.mode = 0;
+                pw.cpad = tc_channel_pad(dt, st.C);
+                if (!is_input(n.in[0]) && pw.cpad != st.C)
+                    return fail(KXC_B200_ERR_UNSUPPORTED, "plan: nn_conv2d over %d channels: intermediate channel counts must be 16/32/64k for bf16 (8/16/32k for tf32)", st.C);
+                pw.bytes = (size_t)pw.O * pw.KH * pw.KW * pw.cpad * eb;
+            }
+            st.cpad = pw.cpad;
+            st.weight = (int)pl->weights.size();
+            pl->weights.push_back(pw);
+            // stash conv attrs in the pool struct slots we do not otherwise use
+            st.pad_h = n.conv.padding[0]; st.pad_w = n.conv.padding[1];
+            st.pool.strides[0] = n.conv.strides[0]; st.pool.strides[1] = n.conv.strides[1];
+            st.pool.pool_size[0] = n.conv.dilation[0]; st.pool.pool_size[1] = n.conv.dilation[1];
+            st.Hp = stem ? 1 : 0;  // marks stem until geometry is filled below
+        } else if (n.op == "add" || n.op == "nn_relu") {
+            st.kind = SKind::Eltwise;
+            st.in0 = n.in[0];
+            st.in1 = n.op == "add" ? n.in[1] : -1;
+            st.relu = n.op == "nn_relu";
+            int cur = n.out;
+            if (n.op == "add") {
+                const int c = sole_consumer(pl, cur);
+                if (c >= 0 && pl->nodes[c].op == "nn_relu") {
+                    st.relu = true;
+                    pl->nodes[c].fused_into_other = true;
+                    cur = pl->nodes[c].out;
+                    emit_at = c;
+                }
+            }
+            st.out = cur;
+            st.numel = numel_of(pl->find(cur)->shape);
+            if (is_const(st.in0) || is_input(st.in0) || (st.in1 >= 0 && (is_const(st.in1) || is_input(st.in1))))
+                return fail(KXC_B200_ERR_UNSUPPORTED, "plan: elementwise ops over graph inputs/constants are not supported");
+        } else if (n.op == "nn_max_pool2d") {
+            Value* x = pl->find(n.in[0]);
+            if (x->kind != VKind::Intermediate) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: pooling over a graph input/constant");
+            st.kind = SKind::MaxPool;
+            st.in0 = n.in[0]; st.out = n.out; st.pool = n.pool;
+            st.N = (int)x->shape[0]; st.C = (int)x->shape[1]; st.H = (int)x->shape[2]; st.W = (int)x->shape[3];
+            st.OH = (int)pl->find(n.out)->shape[2]; st.OW = (int)pl->find(n.out)->shape[3];
+            if (st.C % lanes) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: pooling needs a channel count that is a multiple of %d", lanes);
+        } else if (n.op == "nn_global_avg_pool2d") {
+            Value* x = pl->find(n.in[0]);
+            if (x->kind != VKind::Intermediate) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: pooling over a graph input/constant");
+            st.kind = SKind::Gap;
+            st.in0 = n.in[0]; st.out = n.out;
+            st.N = (int)x->shape[0]; st.C = (int)x->shape[1]; st.H = (int)x->shape[2]; st.W = (int)x->shape[3];
+            if (st.C % lanes) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: pooling needs a channel count that is a multiple of %d", lanes);
+        } else if (n.op == "nn_flatten") {
+            Value* x = pl->find(n.in[0]);
+            bool trailing_ones = true;
+            for (size_t i = 2; i < x->shape.size(); ++i) trailing_ones = trailing_ones && x->shape[i] == 1;
+            if (x->kind != VKind::Intermediate || !trailing_ones)
+                return fail(KXC_B200_ERR_UNSUPPORTED, "plan: nn_flatten is supported on [N,C,1,1] / [N,C] intermediates only");
+            pl->find(n.out)->alias_of = n.in[0];
+            continue;
+        } else if (n.op == "nn_dense" || n.op == "nn_gemm") {
+            const bool gemm = n.op == "nn_gemm";
+            if (gemm && ((double)n.gemm.alpha != 1.0 || (double)n.gemm.beta != 1.0))
+                return fail(KXC_B200_ERR_UNSUPPORTED, "plan: nn_gemm with alpha/beta != 1 (use kxc_b200_nn_gemm)");
+            if (!is_const(n.in[1]) || (gemm && !is_const(n.in[2])) || pl->find(n.in[0])->kind != VKind::Intermediate)
+                return fail(KXC_B200_ERR_UNSUPPORTED, "plan: dense needs an intermediate lhs and constant weight/bias");
+            st.kind = SKind::Gemm;
+            st.in0 = n.in[0]; st.out = n.out;
+            st.bias_const = gemm ? n.in[2] : -1;
+            Value* a = pl->find(n.in[0]);
+            Value* b = pl->find(n.in[1]);
+            const bool transB = !gemm || n.gemm.transB == 1;
+            PackedWeight pw;
+            pw.const_id = n.in[1];
+            pw.mode = transB ? 2 : 3;
+            pw.O = (int)pl->find(n.out)->shape[1];
+            pw.C = (int)a->shape[1];
+            pw.cpad = tc_channel_pad(dt, pw.C);
+            if (pw.cpad != pw.C) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: dense reduction length %d must be 16/32/64k (bf16) or 8/16/32k (tf32)", pw.C);
+            pw.bytes = (size_t)pw.O * pw.cpad * eb;
+            (void)b;
+            st.N = (int)a->shape[0]; st.C = pw.C;
+            st.weight = (int)pl->weights.size();
+            pl->weights.push_back(pw);
+        } else {
+            return fail(KXC_B200_ERR_UNSUPPORTED, "plan: op '%s' is not supported", n.op.c_str());
+        }
+        pending.push_back({emit_at, st});
+    }
+    std::stable_sort(pending.begin(), pending.end(), [](const auto& a, const auto& b) { return a.first < b.first; });
+
+    // input conversion steps go first
+    for (auto& pr : pending) {
+        Step& st = pr.second;
+        if (st.kind != SKind::Conv || !is_input(st.in0)) continue;
+        const bool stem = st.Hp == 1;
+        const int key = st.in0 * 2 + (stem ? 1 : 0);
+        if (input_copy.count(key)) continue;
+        Step cv{};
+        cv.kind = stem ? SKind::InputStem : SKind::InputNHWC;
+        cv.in0 = st.in0;
+        cv.N = st.N; cv.C = st.C; cv.H = st.H; cv.W = st.W;
+        cv.cpad = st.cpad;
+        if (stem) {
+            const PackedWeight& pw = pl->weights[st.weight];
+            const int OW = (int)conv_out_dim(st.W, pw.KW, 2, st.pad_w, 1);
+            cv.pad_h = st.pad_h; cv.pad_w = st.pad_w;
+            cv.Hp = st.H + 2 * st.pad_h;
+            cv.Hp += cv.Hp & 1;
+            cv.Wp = std::max(st.W + 2 * st.pad_w, 2 * (OW - 1) + 8);
+            cv.Wp += cv.Wp & 1;
+        }
+        // the internal copy is a synthetic value with a negative id
+        const int copy_id = -(int)(input_copy.size() + 1);
+        Value v;
+        v.id = copy_id;
+        v.kind = VKind::Intermediate;
+        v.bytes = stem ? (size_t)cv.N * cv.Hp * cv.Wp * 4 * eb : (size_t)cv.N * cv.H * cv.W * cv.cpad * eb;
+        pl->values[copy_id] = v;
+        cv.out = copy_id;
+        input_copy[key] = copy_id;
+        pl->steps.push_back(cv);
+    }
+    for (auto& pr : pending) {
+        Step st = pr.second;
+        if (st.kind == SKind::Conv && is_input(st.in0)) {
+            const bool stem = st.Hp == 1;
+            const int copy_id = input_copy[st.in0 * 2 + (stem ? 1 : 0)];
+            st.in0 = copy_id;
+            if (stem) {
+                for (auto& s2 : pl->steps)
+                    if (s2.out == copy_id) { st.Hp = s2.Hp; st.Wp = s2.Wp; }
+            }
+        } else if (st.kind == SKind::Conv) {
+            st.Hp = 0;
+        }
+        pl->steps.push_back(st);
+    }
+    // graph output: written directly by a conv/gemm epilogue, else converted by one extra step
+    {
+        Step& last = pl->steps.back();
+        bool direct = false;
+        for (auto& st : pl->steps) {
+            if (st.out >= 0 && pl->root_of(st.out) == pl->root_of(pl->output_id) && pl->root_of(st.out) == st.out &&
+                (st.kind == SKind::Conv || st.kind == SKind::Gemm) && pl->find(pl->output_id)->alias_of < 0) {
+                st.out_is_graph_output = true;
+                direct = true;
+            }
+        }
+        (void)last;
+        if (!direct) {
+            Value* ov = pl->find(pl->output_id);
+            Step cv{};
+            cv.kind = SKind::ToNCHW;
+            cv.in0 = pl->output_id;
+            cv.out_is_graph_output = true;
+            if (ov->shape.size() == 4) {
+                cv.N = (int)ov->shape[0]; cv.C = (int)ov->shape[1]; cv.H = (int)ov->shape[2]; cv.W = (int)ov->shape[3];
+            } else if (ov->shape.size() == 2) {
+                cv.N = (int)ov->shape[0]; cv.C = (int)ov->shape[1]; cv.H = 1; cv.W = 1;
+            } else {
+                return fail(KXC_B200_ERR_UNSUPPORTED, "plan: output rank %zu", ov->shape.size());
+            }
+            pl->steps.push_back(cv);
+        }
+    }
+
+    // ---- storage sizes and liveness ----
+    for (size_t si = 0; si < pl->steps.size(); ++si) {
+        Step& st = pl->steps[si];
+        auto touch = [&](int id) {
+            if (id == -1) return;
+            Value* v = pl->find(pl->root_of(id));
+            if (!v || v->kind != VKind::Intermediate) return;
+            if (v->first_step < 0) v->first_step = (int)si;
+            v->last_step = (int)si;
+        };
+        touch(st.in0);
+        touch(st.in1);
+        if (st.out != -1 && !st.out_is_graph_output) {
+            Value* v = pl->find(st.out);
+            if (v->id >= 0) v->bytes = (size_t)numel_of(v->shape) * eb;
+            touch(st.out);
+        }
+    }
+    // greedy arena assignment with reuse of dead blocks
+    struct Block { size_t off, size; };
+    std::vector<Block> free_blocks;
+    size_t top = 0;
+    for (size_t si = 0; si < pl->steps.size(); ++si) {
+        Step& st = pl->steps[si];
+        if (st.out != -1 && !st.out_is_graph_output) {
+            Value* v = pl->find(st.out);
+            if (v->alias_of < 0 && !v->has_storage) {
+                const size_t need = align_up(std::max<size_t>(v->bytes, 16), 1024);
+                int best = -1;
+                for (size_t b = 0; b < free_blocks.size(); ++b)
+                    if (free_blocks[b].size >= need && (best < 0 || free_blocks[b].size < free_blocks[best].size)) best = (int)b;
+                if (best >= 0) {
+                    v->offset = free_blocks[best].off;
+                    if (free_blocks[best].size > need) {
+                        free_blocks[best].off += need;
+                        free_blocks[best].size -= need;
+                    } else {
+                        free_blocks.erase(free_blocks.begin() + best);
+                    }
+                } else {
+                    v->offset = top;
+                    top += need;
+                }
+                v->has_storage = true;
+                v->bytes = need;
+            }
+        }
+        for (auto& kv : pl->values) {
+            Value& v = kv.second;
+            if (v.kind == VKind::Intermediate && v.has_storage && v.alias_of < 0 && v.last_step == (int)si) {
+                free_blocks.push_back({v.offset, v.bytes});
+                // merge adjacent free blocks
+                std::sort(free_blocks.begin(), free_blocks.end(), [](const Block& a, const Block& b) { return a.off < b.off; });
+                for (size_t b = 0; b + 1 < free_blocks.size();) {
+                    if (free_blocks[b].off + free_blocks[b].size == free_blocks[b + 1].off) {
+                        free_blocks[b].size += free_blocks[b + 1].size;
+                        free_blocks.erase(free_blocks.begin() + b + 1);
+                    } else {
+                        ++b;
+                    }
+                }
+            }
+        }
+    }
+    pl->arena_bytes = std::max<size_t>(top, 1024);
+    KXC_CUDA_TRY(cudaMalloc(&pl->arena, pl->arena_bytes));
+    size_t wtop = 0;
+    for (auto& w : pl->weights) wtop += align_up(w.bytes, 1024);
+    KXC_CUDA_TRY(cudaMalloc(&pl->weight_arena, std::max<size_t>(wtop, 1024)));
+    wtop = 0;
+    for (auto& w : pl->weights) {
+        w.ptr = static_cast<uint8_t*>(pl->weight_arena) + wtop;
+        wtop += align_up(w.bytes, 1024);
+    }
+
+    // ---- tensor maps and launch parameters ----
+    for (auto& st : pl->steps) {
+        if (st.kind == SKind::Conv) {
+            const PackedWeight& pw = pl->weights[st.weight];
+            Value* ov = pl->find(st.out);
+            TcOutMode om = st.out_is_graph_output ? kOutNCHW_F32 : (dt == kTcBF16 ? kOutNHWC_BF16 : kOutNHWC_F32);
+            if (st.in1 >= 0 && st.out_is_graph_output)
+                return fail(KXC_B200_ERR_UNSUPPORTED, "plan: a residual convolution cannot be the graph output");
+            if (!st.out_is_graph_output && (pw.O % lanes))
+                return fail(KXC_B200_ERR_UNSUPPORTED, "plan: %d output channels must be a multiple of %d", pw.O, lanes);
+            if (pw.mode == 1) {
+                KXC_TRY(setup_stem(pl, st, st.N, st.C, st.H, st.W, pw.O, pw.KH, pw.KW, st.pad_h, st.pad_w, pl->storage(st.in0), pw.ptr, om));
+            } else {
+                if (st.pool.strides[0] != st.pool.strides[1])
+                    return fail(KXC_B200_ERR_UNSUPPORTED, "plan: nn_conv2d with different strides in h and w");
+                KXC_TRY(tc_setup_conv(&st.params, &st.cfg, dt, om, pl->storage(st.in0), pw.ptr, st.N, st.H, st.W, st.cpad, pw.O,
+                                      pw.KH, pw.KW, st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0], st.pool.pool_size[1]));
+            }
+            st.params.relu = st.relu ? 1 : 0;
+            st.params.residual = st.in1 >= 0 ? pl->storage(st.in1) : nullptr;
+            st.params.out = st.out_is_graph_output ? nullptr : pl->storage(st.out);
+            (void)ov;
+        } else if (st.kind == SKind::Gemm) {
+            const PackedWeight& pw = pl->weights[st.weight];
+            TcOutMode om = st.out_is_graph_output ? kOutNHWC_F32 : (dt == kTcBF16 ? kOutNHWC_BF16 : kOutNHWC_F32);
+            if (!st.out_is_graph_output && (pw.O % lanes))
+                return fail(KXC_B200_ERR_UNSUPPORTED, "plan: %d dense outputs must be a multiple of %d", pw.O, lanes);
+            KXC_TRY(tc_setup_conv(&st.params, &st.cfg, dt, om, pl->storage(st.in0), pw.ptr, st.N, 1, 1, pw.cpad, pw.O, 1, 1, 1, 0, 0, 1, 1));
+            st.params.relu = 0;
+            st.params.residual = nullptr;
+            st.params.out = st.out_is_graph_output ? nullptr : pl->storage(st.out);
+        }
+    }
+    pl->finalized = true;
+    return KXC_B200_OK;
+}
+
+static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream, cudaEvent_t* events) {
+    if (!pl || !pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_run: plan is not finalized");
+    if (!packed_args) return fail(KXC_B200_ERR_INVALID, "plan_run: null packed_args");
+    KXC_TRY(require_device());
+    int dev = -1;
+    KXC_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != pl->device) return fail(KXC_B200_ERR_INVALID, "plan_run: plan was finalized on device %d, current device is %d", pl->device, dev);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const TcDType dt = pl->dtype;
+    const size_t nargs = pl->inputs.size() + pl->constants.size();
+    for (size_t i = 0; i <= nargs; ++i)
+        if (!packed_args[i]) return fail(KXC_B200_ERR_INVALID, "plan_run: packed_args[%zu] is null", i);
+    void* out_ptr = packed_args[nargs];
+    auto arg_of = [&](int id) -> void* { return packed_args[pl->find(id)->arg_index]; };
+
+    // (re)pack constants whose source pointer changed
+    for (auto& w : pl->weights) {
+        const void* src = arg_of(w.const_id);
+        if (src == w.source) continue;
+        switch (w.mode) {
+            case 0: KXC_TRY(pack_weights_ohwi(src, w.ptr, dt, w.O, w.C, w.KH, w.KW, w.cpad, s)); break;
+            case 1: KXC_TRY(stem_pack_weights(static_cast<const float*>(src), w.ptr, dt, w.O, w.C, w.KH, w.KW, s)); break;
+            case 2: KXC_TRY(convert_rows(static_cast<const float*>(src), w.ptr, dt, w.O, w.C, w.cpad, s)); break;
+            case 3: KXC_TRY(nchw_to_nhwc(src, w.ptr, dt, 1, w.C, w.O, w.cpad, s)); break;
+        }
+        w.source = src;
+    }
+
+    size_t step_index = 0;
+    if (events) KXC_CUDA_TRY(cudaEventRecord(events[0], s));
+    for (auto& st : pl->steps) {
+        if (step_index > 0 && events) KXC_CUDA_TRY(cudaEventRecord(events[step_index], s));
+        ++step_index;
+        switch (st.kind) {
+            case SKind::InputNHWC:
+                KXC_TRY(nchw_to_nhwc(arg_of(st.in0), pl->storage(st.out), dt, st.N, st.C, st.H * st.W, st.cpad, s));
+                break;
+            case SKind::InputStem:
+                KXC_TRY(stem_pack(static_cast<const float*>(arg_of(st.in0)), pl->storage(st.out), dt, st.N, st.C, st.H, st.W, st.Hp,
+                                  st.Wp, st.pad_h, st.pad_w, s));
+                break;
+            case SKind::Conv:
+            case SKind::Gemm: {
+                TcParams p = st.params;
+                p.bias = st.bias_const >= 0 ? static_cast<const float*>(arg_of(st.bias_const)) : nullptr;
+                if (st.out_is_graph_output) p.out = out_ptr;
+                tc_finish_params(&p);
+                KXC_TRY(tc_launch(st.cfg, p, s));
+                break;
+            }
+            case SKind::MaxPool:
+                KXC_TRY(maxpool_nhwc(pl->storage(st.in0), pl->storage(st.out), dt, st.N, st.H, st.W, st.C, st.OH, st.OW,
+                                     st.pool.pool_size[0], st.pool.pool_size[1], st.pool.strides[0], st.pool.strides[1],
+                                     st.pool.padding[0], st.pool.padding[1], s));
+                break;
+            case SKind::Gap:
+                KXC_TRY(gap_nhwc(pl->storage(st.in0), pl->storage(st.out), dt, st.N, st.H * st.W, st.C, s));
+                break;
+            case SKind::Eltwise:
+                KXC_TRY(eltwise_nhwc(pl->storage(st.in0), st.in1 >= 0 ? pl->storage(st.in1) : nullptr, pl->storage(st.out), dt,
+                                     st.numel, st.relu ? 1 : 0, s));
+                break;
+            case SKind::ToNCHW:
+                KXC_TRY(nhwc_to_nchw_f32(pl->storage(st.in0), static_cast<float*>(out_ptr), dt, st.N, st.C, st.H * st.W, s));
+                break;
+        }
+    }
+    if (events) KXC_CUDA_TRY(cudaEventRecord(events[step_index], s));
+    return KXC_B200_OK;
+}
+
+extern "C" int32_t kxc_b200_plan_run(kxc_b200_plan* pl, void** packed_args, void* stream) {
+    return plan_run_impl(pl, packed_args, stream, nullptr);
+}
+
+extern "C" int32_t kxc_b200_plan_run_timed(kxc_b200_plan* pl, void** packed_args, void* stream, float* launch_ms,
+                                           int32_t capacity) {
+    if (!pl || !pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_run_timed: plan is not finalized");
+    const int n = (int)pl->steps.size();
+    if (!launch_ms || capacity < n) return fail(KXC_B200_ERR_INVALID, "plan_run_timed: need room for %d durations", n);
+    std::vector<cudaEvent_t> ev(n + 1);
+    for (auto& e : ev) KXC_CUDA_TRY(cudaEventCreate(&e));
+    int32_t rc = plan_run_impl(pl, packed_args, stream, ev.data());
+    if (rc == KXC_B200_OK) {
+        cudaError_t e = cudaEventSynchronize(ev[n]);
+        if (e != cudaSuccess) rc = fail(KXC_B200_ERR_CUDA, "plan_run_timed: %s", cudaGetErrorString(e));
+        for (int i = 0; i < n && rc == KXC_B200_OK; ++i)
+            if (cudaEventElapsedTime(&launch_ms[i], ev[i], ev[i + 1]) != cudaSuccess) rc = fail(KXC_B200_ERR_CUDA, "plan_run_timed: elapsed time");
+    }
+    for (auto& e : ev) cudaEventDestroy(e);
+    return rc;
+}
+
+// ---- measurement support ------------------------------------------------------------------------
+namespace {
+const char* step_kind_name(SKind k) {
+    switch (k) {
+        case SKind::InputNHWC: return "input_nhwc";
+        case SKind::InputStem: return "stem_pack";
+        case SKind::Conv: return "conv_igemm";
+        case SKind::Gemm: return "dense_igemm";
+        case SKind::MaxPool: return "maxpool_nhwc";
+        case SKind::Gap: return "gap_nhwc";
+        case SKind::Eltwise: return "eltwise_nhwc";
+        case SKind::ToNCHW: return "nhwc_to_nchw";
+    }
+    return "?";
+}
+}  // namespace
+
+extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, char* name, int32_t name_size,
+                                             double* flops, double* bytes) {
+    if (!pl || !pl->finalized || index < 0 || index >= (int)pl->steps.size())
+        return fail(KXC_B200_ERR_INVALID, "plan_launch_info: bad plan or index");
+    const Step& st = pl->steps[index];
+    const double eb = pl->eb();
+    double fl = 0.0, by = 0.0;
+    char buf[160];
+    switch (st.kind) {
+        case SKind::Conv: {
+            const PackedWeight& w = pl->weights[st.weight];
+            const TcParams& p = st.params;
+            const double out_elems = (double)p.N * p.OH * p.OW * w.O;
+            fl = 2.0 * out_elems * w.C * w.KH * w.KW;  // padded taps counted, as the reference executes them
+            const double in_bytes = w.mode == 1 ? (double)st.N * st.Hp * st.Wp * 4 * eb : (double)st.N * st.H * st.W * st.cpad * eb;
+            by = in_bytes + (double)w.bytes + out_elems * (st.out_is_graph_output ? 4.0 : eb) + (st.in1 >= 0 ? out_elems * eb : 0.0) + 4.0 * w.O;
+            snprintf(buf, sizeof(buf), "conv_igemm c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d", w.C, st.H, st.W, w.O, w.KH, w.KW,
+                     p.stride, st.in1 >= 0 ? " +res" : "", st.relu ? " +relu" : "", p.BNI, p.BH, p.BW, st.cfg.bn);
+            break;
+        }
+        case SKind::Gemm: {
+            const PackedWeight& w = pl->weights[st.weight];
+            fl = 2.0 * st.N * (double)w.O * w.C;
+            by = (double)st.N * w.C * eb + (double)w.bytes + (double)st.N * w.O * (st.out_is_graph_output ? 4.0 : eb) + 4.0 * w.O;
+            snprintf(buf, sizeof(buf), "dense_igemm m%d k%d -> n%d bn%d", st.N, w.C, w.O, st.cfg.bn);
+            break;
+        }
+        case SKind::MaxPool:
+            by = ((double)st.N * st.H * st.W * st.C + (double)st.N * st.OH * st.OW * st.C) * eb;
+            snprintf(buf, sizeof(buf), "maxpool_nhwc c%d h%d w%d k%dx%d s%d", st.C, st.H, st.W, st.pool.pool_size[0], st.pool.pool_size[1], st.pool.strides[0]);
+            break;
+        case SKind::Gap:
+            by = ((double)st.N * st.H * st.W * st.C + (double)st.N * st.C) * eb;
+            snprintf(buf, sizeof(buf), "gap_nhwc c%d h%d w%d", st.C, st.H, st.W);
+            break;
+        case SKind::Eltwise:
+            by = (double)st.numel * eb * (st.in1 >= 0 ? 3.0 : 2.0);
+            snprintf(buf, sizeof(buf), "eltwise_nhwc n%lld", (long long)st.numel);
+            break;
+        case SKind::InputStem:
+            by = (double)st.N * st.C * st.H * st.W * 4.0 + (double)st.N * st.Hp * st.Wp * 4 * eb;
+            snprintf(buf, sizeof(buf), "stem_pack c%d h%d w%d -> %dx%dx4", st.C, st.H, st.W, st.Hp, st.Wp);
+            break;
+        case SKind::InputNHWC:
+            by = (double)st.N * st.C * st.H * st.W * 4.0 + (double)st.N * st.H * st.W * st.cpad * eb;
+            snprintf(buf, sizeof(buf), "input_nhwc c%d h%d w%d", st.C, st.H, st.W);
+            break;
+        case SKind::ToNCHW:
+            by = (double)st.N * st.C * st.H * st.W * (4.0 + eb);
+            snprintf(buf, sizeof(buf), "nhwc_to_nchw c%d h%d w%d", st.C, st.H, st.W);
+            break;
+    }
+    (void)step_kind_name;
+    if (name && name_size > 0) snprintf(name, (size_t)name_size, "%s", buf);
+    if (flops) *flops = fl;
+    if (bytes) *bytes = by;
+    return KXC_B200_OK;
+}

@@ -209,6 +209,7 @@ extern "C" int32_t kxc_b200_nn_max_pool2d(void** packed_args, const kxc_b200_poo
     KXC_TRY(require_device());
     PoolDims pd;
     KXC_TRY(validate_pool(desc, "nn_max_pool2d", &pd));
+    if (pd.planes == 0) return KXC_B200_OK;
     if (!packed_args || !packed_args[0] || !packed_args[1]) return fail(KXC_B200_ERR_INVALID, "nn_max_pool2d: null tensor pointer");
     return launch_max_pool<false>(static_cast<const float*>(packed_args[0]), nullptr, static_cast<float*>(packed_args[1]),
                                   desc, pd, static_cast<cudaStream_t>(stream), "nn_max_pool2d");
@@ -218,6 +219,7 @@ extern "C" int32_t kxc_b200_max_pool2d_add_relu(void** packed_args, const kxc_b2
     KXC_TRY(require_device());
     PoolDims pd;
     KXC_TRY(validate_pool(desc, "max_pool2d_add_relu", &pd));
+    if (pd.planes == 0) return KXC_B200_OK;
     if (!packed_args || !packed_args[0] || !packed_args[1] || !packed_args[2])
         return fail(KXC_B200_ERR_INVALID, "max_pool2d_add_relu: null tensor pointer");
     return launch_max_pool<true>(static_cast<const float*>(packed_args[0]), static_cast<const float*>(packed_args[1]),
@@ -229,6 +231,7 @@ extern "C" int32_t kxc_b200_nn_avg_pool2d(void** packed_args, const kxc_b200_poo
     KXC_TRY(require_device());
     PoolDims pd;
     KXC_TRY(validate_pool(desc, "nn_avg_pool2d", &pd));
+    if (pd.planes == 0) return KXC_B200_OK;
     if (!packed_args || !packed_args[0] || !packed_args[1]) return fail(KXC_B200_ERR_INVALID, "nn_avg_pool2d: null tensor pointer");
     if (pd.planes == 0) return KXC_B200_OK;
     const int64_t items = pd.planes * pd.OH * pd.OW;
@@ -241,10 +244,10 @@ extern "C" int32_t kxc_b200_nn_global_avg_pool2d(void** packed_args, int32_t n, 
                                                  void* stream) {
     KXC_TRY(require_device());
     if (n < 0 || c < 0 || h <= 0 || w <= 0) return fail(KXC_B200_ERR_INVALID, "nn_global_avg_pool2d: bad shape");
-    if (!packed_args || !packed_args[0] || !packed_args[1])
-        return fail(KXC_B200_ERR_INVALID, "nn_global_avg_pool2d: null tensor pointer");
     const int64_t planes = (int64_t)n * c;
     if (planes == 0) return KXC_B200_OK;
+    if (!packed_args || !packed_args[0] || !packed_args[1])
+        return fail(KXC_B200_ERR_INVALID, "nn_global_avg_pool2d: null tensor pointer");
     const int64_t HW = (int64_t)h * w;
     const float* x = static_cast<const float*>(packed_args[0]);
     float* out = static_cast<float*>(packed_args[1]);

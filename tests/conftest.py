@@ -24,8 +24,18 @@ def bits(a):
     return a.view({4: np.uint32, 1: np.uint8, 2: np.uint16, 8: np.uint64}[a.dtype.itemsize])
 
 
+def _canonical_nan(a):
+    """NaN payloads are the one thing that legitimately differs between processors: x86 SSE returns the
+    first NaN operand quieted, the GPU returns the canonical NaN 0x7fffffff. Both are "NaN"; every
+    other bit pattern (including the sign of zero and infinities) must match exactly."""
+    a = np.array(a, copy=True)
+    if a.dtype.kind == "f":
+        a[np.isnan(a)] = np.nan
+    return a
+
+
 def assert_bit_exact(actual, expected, what=""):
-    actual, expected = np.asarray(actual), np.asarray(expected)
+    actual, expected = _canonical_nan(actual), _canonical_nan(expected)
     assert actual.shape == expected.shape, f"{what}: shape {actual.shape} vs {expected.shape}"
     ba, be = bits(actual), bits(expected)
     if not np.array_equal(ba, be):

@@ -1,0 +1,138 @@
+"""GPU parity tests of the whole-graph entry point (kxc_b200_plan_*) against the CPU oracle walking the
+same Relay-style graph call by call."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, ref_metric
+from oracle import graph as ograph
+from oracle import port
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+
+
+@pytest.fixture(scope="module")
+def kxc():
+    import hdkx_aicompiler_b200 as k
+    from hdkx_aicompiler_b200 import ops, plan, relay, resnet18  # noqa: F401
+    assert torch.cuda.is_available()
+    return k
+
+
+def cuda_const(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+ROUND = {"bf16": port.round_bf16, "tf32": port.round_tf32}
+TOL = {"bf16": 1e-2, "tf32": 1e-3}
+
+
+def run_plan(kxc, func, x, precision):
+    g = kxc.plan.CompiledGraph(func, precision)
+    out = g.run(torch.from_numpy(x).cuda())
+    assert kxc.ops.device_status() == 0
+    return out.cpu().numpy(), g
+
+
+def small_cnn(kxc, rng, N=3, C=8, H=20, O=64):
+    """conv(s2) -> relu -> maxpool -> [conv -> relu -> conv -> add -> relu] -> gap -> flatten -> gemm"""
+    R = kxc.relay
+    w = lambda *s: R.Constant(cuda_const(rng.normal(0, np.sqrt(2.0 / np.prod(s[1:])), s).astype(f32)))  # noqa: E731
+    b = lambda n: R.Constant(cuda_const(rng.normal(0, 0.05, (n,)).astype(f32)))  # noqa: E731
+    x = R.Var("input", (N, C, H, H))
+    y = R.Call("nn_relu", [R.Call("nn_conv2d", [x, w(O, C, 3, 3), b(O)], R.Conv2DAttrs((2, 2), (1, 1, 1, 1), (1, 1), 1))])
+    y = R.Call("nn_max_pool2d", [y], R.MaxPool2DAttrs((2, 2), (1, 1, 1, 1), (1, 1), (3, 3), "NCHW", False))
+    a = R.Call("nn_relu", [R.Call("nn_conv2d", [y, w(O, O, 3, 3), b(O)], R.Conv2DAttrs((1, 1), (1, 1, 1, 1), (1, 1), 1))])
+    c = R.Call("nn_conv2d", [a, w(O, O, 3, 3), b(O)], R.Conv2DAttrs((1, 1), (1, 1, 1, 1), (1, 1), 1))
+    y = R.Call("nn_relu", [R.Call("add", [c, y])])
+    y = R.Call("nn_flatten", [R.Call("nn_global_avg_pool2d", [y])])
+    y = R.Call("nn_gemm", [y, w(10, O), b(10)], R.GemmAttrs(1.0, 1.0, 0, 1))
+    return R.Function([x], y)
+
+
+def host_func(func):
+    """Same graph with numpy constants for the oracle."""
+    import copy
+    memo = {}
+
+    def conv(e):
+        if id(e) in memo:
+            return memo[id(e)]
+        if hasattr(e, "args"):
+            r = copy.copy(e)
+            r.args = [conv(a) for a in e.args]
+        elif hasattr(e, "data"):
+            r = copy.copy(e)
+            r.data = e.data.cpu().numpy()
+        else:
+            r = e
+        memo[id(e)] = r
+        return r
+
+    out = copy.copy(func)
+    out.body = conv(func.body)
+    return out
+
+
+@pytest.mark.parametrize("precision", ["bf16", "tf32"])
+def test_small_cnn_plan(kxc, rng, precision):
+    func = small_cnn(kxc, rng)
+    x = rng.normal(0, 1, (3, 8, 20, 20)).astype(f32)
+    got, g = run_plan(kxc, func, x, precision)
+    hf = host_func(func)
+    assert g.num_launches <= 7  # input conversion, 3 fused convs, pool, gap, gemm
+    exact = ograph.run(hf, [x])
+    assert_close(got, exact, TOL[precision] * 2, f"small cnn {precision} vs fp32 reference arithmetic")
+    emu = ograph.run(hf, [x], operand_round=ROUND[precision])
+    max_abs, max_rel = ref_metric(got, emu)
+    assert min(max_abs, max_rel) <= (3e-3 if precision == "bf16" else 2e-4), (max_abs, max_rel)
+    # running twice gives identical bits (no atomics, fixed summation order)
+    again = g.run(torch.from_numpy(x).cuda()).cpu().numpy()
+    assert np.array_equal(got, again)
+
+
+def test_single_conv_plan_matches_per_op(kxc, rng):
+    R = kxc.relay
+    x = rng.uniform(-1, 1, (2, 64, 14, 14)).astype(f32)
+    wt = rng.normal(0, 0.05, (128, 64, 3, 3)).astype(f32)
+    bs = rng.normal(0, 0.05, (128,)).astype(f32)
+    xv = R.Var("input", x.shape)
+    func = R.Function([xv], R.Call("nn_relu", [R.Call("nn_conv2d", [xv, R.Constant(cuda_const(wt)), R.Constant(cuda_const(bs))],
+                                                      R.Conv2DAttrs((1, 1), (1, 1, 1, 1), (1, 1), 1))]))
+    got, g = run_plan(kxc, func, x, "bf16")
+    per_op = kxc.ops.nn_conv2d(cuda_const(x), cuda_const(wt), cuda_const(bs), (1, 1), (1, 1), relu=True, precision="bf16").cpu().numpy()
+    assert np.array_equal(got, per_op)
+    exp = port.relu(port.conv2d(port.round_bf16(x), port.round_bf16(wt), bs, (1, 1), (1, 1)))
+    assert np.abs(got - exp).max() <= 2e-4
+
+
+def test_plan_rejects_unsupported(kxc):
+    R = kxc.relay
+    xv = R.Var("input", (1, 8, 4, 4))
+    func = R.Function([xv], R.Call("softmax", [xv]))
+    with pytest.raises(kxc.KxcError):
+        kxc.plan.CompiledGraph(func, "bf16")
+
+
+@pytest.mark.parametrize("precision", ["bf16", "tf32"])
+def test_resnet18_plan(kxc, precision):
+    """Full ResNet-18 at batch 2 (the benchmark's architecture and weight/input distributions)."""
+    rs = kxc.resnet18
+    weights = rs.make_weights(seed=0)
+    N = 2
+    x = np.random.default_rng(7).normal(0, 1, (N, 3, 224, 224)).astype(f32)
+    func = rs.build(N, weights, to_constant=cuda_const)
+    got, g = run_plan(kxc, func, x, precision)
+    assert got.shape == (N, 1000)
+    assert g.num_launches == 25  # stem pack + 20 fused convs + maxpool + gap + gemm... flatten is a view
+    hf = rs.build(N, weights)
+    exact = ograph.run(hf, [x], workers=8)
+    max_abs, max_rel = ref_metric(got, exact)
+    print(f"resnet18 {precision}: vs fp32 reference arithmetic max_abs={max_abs:.3e} max_rel={max_rel:.3e}")
+    emu = ograph.run(hf, [x], operand_round=ROUND[precision], workers=8)
+    e_abs, e_rel = ref_metric(got, emu)
+    print(f"resnet18 {precision}: vs same-rounding oracle max_abs={e_abs:.3e} max_rel={e_rel:.3e}")
+    assert min(e_abs, e_rel) <= (1e-2 if precision == "bf16" else 1e-3)
+    assert min(max_abs, max_rel) <= (5e-2 if precision == "bf16" else 5e-3)
+    assert (got.argmax(1) == exact.argmax(1)).all()
