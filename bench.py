@@ -1,0 +1,276 @@
+#!/usr/bin/env python
+"""Headline benchmark: ResNet-18 inference throughput (img/s) through the B200 operator path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--batch B]
+
+One "step" = one pass of the whole graph (stem pack, 20 fused tensor-core convolutions, max pool,
+global average pool, dense) over the global batch of 1024 synthetic images, bf16 operands with fp32
+accumulation, sharded data-parallel over N GPUs (1024/N images per GPU, weights replicated, logits
+gathered to rank 0 with one NCCL gather inside the step). Prints ONE JSON line on rank 0.
+
+value     device-timed (CUDA events, max over ranks) with the inputs resident in HBM
+e2e       the same step through the public API with HOST buffers: pinned-host -> device copy of the
+          images and device -> host read of the logits inside the timed region
+roofline  the tensor-core implicit-GEMM kernel (20 conv + 1 dense launches per step): algorithmic FLOPs
+          / its summed launch durations, from one run with CUDA events between launches
+cpu_baseline  the reference compiler's own CPU lowering (oracle/_ref) on a bounded sample, rank 0 only
+
+--impl reference times that CPU path alone, on all host cores (independent batch shards per core).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+GLOBAL_BATCH = 1024
+METRIC = "resnet18_inference_throughput"
+UNIT = "img/s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"], "tflops_sustained": p["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.samples, self.proc, self.thread, self.index = [], None, None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm / cpu baseline
+def cpu_reference_throughput(images_per_worker, workers, steps=1, warmup=0):
+    """ResNet-18 through the reference compiler's own CPU lowering (oracle/_ref kernels chained per call),
+    `workers` independent single-threaded batch shards. Returns (img/s, kind)."""
+    import numpy as np
+    from concurrent.futures import ThreadPoolExecutor
+
+    from hdkx_aicompiler_b200 import resnet18
+    from oracle import graph as ograph
+    from oracle import ref as oref
+    kind = "reference" if oref.available() else "port"
+    backend = oref if kind == "reference" else None
+    weights = resnet18.make_weights(seed=0)
+    func = resnet18.build(images_per_worker, weights)
+    rng = np.random.default_rng(1)
+    shards = [rng.normal(0, 1, (images_per_worker, 3, 224, 224)).astype(np.float32) for _ in range(workers)]
+    run = lambda x: ograph.run(func, [x], backend=backend)  # noqa: E731
+    run(shards[0][:images_per_worker])  # compiles/loads the per-op kernels outside the timed region
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        if workers == 1:
+            run(shards[0])
+        else:
+            with ThreadPoolExecutor(workers) as ex:
+                list(ex.map(run, shards))
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    return images_per_worker * workers * len(times) / sum(times), kind
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    per_worker = 1
+    value, kind = cpu_reference_throughput(per_worker, cores, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    sample = f"{per_worker} image per core x {cores} cores per step (independent single-threaded shards), {max(1, args.steps)} steps"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * per_worker * cores / value, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"resnet18 inference, global batch {GLOBAL_BATCH} (bounded CPU sample)", "global_batch": GLOBAL_BATCH},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch (default: the benchmark's 1024)")
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "tf32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from hdkx_aicompiler_b200 import ops, plan, resnet18
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    assert args.batch % world == 0
+    per_gpu = args.batch // world
+    warmup = max(args.warmup, 3)
+
+    weights = resnet18.make_weights(seed=0)
+    func = resnet18.build(per_gpu, weights, to_constant=lambda a: torch.from_numpy(a).to(device))
+    graph = plan.CompiledGraph(func, args.precision)
+
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    host_in = torch.empty((per_gpu, 3, 224, 224), dtype=torch.float32).normal_(0, 1, generator=gen).pin_memory()
+    x = host_in.to(device, non_blocking=True)
+    logits = torch.empty(graph.out_shape, dtype=torch.float32, device=device)
+    gathered = [torch.empty_like(logits) for _ in range(world)] if (world > 1 and rank == 0) else None
+    host_out = torch.empty((args.batch if rank == 0 else per_gpu, graph.out_shape[1]), dtype=torch.float32).pin_memory()
+
+    def step(from_host):
+        if from_host:
+            x.copy_(host_in, non_blocking=True)
+        graph.run(x, out=logits)
+        if world > 1:
+            dist.gather(logits, gathered, dst=0)  # GatherToWorker0: concat shards on dim 0 in rank order
+        if from_host:
+            if world > 1 and rank == 0:
+                for r in range(world):
+                    host_out[r * per_gpu:(r + 1) * per_gpu].copy_(gathered[r], non_blocking=True)
+            elif world == 1:
+                host_out.copy_(logits, non_blocking=True)
+
+    def timed(from_host, steps):
+        for _ in range(warmup):
+            step(from_host)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step(from_host)
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total_ms = timed(False, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_ms = timed(True, args.steps)
+    ops.device_status(device)
+
+    # per-launch durations (one extra run with an event between launches), rank 0's shard
+    _, launch_ms = graph.run_timed(x, out=logits)
+    for _ in range(2):
+        _, more = graph.run_timed(x, out=logits)
+        launch_ms = [min(a, b) for a, b in zip(launch_ms, more)]
+    info = graph.launch_info()
+
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    ms_per_step = total_ms / args.steps
+    value = args.batch / (ms_per_step / 1e3)
+    tc = [(n, f, b, t) for (n, f, b), t in zip(info, launch_ms) if n.startswith(("conv_igemm", "dense_igemm"))]
+    tc_flops = sum(f for _, f, _, _ in tc)
+    tc_ms = sum(t for _, _, _, t in tc)
+    achieved = tc_flops / (tc_ms / 1e3) / 1e12
+    layers = [{"launch": n, "ms": round(t, 4), "tflops": round(f / (t / 1e3) / 1e12, 1) if f else None,
+               "gbs": round(b / (t / 1e3) / 1e9, 0)} for (n, f, b), t in zip(info, launch_ms)]
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16" if args.precision == "bf16" else "tf32", "data": "synthetic",
+        "config": {"workload": f"resnet18 inference, global batch {args.batch}, {args.precision} operands / fp32 accumulate, "
+                               f"{per_gpu} images per GPU, weights replicated, logits gathered to rank 0",
+                   "global_batch": args.batch, "per_gpu_batch": per_gpu, "parallelism": f"dp{world}",
+                   "l2": "inputs larger than L2 (616 MB of images and >1 GB of activations per step per GPU at N=1)"},
+        "clocks": clocks,
+        "e2e": {"value": args.batch / (e2e_ms / args.steps / 1e3), "unit": UNIT,
+                "h2d_bytes_per_step": int(host_in.numel() * 4 * world), "d2h_bytes_per_step": int(args.batch * graph.out_shape[1] * 4)},
+        "gpu_launches": int(graph.num_launches * args.steps),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["tflops_sustained"], "traffic": None, "peak_source": peaks["source"],
+                     "kernel": "conv_igemm_kernel (20 conv + 1 dense launches per step)",
+                     "flops_per_step_per_gpu": tc_flops, "ms_per_step_in_kernel": tc_ms},
+        "launches": layers,
+    }
+    if not args.no_cpu_baseline:
+        t0 = time.perf_counter()
+        cpu_value, kind = cpu_reference_throughput(4, 1, steps=1, warmup=0)
+        line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": kind,
+                                "sample": f"4 images of the same network, one core, {time.perf_counter() - t0:.0f} s incl. kernel build"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

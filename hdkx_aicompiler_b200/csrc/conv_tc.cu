@@ -6,7 +6,8 @@
 //   warp 1      MMA issuer     one lane issues tcgen05.mma (M = 128, N = BN, K = 32 bytes per
 //                              instruction) into one of two TMEM accumulators; tcgen05.commit
 //                              releases stages and publishes finished accumulators; owns TMEM alloc
-//   warps 2..5  epilogue       tcgen05.ld the accumulator (each warp its own 32-lane quadrant),
+//   warps 2..9  epilogue       tcgen05.ld the accumulator (two warps per 32-lane quadrant, each half
+//                              of the columns),
 //                              +bias -> +residual -> ReLU (or int8 requantize), store; overlaps the
 //                              next tile's main loop through the second accumulator
 //
@@ -27,7 +28,7 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;  // 2 control warps + 8 epilogue warps
 constexpr int kSmemLimit = 227 * 1024;
 
 template <int KB_BYTES, int BN>
@@ -170,6 +171,14 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
 #pragma unroll
                 for (int j = 0; j < 32; ++j) f[j] = f[j] > 0.0f ? f[j] : 0.0f;
             }
+            if (p.round_out_tf32) {  // activation that feeds another tf32 contraction: store what it will read
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    uint32_t u = __float_as_uint(f[j]);
+                    if ((u & 0x7f800000u) != 0x7f800000u) u = (u + 0xfffu + ((u >> 13) & 1u)) & 0xffffe000u;
+                    f[j] = __uint_as_float(u);
+                }
+            }
             if (vec) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
@@ -194,6 +203,51 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
                 }
             }
         }
+    }
+}
+
+// Hot-path epilogue (bf16 NHWC activations, channel count a multiple of 32, 16-byte aligned pointers):
+// the residual vector is fetched by the caller BEFORE it waits for the accumulator, so its latency
+// hides behind the main loop.
+__device__ __forceinline__ void epilogue_fast_bf16(const TcParams& p, const uint32_t (&v)[32], int c0, size_t pix,
+                                                   const uint4 (&res)[4], bool has_res) {
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+    if (p.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + j));
+            f[j] = __fadd_rn(f[j], b.x);
+            f[j + 1] = __fadd_rn(f[j + 1], b.y);
+            f[j + 2] = __fadd_rn(f[j + 2], b.z);
+            f[j + 3] = __fadd_rn(f[j + 3], b.w);
+        }
+    }
+    if (has_res) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const uint32_t w[4] = {res[g].x, res[g].y, res[g].z, res[g].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                f[g * 8 + 2 * k] = __fadd_rn(f[g * 8 + 2 * k], bf16_lo(w[k]));
+                f[g * 8 + 2 * k + 1] = __fadd_rn(f[g * 8 + 2 * k + 1], bf16_hi(w[k]));
+            }
+        }
+    }
+    if (p.relu) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = f[j] > 0.0f ? f[j] : 0.0f;
+    }
+    uint4* out = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + pix * p.Cout + c0);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        uint4 o;
+        o.x = pack_bf16(f[g * 8 + 0], f[g * 8 + 1]);
+        o.y = pack_bf16(f[g * 8 + 2], f[g * 8 + 3]);
+        o.z = pack_bf16(f[g * 8 + 4], f[g * 8 + 5]);
+        o.w = pack_bf16(f[g * 8 + 6], f[g * 8 + 7]);
+        out[g] = o;
     }
 }
 
@@ -226,7 +280,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&bar_acc_full[a]), 1);
-            mbar_init(smem_u32(&bar_acc_empty[a]), 4);  // one arrival per epilogue warp
+            mbar_init(smem_u32(&bar_acc_empty[a]), 8);  // one arrival per epilogue warp
         }
         mbar_fence_init();
     }
@@ -327,12 +381,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
     } else {
         // ------------------------------ epilogue ------------------------------
         const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+        const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp handles
+        constexpr int kChunksPerWarp = BN / 64;
         const int row = quad * 32 + lane;
         const int box_hw = p.BH * p.BW;
         const int n_l = row / box_hw;
         const int rem = row - n_l * box_hw;
         const int h_l = rem / p.BW;
         const int w_l = rem - h_l * p.BW;
+        const bool fast = (kOutMode == kOutNHWC_BF16) && p.vec_ok && ((p.Cout & 31) == 0);
+        const bool has_res = p.residual != nullptr;
         int acc = 0;
         uint32_t acc_phase = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
@@ -343,17 +401,39 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
             const int tn = r / p.tiles_h;
             const int n = tn * p.BNI + n_l, oh = th * p.BH + h_l, ow = tw * p.BW + w_l;
             const bool valid = (row < rows_used) && (n < p.N) && (oh < p.OH) && (ow < p.OW);
+            const size_t pix = ((size_t)n * p.OH + oh) * p.OW + ow;
+            const int col0 = half * kChunksPerWarp * 32;  // first column of this warp inside the tile
+            const int c_base = ct * BN + col0;
+            uint4 res_cur[4] = {};
+            if (fast && has_res && valid && c_base < p.Cout) {
+                const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.residual) + pix * p.Cout + c_base);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) res_cur[g] = __ldg(rp + g);
+            }
             bool ok = mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + col0);
 #pragma unroll 1
-            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+            for (int i = 0; i < kChunksPerWarp; ++i) {
+                const int c0 = c_base + i * 32;
                 uint32_t v[32];
-                tmem_ld_32x32(t_addr + (uint32_t)(chunk * 32), v);
+                tmem_ld_32x32(t_addr + (uint32_t)(i * 32), v);
+                uint4 res_next[4] = {};
+                if (fast && has_res && valid && (i + 1 < kChunksPerWarp) && (c0 + 32 < p.Cout)) {
+                    const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.residual) + pix * p.Cout + c0 + 32);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) res_next[g] = __ldg(rp + g);
+                }
                 tmem_ld_wait();
-                epilogue_chunk<kOutMode>(p, v, ct * BN + chunk * 32, valid, n, oh, ow);
+                if (fast) {
+                    if (valid && c0 < p.Cout) epilogue_fast_bf16(p, v, c0, pix, res_cur, has_res);
+                } else {
+                    epilogue_chunk<kOutMode>(p, v, c0, valid, n, oh, ow);
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) res_cur[g] = res_next[g];
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -459,8 +539,11 @@ void tc_pick_tile(int N, int OH, int OW, int* BW, int* BH, int* BNI) {
             if (bn < 1) bn = 1;
             const long long tiles = (long long)((OW + bw - 1) / bw) * ((OH + bh - 1) / bh) * ((N + bn - 1) / bn);
             const double eff = (double)N * OH * OW / ((double)tiles * 128.0);
-            // prefer higher efficiency; on ties a wider box (longer contiguous runs for TMA and stores)
-            if (eff > best + 1e-9 || (eff > best - 1e-9 && bw > bw_best)) {
+            // prefer higher efficiency; on ties the box with the most pixels per image (neighbouring filter
+            // taps of one tile then re-read the same cache lines), then the squarer one (smaller halo)
+            const int area = bw * bh, area_best = bw_best * bh_best;
+            const int skew = bw > bh ? bw - bh : bh - bw, skew_best = bw_best > bh_best ? bw_best - bh_best : bh_best - bw_best;
+            if (eff > best + 1e-9 || (eff > best - 1e-9 && (area > area_best || (area == area_best && skew < skew_best)))) {
                 best = eff;
                 bw_best = bw; bh_best = bh; bn_best = bn;
             }
@@ -547,7 +630,7 @@ int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_m
     p->tiles_h = (OH + p->BH - 1) / p->BH;
     p->tiles_n = (N + p->BNI - 1) / p->BNI;
 
-    int bn = Cout <= 64 ? 64 : 128;
+    int bn = Cout <= 64 ? 64 : (Cout <= 128 ? 128 : 256);
     cfg->dtype = dtype; cfg->kb_bytes = kb_bytes; cfg->bn = bn; cfg->out_mode = out_mode;
     p->tiles_c = (Cout + bn - 1) / bn;
 

@@ -40,6 +40,7 @@ struct alignas(64) TcParams {
     int BW, BH, BNI;             // tile box: cols x rows x images (BW*BH*BNI <= 128)
     int tiles_w, tiles_h, tiles_n, tiles_c;
     int relu;
+    int round_out_tf32;          // kOutNHWC_F32 only: round stored values to tf32 (they feed another tf32 contraction)
     int vec_ok;                  // bias/residual/out base pointers are 16-byte aligned: vector epilogue allowed
     const float* bias;           // fp32 bias (float paths), may be null
     const int32_t* bias_i32;     // int32 bias (int8 path)

@@ -52,8 +52,15 @@ struct Vec<float> {
         const float4 u = __ldg(reinterpret_cast<const float4*>(p));
         f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
     }
+    // fp32 storage holds tf32 operands: every stored activation is rounded (nearest even) to the 10-bit
+    // mantissa the tensor cores read, so that what the next contraction sees is well defined
+    __device__ static float rnd(float x) {
+        uint32_t u = __float_as_uint(x);
+        if ((u & 0x7f800000u) != 0x7f800000u) u = (u + 0xfffu + ((u >> 13) & 1u)) & 0xffffe000u;
+        return __uint_as_float(u);
+    }
     __device__ static void store(float* p, const float (&f)[4]) {
-        *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(p) = make_float4(rnd(f[0]), rnd(f[1]), rnd(f[2]), rnd(f[3]));
     }
 };
 

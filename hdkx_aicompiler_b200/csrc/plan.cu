@@ -223,7 +223,7 @@ int32_t setup_stem(kxc_b200_plan* pl, Step& st, int N, int C, int H, int W, int 
     p.tiles_w = (OW + p.BW - 1) / p.BW;
     p.tiles_h = (OH + p.BH - 1) / p.BH;
     p.tiles_n = (N + p.BNI - 1) / p.BNI;
-    const int bn = O <= 64 ? 64 : 128;
+    const int bn = O <= 64 ? 64 : (O <= 128 ? 128 : 256);
     p.tiles_c = (O + bn - 1) / bn;
     st.cfg = TcConfig{dt, 32 * eb, bn, out_mode};
     const size_t px = (size_t)4 * eb;  // bytes per packed pixel
@@ -381,7 +381,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
             st.bias_const = n.in.size() == 3 ? n.in[2] : -1;
             int cur = n.out;
             int c = sole_consumer(pl, cur);
-            if (c >= 0 && pl->nodes[c].op == "add") {
+            if (c >= 0 && pl->nodes[c].op == "add" && !pl->nodes[c].fused_into_other) {
                 Node& a = pl->nodes[c];
                 const int other = a.in[0] == cur ? a.in[1] : a.in[0];
                 Value* ov = pl->find(other);
@@ -393,7 +393,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
                     c = sole_consumer(pl, cur);
                 }
             }
-            if (c >= 0 && pl->nodes[c].op == "nn_relu") {
+            if (c >= 0 && pl->nodes[c].op == "nn_relu" && !pl->nodes[c].fused_into_other) {
                 st.relu = true;
                 pl->nodes[c].fused_into_other = true;
                 cur = pl->nodes[c].out;
@@ -435,7 +435,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
             int cur = n.out;
             if (n.op == "add") {
                 const int c = sole_consumer(pl, cur);
-                if (c >= 0 && pl->nodes[c].op == "nn_relu") {
+                if (c >= 0 && pl->nodes[c].op == "nn_relu" && !pl->nodes[c].fused_into_other) {
                     st.relu = true;
                     pl->nodes[c].fused_into_other = true;
                     cur = pl->nodes[c].out;
@@ -522,7 +522,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
             cv.Wp += cv.Wp & 1;
         }
         // the internal copy is a synthetic value with a negative id
-        const int copy_id = -(int)(input_copy.size() + 1);
+        const int copy_id = -(int)(input_copy.size() + 2);  // -1 means "no value"
         Value v;
         v.id = copy_id;
         v.kind = VKind::Intermediate;
@@ -670,6 +670,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
                                       pw.KH, pw.KW, st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0], st.pool.pool_size[1]));
             }
             st.params.relu = st.relu ? 1 : 0;
+            st.params.round_out_tf32 = (!st.out_is_graph_output && dt == kTcTF32) ? 1 : 0;
             st.params.residual = st.in1 >= 0 ? pl->storage(st.in1) : nullptr;
             st.params.out = st.out_is_graph_output ? nullptr : pl->storage(st.out);
             (void)ov;
@@ -680,6 +681,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
                 return fail(KXC_B200_ERR_UNSUPPORTED, "plan: %d dense outputs must be a multiple of %d", pw.O, lanes);
             KXC_TRY(tc_setup_conv(&st.params, &st.cfg, dt, om, pl->storage(st.in0), pw.ptr, st.N, 1, 1, pw.cpad, pw.O, 1, 1, 1, 0, 0, 1, 1));
             st.params.relu = 0;
+            st.params.round_out_tf32 = (!st.out_is_graph_output && dt == kTcTF32) ? 1 : 0;
             st.params.residual = nullptr;
             st.params.out = st.out_is_graph_output ? nullptr : pl->storage(st.out);
         }

@@ -42,24 +42,35 @@ def _post_order(body):
 
 
 def _materialised(calls, body):
-    """ids of call results that a fusing executor writes to memory."""
+    """ids of call results that a fusing executor writes to memory. Calls are visited in dependency
+    order; an add / relu can be absorbed by only one producer (the first that reaches it), so of the
+    two convolutions feeding a residual add, the second one's result is materialised."""
     cons = _consumers(calls)
-    fused_away = set()
+    fused_away, claimed = set(), set()
+
+    def sole(c, op):
+        cs = cons.get(id(c), [])
+        return cs[0] if (len(cs) == 1 and cs[0].op == op and c is not body and id(cs[0]) not in claimed) else None
+
     for c in calls:
-        if c.op != "nn_conv2d":
-            if c.op == "add" and id(c) not in fused_away:
-                cs = cons.get(id(c), [])
-                if len(cs) == 1 and cs[0].op == "nn_relu" and c is not body:
-                    fused_away.add(id(c))  # add -> relu pair: only the relu result is stored
+        if id(c) in claimed:
             continue
-        cur = c
-        cs = cons.get(id(cur), [])
-        if len(cs) == 1 and cs[0].op == "add" and cur is not body:
-            fused_away.add(id(cur))
-            cur = cs[0]
-            cs = cons.get(id(cur), [])
-        if len(cs) == 1 and cs[0].op == "nn_relu" and cur is not body:
-            fused_away.add(id(cur))
+        if c.op == "nn_conv2d":
+            cur = c
+            a = sole(cur, "add")
+            if a is not None:
+                fused_away.add(id(cur))
+                claimed.add(id(a))
+                cur = a
+            r = sole(cur, "nn_relu")
+            if r is not None:
+                fused_away.add(id(cur))
+                claimed.add(id(r))
+        elif c.op == "add":
+            r = sole(c, "nn_relu")
+            if r is not None:
+                fused_away.add(id(c))
+                claimed.add(id(r))
     return {id(c) for c in calls if id(c) not in fused_away}
 
 
@@ -74,7 +85,10 @@ def _batch_parallel(fn, x, workers):
     return np.concatenate(outs, axis=0)
 
 
-def run(func, inputs, operand_round=None, workers=1):
+def run(func, inputs, operand_round=None, workers=1, backend=None):
+    """backend: a module with the per-op functions (oracle.port by default, or oracle.ref for the
+    reference compiler's own generated kernels)."""
+    be = backend if backend is not None else port
     calls = _post_order(func.body)
     stored = _materialised(calls, func.body)
     rnd = operand_round if operand_round is not None else (lambda a: a)
@@ -100,22 +114,22 @@ def run(func, inputs, operand_round=None, workers=1):
             x, w = val(c.args[0], True), val(c.args[1], True)
             b = val(c.args[2]) if len(c.args) == 3 else None
             s, p, d = tuple(a.strides[:2]), tuple(a.padding[:2]), tuple(a.dilation[:2])
-            y = _batch_parallel(lambda xx: port.conv2d(xx, w, b, s, p, d), x, workers)
+            y = _batch_parallel(lambda xx: be.conv2d(xx, w, b, s, p, d), x, workers)
         elif c.op == "nn_relu":
-            y = port.relu(val(c.args[0]))
+            y = be.relu(val(c.args[0]))
         elif c.op == "add":
-            y = port.add(val(c.args[0]), val(c.args[1]))
+            y = be.add(val(c.args[0]), val(c.args[1]))
         elif c.op == "nn_max_pool2d":
-            y = port.max_pool2d(val(c.args[0]), tuple(a.pool_size[:2]), tuple(a.strides[:2]), tuple(a.padding), a.ceil_mode)
+            y = be.max_pool2d(val(c.args[0]), tuple(a.pool_size[:2]), tuple(a.strides[:2]), tuple(a.padding), a.ceil_mode)
         elif c.op == "nn_global_avg_pool2d":
-            y = port.global_avg_pool2d(val(c.args[0]))
+            y = be.global_avg_pool2d(val(c.args[0]))
         elif c.op == "nn_flatten":
             v = val(c.args[0])
             y = v.reshape(v.shape[0], -1)
         elif c.op == "nn_dense":
-            y = port.dense(val(c.args[0], True), val(c.args[1], True))
+            y = be.dense(val(c.args[0], True), val(c.args[1], True))
         elif c.op == "nn_gemm":
-            y = port.gemm(val(c.args[0], True), val(c.args[1], True), val(c.args[2]), a.alpha, a.beta, a.transA, a.transB)
+            y = be.gemm(val(c.args[0], True), val(c.args[1], True), val(c.args[2]), a.alpha, a.beta, a.transA, a.transB)
         else:
             raise NotImplementedError(c.op)
         if operand_round is not None and id(c) in stored and c is not func.body:

