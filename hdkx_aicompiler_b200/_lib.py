@@ -52,6 +52,8 @@ SYMBOLS = {
     "kxc_b200_device_status": (i32, [vp, ctypes.POINTER(i32)]),
     "kxc_b200_nn_conv2d": (i32, [vpp, ctypes.POINTER(Conv2dDesc), vp]),
     "kxc_b200_nn_conv2d_s8": (i32, [vpp, ctypes.POINTER(Conv2dDesc), vp]),
+    "kxc_b200_nn_conv2d_static_scratch": (i32, [vpp, ctypes.POINTER(Conv2dDesc), vp]),
+    "kxc_b200_static_scratch_bytes": (i64, []),
     "kxc_b200_nn_relu": (i32, [vpp, i64, vp]),
     "kxc_b200_add": (i32, [vpp, ctypes.POINTER(AddDesc), vp]),
     "kxc_b200_nn_max_pool2d": (i32, [vpp, ctypes.POINTER(Pool2dDesc), vp]),

@@ -608,7 +608,7 @@ int32_t tc_status_word(int** out) {
 
 int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_mode, const void* act_nhwc,
                       const void* w_packed, int N, int H, int W, int cpad, int Cout, int KH, int KW, int stride, int pad_h,
-                      int pad_w, int dil_h, int dil_w) {
+                      int pad_w, int dil_h, int dil_w, int* status_word) {
     const int eb = tc_elem_bytes(dtype);
     if (stride != 1 && stride != 2) return fail(KXC_B200_ERR_UNSUPPORTED, "tensor-core conv: stride %d", stride);
     const int row_bytes = cpad * eb;
@@ -660,7 +660,11 @@ int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_m
     const uint64_t bstrides[1] = {ktot * eb};
     const uint32_t bbox[2] = {(uint32_t)p->kb_elems, (uint32_t)bn};
     KXC_TRY(tc_make_tmap(&p->tmB, dtype, 2, const_cast<void*>(w_packed), bdims, bstrides, bbox, kb_bytes));
-    KXC_TRY(tc_status_word(&p->status));
+    if (status_word != nullptr) {
+        p->status = status_word;
+    } else {
+        KXC_TRY(tc_status_word(&p->status));
+    }
     return KXC_B200_OK;
 }
 

@@ -79,9 +79,11 @@ int32_t tc_status_word(int** out);
 
 // Fills tmA/tmB and the geometry of `p` for a regular convolution over an NHWC activation tensor
 // with `cpad` channels and weights packed as [Cout][KH][KW][cpad].
+// `status_word`: device int the kernel reports a run-out wait into; nullptr = the process-wide word
+// from tc_status_word().
 int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_mode, const void* act_nhwc,
                       const void* w_packed, int N, int H, int W, int cpad, int Cout, int KH, int KW, int stride, int pad_h,
-                      int pad_w, int dil_h, int dil_w);
+                      int pad_w, int dil_h, int dil_w, int* status_word = nullptr);
 
 inline int tc_elem_bytes(TcDType t) { return t == kTcBF16 ? 2 : (t == kTcTF32 ? 4 : 1); }
 // Channel padding the tensor-core path needs for `c` input channels: one K block per tap must be

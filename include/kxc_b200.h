@@ -84,6 +84,19 @@ typedef struct kxc_b200_conv2d_desc {
 
 int32_t kxc_b200_nn_conv2d(void** packed_args, const kxc_b200_conv2d_desc* desc, void* stream);
 
+/* nn_conv2d on the tensor cores WITHOUT any allocation (no counterpart in the reference, whose kernels
+ * malloc their intermediates on every call, src/codegen/codegen_llvm.cc:591-616).
+ * Same arguments and results as kxc_b200_nn_conv2d with precision KXC_B200_PREC_BF16 / _TF32, for hosts
+ * that cannot call the CUDA allocator at run time (a runtime that owns all device memory through its own
+ * pool, a latency-critical loop that may not take allocator locks). The operand workspace is a fixed
+ * array inside the library: each GPU that loads the library holds kxc_b200_static_scratch_bytes()
+ * (32 MiB) for it until exit. A convolution whose converted activations + packed weights exceed that
+ * size is rejected with KXC_B200_ERR_NOMEM. All calls share the array: calls whose GPU work overlaps
+ * (different streams) race, so keep them on one stream. The first call on a device resolves the array's
+ * address; make it before any stream capture begins. */
+int32_t kxc_b200_nn_conv2d_static_scratch(void** packed_args, const kxc_b200_conv2d_desc* desc, void* stream);
+int64_t kxc_b200_static_scratch_bytes(void);
+
 /* int8 convolution with int32 accumulate and fixed-point requantize. The reference has no quantized
  * op; accumulators equal its nn_conv2d run on the int8 values widened to int32 (include/te/topi/nn.h:107-158).
  * packed_args = { data int8[N,C,H,W], weight int8[O,C,KH,KW], bias int32[O], multiplier int32[O],
