@@ -152,6 +152,7 @@ def main():
     import torch.distributed as dist
 
     from hdkx_aicompiler_b200 import ops, plan, resnet18
+    from hdkx_aicompiler_b200.parallel import GatherToWorker0, shard_range
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -164,8 +165,8 @@ def main():
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    assert args.batch % world == 0
-    per_gpu = args.batch // world
+    shard_begin, shard_end = shard_range(rank, world, args.batch)
+    per_gpu = shard_end - shard_begin
     warmup = max(args.warmup, 3)
 
     weights = resnet18.make_weights(seed=0)
@@ -176,21 +177,17 @@ def main():
     host_in = torch.empty((per_gpu, 3, 224, 224), dtype=torch.float32).normal_(0, 1, generator=gen).pin_memory()
     x = host_in.to(device, non_blocking=True)
     logits = torch.empty(graph.out_shape, dtype=torch.float32, device=device)
-    gathered = [torch.empty_like(logits) for _ in range(world)] if (world > 1 and rank == 0) else None
+    gather = GatherToWorker0(graph.out_shape, torch.float32, device)
     host_out = torch.empty((args.batch if rank == 0 else per_gpu, graph.out_shape[1]), dtype=torch.float32).pin_memory()
 
     def step(from_host):
         if from_host:
             x.copy_(host_in, non_blocking=True)
         graph.run(x, out=logits)
-        if world > 1:
-            dist.gather(logits, gathered, dst=0)  # GatherToWorker0: concat shards on dim 0 in rank order
-        if from_host:
-            if world > 1 and rank == 0:
-                for r in range(world):
-                    host_out[r * per_gpu:(r + 1) * per_gpu].copy_(gathered[r], non_blocking=True)
-            elif world == 1:
-                host_out.copy_(logits, non_blocking=True)
+        parts = gather(logits)  # GatherToWorker0: shards in rank order on rank 0
+        if from_host and rank == 0:
+            for r, part in enumerate(parts):
+                host_out[r * per_gpu:(r + 1) * per_gpu].copy_(part, non_blocking=True)
 
     def timed(from_host, steps):
         for _ in range(warmup):
