@@ -235,7 +235,7 @@ def main():
     peaks = load_peaks()
     ms_per_step = total_ms / args.steps
     value = args.batch / (ms_per_step / 1e3)
-    tc = [(n, f, b, t) for (n, f, b), t in zip(info, launch_ms) if n.startswith(("conv_igemm", "dense_igemm"))]
+    tc = [(n, f, b, t) for (n, f, b), t in zip(info, launch_ms) if n.startswith(("conv_igemm", "conv_direct", "dense_igemm"))]
     tc_flops = sum(f for _, f, _, _ in tc)
     tc_ms = sum(t for _, _, _, t in tc)
     achieved = tc_flops / (tc_ms / 1e3) / 1e12

@@ -20,6 +20,7 @@
 #include "kxc_b200_plan.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -27,6 +28,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "conv_direct.cuh"
 #include "conv_tc.cuh"
 #include "layout.cuh"
 #include "nhwc_kernels.cuh"
@@ -79,6 +81,7 @@ struct Step {
     int bias_const = -1;  // constant value id (fp32 user pointer), -1 = none
     bool relu = false;
     bool out_is_graph_output = false;
+    int direct = 0;  // 0 = implicit-GEMM kernel; 1 = direct 3x3 kernel (resident weights, one halo load per tile)
     // conv / gemm
     TcParams params{};
     TcConfig cfg{};
@@ -553,7 +556,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
         bool direct = false;
         for (auto& st : pl->steps) {
             if (st.out >= 0 && pl->root_of(st.out) == pl->root_of(pl->output_id) && pl->root_of(st.out) == st.out &&
-                (st.kind == SKind::Conv || st.kind == SKind::Gemm) && pl->find(pl->output_id)->alias_of < 0) {
+                ((st.kind == SKind::Conv && st.in1 < 0) || st.kind == SKind::Gemm) && pl->find(pl->output_id)->alias_of < 0) {
                 st.out_is_graph_output = true;
                 direct = true;
             }
@@ -666,6 +669,15 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
             } else {
                 if (st.pool.strides[0] != st.pool.strides[1])
                     return fail(KXC_B200_ERR_UNSUPPORTED, "plan: nn_conv2d with different strides in h and w");
+                const char* dmode = getenv("KXC_B200_DIRECT3X3");  // "0" selects the implicit-GEMM kernel for A/B runs
+                const int direct_mode = dmode ? atoi(dmode) : 1;
+                if (direct_mode > 0 && !st.out_is_graph_output &&
+                    direct3x3_applicable(dt, st.C, pw.O, pw.KH, pw.KW, st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0],
+                                         st.pool.pool_size[1], (int)ov->shape[3])) {
+                    st.direct = 1;
+                    KXC_TRY(direct3x3_setup(&st.params, pl->storage(st.in0), pw.ptr, st.N, st.H, st.W));
+                    st.cfg = TcConfig{dt, 128, 64, om};
+                } else
                 KXC_TRY(tc_setup_conv(&st.params, &st.cfg, dt, om, pl->storage(st.in0), pw.ptr, st.N, st.H, st.W, st.cpad, pw.O,
                                       pw.KH, pw.KW, st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0], st.pool.pool_size[1]));
             }
@@ -737,7 +749,11 @@ static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream
                 p.bias = st.bias_const >= 0 ? static_cast<const float*>(arg_of(st.bias_const)) : nullptr;
                 if (st.out_is_graph_output) p.out = out_ptr;
                 tc_finish_params(&p);
-                KXC_TRY(tc_launch(st.cfg, p, s));
+                if (st.direct > 0) {
+                    KXC_TRY(direct3x3_launch(p, s));
+                } else {
+                    KXC_TRY(tc_launch(st.cfg, p, s));
+                }
                 break;
             }
             case SKind::MaxPool:
@@ -816,7 +832,7 @@ extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, c
             fl = 2.0 * out_elems * w.C * w.KH * w.KW;  // padded taps counted, as the reference executes them
             const double in_bytes = w.mode == 1 ? (double)st.N * st.Hp * st.Wp * 4 * eb : (double)st.N * st.H * st.W * st.cpad * eb;
             by = in_bytes + (double)w.bytes + out_elems * (st.out_is_graph_output ? 4.0 : eb) + (st.in1 >= 0 ? out_elems * eb : 0.0) + 4.0 * w.O;
-            snprintf(buf, sizeof(buf), "conv_igemm c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d", w.C, st.H, st.W, w.O, w.KH, w.KW,
+            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d", st.direct ? "conv_direct" : "conv_igemm", w.C, st.H, st.W, w.O, w.KH, w.KW,
                      p.stride, st.in1 >= 0 ? " +res" : "", st.relu ? " +relu" : "", p.BNI, p.BH, p.BW, st.cfg.bn);
             break;
         }
