@@ -1,0 +1,279 @@
+// Direct stride-2 "stem" convolution (few input channels, KW <= 8, 64 output channels; the 7x7/s2
+// first layer of ResNet) on tcgen05 + TMEM, bf16.
+//
+// Input: the packed stem layout [N][Hp][Wp][4] bf16 with a zero border (8 bytes per pixel). For output
+// pixel (oh, ow) and filter row kh the K vector is the 8 consecutive pixels x 4 channels that start at
+// packed pixel (2*oh + kh, 2*ow): 64 contiguous bytes, and the vector of ow+1 starts 16 bytes later.
+// In the UNSWIZZLED K-major operand layout the rows of an 8-row core matrix are exactly 16 bytes apart
+// and the two 16-byte K chunks of one MMA are `leading byte offset` apart, so with LBO = 16 and
+// SBO = 128 the A operand of 128 consecutive output columns is simply a window of ONE packed input row
+// in shared memory — overlapping rows, no im2col copy, no per-tap TMA box.
+//
+// A CTA owns a strip of R consecutive output rows of one image: the 2R+5 packed input rows it needs
+// are fetched with one bulk copy (they are contiguous in global memory), each input row is used by up
+// to four output rows, and the 28 KiB of weights stay resident in shared memory in core-matrix order
+// [kh][k-chunk][cout][8]. Per output row: KH x 2 MMAs (M = 128 columns, N = 64, K = 16).
+//
+// Roles as in conv_tc.cu (producer warp, MMA warp + TMEM owner, 8 epilogue warps, two accumulators,
+// bounded waits).
+#include "conv_stem.cuh"
+
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "conv_epilogue.cuh"
+#include "sm100.cuh"
+
+namespace kxc_b200 {
+namespace {
+
+using namespace sm100;
+
+constexpr int kThreads = 320;
+constexpr int kBN = 64;
+constexpr int kMaxKH = 7;
+constexpr int kStripRows = 8;                         // output rows per strip
+constexpr int kMaxInRows = 2 * (kStripRows - 1) + kMaxKH;  // 21
+constexpr int kMaxRowBytes = 2048;                    // packed row (Wp * 8 bytes) upper bound
+constexpr int kStripBytes = ((kMaxInRows * kMaxRowBytes + 4096 + 1023) / 1024) * 1024;  // + slack for the M=128 over-read
+constexpr int kStages = 3;
+constexpr int kWeightBytes = kMaxKH * 4 * kBN * 16;   // 28672
+constexpr int kSmemBytes = kWeightBytes + kStages * kStripBytes + 1024;
+
+// Unswizzled K-major descriptor: rows 16 B apart inside a core matrix (fixed by the layout), K chunks
+// `lbo` apart, 8-row groups `sbo` apart.
+__device__ __forceinline__ uint64_t make_desc_none(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffff) >> 4);
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;  // layout type 0 = no swizzle
+}
+
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __grid_constant__ TcParams p) {
+    constexpr uint32_t kTmemCols = 2 * kBN;
+    constexpr uint32_t kIdesc = make_instr_desc(kFmtBF16, kAccF32, kBN);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_w;
+    __shared__ __align__(8) uint64_t bar_full[kStages];
+    __shared__ __align__(8) uint64_t bar_empty[kStages];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t w_smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t strip_smem = w_smem + kWeightBytes;
+
+    const int KH = p.taps_h;
+    const int row_bytes = p.aux_row_bytes;          // Wp * 8
+    const int Hp = p.aux_hp;
+    const int strips_per_image = (p.OH + kStripRows - 1) / kStripRows;
+    const int total_strips = strips_per_image * p.N;
+    const uint8_t* in_base = static_cast<const uint8_t*>(p.aux_in);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar_w), 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bar_acc_full[a]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[a]), 8);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    // The MMA of the last output columns reads a little past the last copied input row: make sure those
+    // bytes are finite bf16 (they only feed accumulator rows that are never stored).
+    for (uint32_t i = threadIdx.x; i < (uint32_t)(kStages * kStripBytes / 16); i += kThreads) {
+        const uint32_t addr = strip_smem + i * 16;
+        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort_ptr = &abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t wbytes = (uint32_t)(KH * 4 * kBN * 16);
+            mbar_arrive_expect_tx(smem_u32(&bar_w), wbytes);
+            bulk_copy_g2s(w_smem, p.aux_w, wbytes, smem_u32(&bar_w));
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int strip = blockIdx.x; strip < total_strips; strip += gridDim.x) {
+                const int n = strip / strips_per_image;
+                const int oh0 = (strip - n * strips_per_image) * kStripRows;
+                const int rows_out = (p.OH - oh0) < kStripRows ? (p.OH - oh0) : kStripRows;
+                int rows_in = 2 * (rows_out - 1) + KH;
+                if (2 * oh0 + rows_in > Hp) rows_in = Hp - 2 * oh0;
+                if (!mbar_wait_bounded(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr)) break;
+                const uint32_t full = smem_u32(&bar_full[stage]);
+                const uint32_t bytes = (uint32_t)(rows_in * row_bytes);
+                mbar_arrive_expect_tx(full, bytes);
+                bulk_copy_g2s(strip_smem + stage * kStripBytes, in_base + ((size_t)n * Hp + 2 * oh0) * row_bytes, bytes, full);
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = mbar_wait_bounded(smem_u32(&bar_w), 0, abort_ptr);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            for (int strip = blockIdx.x; ok && strip < total_strips; strip += gridDim.x) {
+                const int oh0 = (strip % strips_per_image) * kStripRows;
+                const int rows_out = (p.OH - oh0) < kStripRows ? (p.OH - oh0) : kStripRows;
+                if (!mbar_wait_bounded(smem_u32(&bar_full[stage]), phase, abort_ptr)) break;
+                tc_fence_after_sync();
+                const uint32_t strip_base = strip_smem + stage * kStripBytes;
+                for (int rr = 0; rr < rows_out; ++rr) {
+                    if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kBN);
+                    for (int kh = 0; kh < KH; ++kh) {
+                        const uint32_t a_row = strip_base + (uint32_t)((2 * rr + kh) * row_bytes);
+                        const uint32_t b_tap = w_smem + (uint32_t)(kh * 4 * kBN * 16);
+#pragma unroll
+                        for (int m = 0; m < 2; ++m) {
+                            const uint64_t a_desc = make_desc_none(a_row + m * 32, 16, 128);
+                            const uint64_t b_desc = make_desc_none(b_tap + m * 2 * (kBN * 16), kBN * 16, 128);
+                            umma<MmaKind::F16>(d_tmem, a_desc, b_desc, kIdesc, (kh | m) != 0 ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(smem_u32(&bar_acc_full[acc]));
+                    acc ^= 1;
+                    if (acc == 0) acc_phase ^= 1u;
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&bar_empty[stage]));
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int ow = quad * 32 + lane;
+        const int c0 = half * 32;
+        const bool col_ok = ow < p.OW;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int strip = blockIdx.x; ok && strip < total_strips; strip += gridDim.x) {
+            const int n = strip / strips_per_image;
+            const int oh0 = (strip - n * strips_per_image) * kStripRows;
+            const int rows_out = (p.OH - oh0) < kStripRows ? (p.OH - oh0) : kStripRows;
+            for (int rr = 0; rr < rows_out; ++rr) {
+                ok = mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kBN + c0), v);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+                if (col_ok) {
+                    const size_t pix = ((size_t)n * p.OH + (oh0 + rr)) * p.OW + ow;
+                    const uint4 no_res[4] = {};
+                    epilogue_fast_bf16(p, v, c0, pix, no_res, false);
+                }
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    }
+
+    if (*abort_ptr) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_ptr && p.status != nullptr) atomicExch(p.status, KXC_B200_ERR_DEVICE_WAIT);
+}
+
+// Stem weights in core-matrix order: [KH][4 k-chunks][64 cout][8] bf16, element e of chunk j = pixel 2j + e/4,
+// channel e%4; zero for kw >= KW or c >= C.
+__global__ void stem_pack_weights_core_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int O, int C,
+                                              int KH, int KW) {
+    const int total = KH * 4 * kBN * 8;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int e = i & 7, o = (i >> 3) & (kBN - 1), j = (i >> 9) & 3, kh = i >> 11;
+        const int kw = 2 * j + (e >> 2), c = e & 3;
+        float f = 0.0f;
+        if (o < O && c < C && kw < KW) f = w[((o * C + c) * KH + kh) * KW + kw];
+        out[i] = __float2bfloat16_rn(f);
+    }
+}
+
+}  // namespace
+
+bool stem_direct_applicable(TcDType dtype, int C, int O, int KH, int KW, int OW, int Wp) {
+    return dtype == kTcBF16 && C <= 4 && O == kBN && KH <= kMaxKH && KW <= 8 && OW <= 128 && Wp * 8 <= kMaxRowBytes &&
+           (Wp * 8) % 16 == 0;
+}
+
+size_t stem_direct_weight_bytes(int KH) { return (size_t)KH * 4 * kBN * 16; }
+
+int32_t stem_direct_pack_weights(const float* w, void* out, int O, int C, int KH, int KW, cudaStream_t s) {
+    stem_pack_weights_core_kernel<<<(KH * 4 * kBN * 8 + 255) / 256, 256, 0, s>>>(w, static_cast<__nv_bfloat16*>(out), O, C, KH, KW);
+    return check_launch("stem_pack_weights_core");
+}
+
+int32_t stem_direct_setup(TcParams* p, const void* packed_in, const void* packed_w, int N, int OH, int OW, int KH, int Hp, int Wp) {
+    p->N = N; p->OH = OH; p->OW = OW; p->Cout = kBN;
+    p->taps_h = KH; p->taps_w = 1; p->stride = 2;
+    p->BW = 128; p->BH = 1; p->BNI = 1;
+    p->tiles_w = 1; p->tiles_h = OH; p->tiles_n = N; p->tiles_c = 1;
+    p->aux_in = packed_in;
+    p->aux_w = packed_w;
+    p->aux_row_bytes = Wp * 8;
+    p->aux_hp = Hp;
+    KXC_TRY(tc_status_word(&p->status));
+    return KXC_B200_OK;
+}
+
+int32_t stem_direct_launch(const TcParams& p, cudaStream_t stream) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(conv_stem_direct_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    });
+    if (attr_err != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
+    if (!p.vec_ok || p.out == nullptr) return fail(KXC_B200_ERR_INVALID, "direct stem conv: pointers must be 16-byte aligned");
+    const long long strips = (long long)((p.OH + kStripRows - 1) / kStripRows) * p.N;
+    if (strips <= 0) return KXC_B200_OK;
+    const int grid = (int)(strips < kNumSMs ? strips : kNumSMs);
+    conv_stem_direct_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+    return check_launch("conv_stem_direct_kernel");
+}
+
+}  // namespace kxc_b200

@@ -1,0 +1,15 @@
+// Direct stride-2 stem convolution on the packed [N][Hp][Wp][4] bf16 layout (see conv_stem.cu).
+#pragma once
+
+#include "conv_tc.cuh"
+
+namespace kxc_b200 {
+
+bool stem_direct_applicable(TcDType dtype, int C, int O, int KH, int KW, int OW, int Wp);
+size_t stem_direct_weight_bytes(int KH);
+// OIHW fp32 -> [KH][4][64][8] bf16 core-matrix order
+int32_t stem_direct_pack_weights(const float* w, void* out, int O, int C, int KH, int KW, cudaStream_t s);
+int32_t stem_direct_setup(TcParams* p, const void* packed_in, const void* packed_w, int N, int OH, int OW, int KH, int Hp, int Wp);
+int32_t stem_direct_launch(const TcParams& p, cudaStream_t stream);
+
+}  // namespace kxc_b200

@@ -49,6 +49,10 @@ struct alignas(64) TcParams {
     const void* residual;        // same layout/dtype as out, may be null
     void* out;
     int* status;                 // device status word; non-zero after a bounded wait ran out
+    // direct stem kernel only (conv_stem.cu): packed input / core-matrix weights, packed row pitch, padded height
+    const void* aux_in;
+    const void* aux_w;
+    int aux_row_bytes, aux_hp;
 };
 
 struct TcConfig {

@@ -99,6 +99,63 @@ __global__ void __launch_bounds__(kThreads) maxpool_nhwc_kernel(const T* __restr
     }
 }
 
+// 3x3 window, stride 2, padding 1, even OH/OW: a thread produces a 2x2 block of outputs for one channel
+// vector from the 5x5 input window, walking the window ONCE in row-major order. Every one of the four
+// accumulators thereby still sees its own nine taps in the reference's rh -> rw order (bit-exact,
+// NaN handling included), with 25 loads per 4 outputs instead of 36.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) maxpool3x3s2p1_nhwc_kernel(const T* __restrict__ x, T* __restrict__ out, int N, int H,
+                                                                       int W, int C, int OH, int OW) {
+    constexpr int L = Vec<T>::kLanes;
+    const int cg = C / L, ow2n = OW / 2, oh2n = OH / 2;
+    const int64_t total = (int64_t)N * oh2n * ow2n * cg;
+    for (int64_t lin = (int64_t)blockIdx.x * kThreads + threadIdx.x; lin < total; lin += (int64_t)gridDim.x * kThreads) {
+        const int g = (int)(lin % cg);
+        int64_t t = lin / cg;
+        const int ow2 = (int)(t % ow2n); t /= ow2n;
+        const int oh2 = (int)(t % oh2n);
+        const int n = (int)(t / oh2n);
+        float m[2][2][L];
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int j = 0; j < L; ++j) m[a][b][j] = -INFINITY;
+        const T* base = x + (int64_t)n * H * W * C + g * L;
+#pragma unroll
+        for (int ir = 0; ir < 5; ++ir) {
+            const int ih = 4 * oh2 - 1 + ir;
+            const bool row_ok = ih >= 0 && ih < H;
+#pragma unroll
+            for (int ic = 0; ic < 5; ++ic) {
+                const int iw = 4 * ow2 - 1 + ic;
+                float v[L];
+                if (row_ok && iw >= 0 && iw < W) {
+                    Vec<T>::load(base + ((int64_t)ih * W + iw) * C, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < L; ++j) v[j] = -1e30f;
+                }
+                // input (ir, ic) is tap (ir - 2a, ic - 2b) of output (a, b) when both offsets are in [0, 2]
+#pragma unroll
+                for (int a = 0; a < 2; ++a)
+#pragma unroll
+                    for (int b = 0; b < 2; ++b)
+                        if (ir - 2 * a >= 0 && ir - 2 * a <= 2 && ic - 2 * b >= 0 && ic - 2 * b <= 2) {
+#pragma unroll
+                            for (int j = 0; j < L; ++j) m[a][b][j] = (m[a][b][j] > v[j]) ? m[a][b][j] : v[j];
+                        }
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+                Vec<T>::store(out + ((((int64_t)n * OH + 2 * oh2 + a) * OW + 2 * ow2 + b) * C) + g * L, m[a][b]);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads) gap_nhwc_kernel(const T* __restrict__ x, T* __restrict__ out, int N, int HW, int C) {
     constexpr int L = Vec<T>::kLanes;
@@ -183,26 +240,34 @@ __device__ __forceinline__ float to_operand<float>(float v) { return round_tf32_
 template <typename T>
 __global__ void __launch_bounds__(kThreads) stem_pack_kernel(const float* __restrict__ x, T* __restrict__ out, int N, int C,
                                                              int H, int W, int Hp, int Wp, int pad_h, int pad_w) {
-    const int64_t total = (int64_t)N * Hp * Wp;
+    // four consecutive packed pixels per thread (Wp is a multiple of 4): 12 independent loads in flight,
+    // 32 or 64 contiguous bytes stored
+    const int wq = Wp / 4;
+    const int64_t total = (int64_t)N * Hp * wq;
     for (int64_t lin = (int64_t)blockIdx.x * kThreads + threadIdx.x; lin < total; lin += (int64_t)gridDim.x * kThreads) {
-        const int wp = (int)(lin % Wp);
-        int64_t t = lin / Wp;
+        const int wp0 = (int)(lin % wq) * 4;
+        int64_t t = lin / wq;
         const int hp = (int)(t % Hp);
         const int n = (int)(t / Hp);
-        const int h = hp - pad_h, w = wp - pad_w;
-        T v[4];
+        const int h = hp - pad_h;
+        const bool row_ok = h >= 0 && h < H;
+        float f[4][4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            float f = 0.0f;
-            if (c < C && h >= 0 && h < H && w >= 0 && w < W) f = __ldg(x + (((int64_t)n * C + c) * H + h) * W + w);
-            v[c] = to_operand<T>(f);
+        for (int px = 0; px < 4; ++px) {
+            const int w = wp0 + px - pad_w;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                f[px][c] = (c < C && row_ok && w >= 0 && w < W) ? __ldg(x + (((int64_t)n * C + c) * H + h) * W + w) : 0.0f;
         }
-        T* dst = out + lin * 4;
-        if constexpr (sizeof(T) == 2) {
-            *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(v);
-        } else {
-            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(v);
-        }
+        T v[16];
+#pragma unroll
+        for (int px = 0; px < 4; ++px)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) v[px * 4 + c] = to_operand<T>(f[px][c]);
+        T* dst = out + (((int64_t)n * Hp + hp) * Wp + wp0) * 4;
+        constexpr int kVecs = (int)(sizeof(T) * 16 / 16);
+#pragma unroll
+        for (int q = 0; q < kVecs; ++q) reinterpret_cast<uint4*>(dst)[q] = reinterpret_cast<const uint4*>(v)[q];
     }
 }
 
@@ -246,6 +311,12 @@ int32_t maxpool_nhwc(const void* x, void* out, TcDType dt, int N, int H, int W, 
     if (C % lanes != 0) return fail(KXC_B200_ERR_UNSUPPORTED, "NHWC max pool: %d channels is not a multiple of %d", C, lanes);
     const int64_t items = (int64_t)N * OH * OW * (C / lanes);
     if (items == 0) return KXC_B200_OK;
+    if (KH == 3 && KW == 3 && SH == 2 && SW == 2 && PT == 1 && PL == 1 && (OH % 2) == 0 && (OW % 2) == 0 && OH == (H + 2 - 3) / 2 + 1 &&
+        OW == (W + 2 - 3) / 2 + 1) {
+        KXC_DISPATCH_ACT(dt, (maxpool3x3s2p1_nhwc_kernel<T><<<grid_for(items / 4, 16), kThreads, 0, s>>>(
+                                 static_cast<const T*>(x), static_cast<T*>(out), N, H, W, C, OH, OW)));
+        return check_launch("maxpool3x3s2p1_nhwc");
+    }
     KXC_DISPATCH_ACT(dt, (maxpool_nhwc_kernel<T><<<grid_for(items, 16), kThreads, 0, s>>>(
                              static_cast<const T*>(x), static_cast<T*>(out), N, H, W, C, OH, OW, KH, KW, SH, SW, PT, PL)));
     return check_launch("maxpool_nhwc");
@@ -281,7 +352,8 @@ int32_t nhwc_to_nchw_f32(const void* in, float* out, TcDType dt, int N, int C, i
 
 int32_t stem_pack(const float* x, void* out, TcDType dt, int N, int C, int H, int W, int Hp, int Wp, int pad_h, int pad_w,
                   cudaStream_t s) {
-    const int64_t items = (int64_t)N * Hp * Wp;
+    if (Wp % 4 != 0) return fail(KXC_B200_ERR_INVALID, "stem_pack: packed width %d must be a multiple of 4", Wp);
+    const int64_t items = (int64_t)N * Hp * (Wp / 4);
     if (items == 0) return KXC_B200_OK;
     KXC_DISPATCH_ACT(dt, (stem_pack_kernel<T><<<grid_for(items, 16), kThreads, 0, s>>>(x, static_cast<T*>(out), N, C, H, W, Hp, Wp,
                                                                                      pad_h, pad_w)));

@@ -29,6 +29,7 @@
 
 #include "common.cuh"
 #include "conv_direct.cuh"
+#include "conv_stem.cuh"
 #include "conv_tc.cuh"
 #include "layout.cuh"
 #include "nhwc_kernels.cuh"
@@ -69,7 +70,7 @@ struct PackedWeight {
     void* ptr = nullptr;       // plan-owned, tensor-core layout
     size_t bytes = 0;
     const void* source = nullptr;  // user pointer it was packed from
-    int mode = 0;              // 0 conv OHWI, 1 stem, 2 dense [N,K], 3 dense from [K,N]
+    int mode = 0;              // 0 conv OHWI, 1 stem (igemm), 2 dense [N,K], 3 dense from [K,N], 4 stem (direct kernel)
     int O = 0, C = 0, KH = 0, KW = 0, cpad = 0;
 };
 
@@ -116,8 +117,14 @@ struct kxc_b200_plan {
     size_t arena_bytes = 0;
     void* weight_arena = nullptr;
     int device = -1;
+    // optional CUDA-graph replay of one run (launch-bound small batches): the graph captured for a given
+    // packed-argument list is replayed while the caller keeps passing the same pointers
+    bool use_graph = false;
+    std::vector<void*> graph_args;
+    cudaGraphExec_t graph_exec = nullptr;
 
     ~kxc_b200_plan() {
+        if (graph_exec) cudaGraphExecDestroy(graph_exec);
         if (arena) cudaFree(arena);
         if (weight_arena) cudaFree(weight_arena);
     }
@@ -522,7 +529,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
             cv.Hp = st.H + 2 * st.pad_h;
             cv.Hp += cv.Hp & 1;
             cv.Wp = std::max(st.W + 2 * st.pad_w, 2 * (OW - 1) + 8);
-            cv.Wp += cv.Wp & 1;
+            cv.Wp = (cv.Wp + 3) / 4 * 4;  // the pack kernel writes four pixels per thread; rows stay 16-byte multiples
         }
         // the internal copy is a synthetic value with a negative id
         const int copy_id = -(int)(input_copy.size() + 2);  // -1 means "no value"
@@ -657,14 +664,26 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
     // ---- tensor maps and launch parameters ----
     for (auto& st : pl->steps) {
         if (st.kind == SKind::Conv) {
-            const PackedWeight& pw = pl->weights[st.weight];
+            PackedWeight& pw = pl->weights[st.weight];
             Value* ov = pl->find(st.out);
+            if (pw.mode == 1 && !st.out_is_graph_output) {
+                // the direct stem kernel writes bf16 NHWC only; its packed weights take the same number of bytes
+                const char* e = getenv("KXC_B200_STEM_DIRECT");  // "0" keeps the implicit-GEMM stem for A/B runs
+                if ((!e || atoi(e) != 0) && stem_direct_applicable(dt, st.C, pw.O, pw.KH, pw.KW, (int)ov->shape[3], st.Wp) &&
+                    stem_direct_weight_bytes(pw.KH) <= pw.bytes)
+                    pw.mode = 4;
+            }
             TcOutMode om = st.out_is_graph_output ? kOutNCHW_F32 : (dt == kTcBF16 ? kOutNHWC_BF16 : kOutNHWC_F32);
             if (st.in1 >= 0 && st.out_is_graph_output)
                 return fail(KXC_B200_ERR_UNSUPPORTED, "plan: a residual convolution cannot be the graph output");
             if (!st.out_is_graph_output && (pw.O % lanes))
                 return fail(KXC_B200_ERR_UNSUPPORTED, "plan: %d output channels must be a multiple of %d", pw.O, lanes);
-            if (pw.mode == 1) {
+            if (pw.mode == 4) {
+                st.direct = 2;
+                KXC_TRY(stem_direct_setup(&st.params, pl->storage(st.in0), pw.ptr, st.N, (int)ov->shape[2], (int)ov->shape[3], pw.KH,
+                                          st.Hp, st.Wp));
+                st.cfg = TcConfig{dt, 64, 64, om};
+            } else if (pw.mode == 1) {
                 KXC_TRY(setup_stem(pl, st, st.N, st.C, st.H, st.W, pw.O, pw.KH, pw.KW, st.pad_h, st.pad_w, pl->storage(st.in0), pw.ptr, om));
             } else {
                 if (st.pool.strides[0] != st.pool.strides[1])
@@ -724,6 +743,7 @@ static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream
         switch (w.mode) {
             case 0: KXC_TRY(pack_weights_ohwi(src, w.ptr, dt, w.O, w.C, w.KH, w.KW, w.cpad, s)); break;
             case 1: KXC_TRY(stem_pack_weights(static_cast<const float*>(src), w.ptr, dt, w.O, w.C, w.KH, w.KW, s)); break;
+            case 4: KXC_TRY(stem_direct_pack_weights(static_cast<const float*>(src), w.ptr, w.O, w.C, w.KH, w.KW, s)); break;
             case 2: KXC_TRY(convert_rows(static_cast<const float*>(src), w.ptr, dt, w.O, w.C, w.cpad, s)); break;
             case 3: KXC_TRY(nchw_to_nhwc(src, w.ptr, dt, 1, w.C, w.O, w.cpad, s)); break;
         }
@@ -749,7 +769,9 @@ static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream
                 p.bias = st.bias_const >= 0 ? static_cast<const float*>(arg_of(st.bias_const)) : nullptr;
                 if (st.out_is_graph_output) p.out = out_ptr;
                 tc_finish_params(&p);
-                if (st.direct > 0) {
+                if (st.direct == 2) {
+                    KXC_TRY(stem_direct_launch(p, s));
+                } else if (st.direct == 1) {
                     KXC_TRY(direct3x3_launch(p, s));
                 } else {
                     KXC_TRY(tc_launch(st.cfg, p, s));
@@ -777,8 +799,50 @@ static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream
     return KXC_B200_OK;
 }
 
+extern "C" int32_t kxc_b200_plan_set_cuda_graph(kxc_b200_plan* pl, int32_t enable) {
+    if (!pl) return fail(KXC_B200_ERR_INVALID, "plan_set_cuda_graph: null plan");
+    pl->use_graph = enable != 0;
+    return KXC_B200_OK;
+}
+
 extern "C" int32_t kxc_b200_plan_run(kxc_b200_plan* pl, void** packed_args, void* stream) {
-    return plan_run_impl(pl, packed_args, stream, nullptr);
+    if (!pl || !pl->finalized || !packed_args || !pl->use_graph) return plan_run_impl(pl, packed_args, stream, nullptr);
+    const size_t nargs = pl->inputs.size() + pl->constants.size() + 1;
+    bool packed = true;  // weights must already be packed from these constants: packing stays outside the graph
+    for (auto& w : pl->weights) packed = packed && (w.source == packed_args[pl->find(w.const_id)->arg_index]);
+    if (!packed) return plan_run_impl(pl, packed_args, stream, nullptr);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the legacy default stream cannot be captured: run eagerly there
+    if (s == nullptr || s == cudaStreamLegacy) return plan_run_impl(pl, packed_args, stream, nullptr);
+    const bool same = pl->graph_exec != nullptr && pl->graph_args.size() == nargs &&
+                      std::equal(pl->graph_args.begin(), pl->graph_args.end(), packed_args);
+    if (!same) {
+        if (pl->graph_exec) {
+            cudaGraphExecDestroy(pl->graph_exec);
+            pl->graph_exec = nullptr;
+        }
+        cudaGraph_t graph = nullptr;
+        if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+            cudaGetLastError();  // capture not possible on this stream right now: fall back to eager launches
+            return plan_run_impl(pl, packed_args, stream, nullptr);
+        }
+        const int32_t rc = plan_run_impl(pl, packed_args, stream, nullptr);
+        const cudaError_t e = cudaStreamEndCapture(s, &graph);
+        if (rc != KXC_B200_OK) {
+            if (graph) cudaGraphDestroy(graph);
+            return rc;
+        }
+        if (e != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+        const cudaError_t ie = cudaGraphInstantiate(&pl->graph_exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ie != cudaSuccess) {
+            pl->graph_exec = nullptr;
+            return fail(KXC_B200_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(ie));
+        }
+        pl->graph_args.assign(packed_args, packed_args + nargs);
+    }
+    KXC_CUDA_TRY(cudaGraphLaunch(pl->graph_exec, s));
+    return KXC_B200_OK;
 }
 
 extern "C" int32_t kxc_b200_plan_run_timed(kxc_b200_plan* pl, void** packed_args, void* stream, float* launch_ms,
@@ -830,9 +894,9 @@ extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, c
             const TcParams& p = st.params;
             const double out_elems = (double)p.N * p.OH * p.OW * w.O;
             fl = 2.0 * out_elems * w.C * w.KH * w.KW;  // padded taps counted, as the reference executes them
-            const double in_bytes = w.mode == 1 ? (double)st.N * st.Hp * st.Wp * 4 * eb : (double)st.N * st.H * st.W * st.cpad * eb;
+            const double in_bytes = (w.mode == 1 || w.mode == 4) ? (double)st.N * st.Hp * st.Wp * 4 * eb : (double)st.N * st.H * st.W * st.cpad * eb;
             by = in_bytes + (double)w.bytes + out_elems * (st.out_is_graph_output ? 4.0 : eb) + (st.in1 >= 0 ? out_elems * eb : 0.0) + 4.0 * w.O;
-            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d", st.direct ? "conv_direct" : "conv_igemm", w.C, st.H, st.W, w.O, w.KH, w.KW,
+            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d", st.direct == 2 ? "conv_stem_direct" : (st.direct ? "conv_direct" : "conv_igemm"), w.C, st.H, st.W, w.O, w.KH, w.KW,
                      p.stride, st.in1 >= 0 ? " +res" : "", st.relu ? " +relu" : "", p.BNI, p.BH, p.BW, st.cfg.bn);
             break;
         }

@@ -1,0 +1,120 @@
+"""Per-kernel measurements for the benchmark configurations that are not the headline number:
+
+  config 1  fused conv2d + bias + ReLU, 1x64x56x56 (*) 64x64x3x3          (tensor / launch bound)
+  config 2  max_pool2d 3x3 s2 p1 on 32x64x112x112 -> add -> relu            (HBM bound)
+  config 5  int8 convolution sweep over the 11 distinct ResNet-18 shapes at N=256, requantize + ReLU
+
+    python -m hdkx_aicompiler_b200.microbench [--config 1|2|5|all] [--iters 20]
+
+Prints one JSON line per measured kernel: CUDA-event time (L2 flushed between iterations by writing a
+256 MB buffer), achieved GB/s or TOP/s and the fraction of the measured peak in MEASURED_PEAKS.json
+(copy bandwidth / bf16 GEMM; int8 is reported against 2x the bf16 figure, the nominal ratio).
+Inputs are synthetic with the configurations' shapes and value distributions.
+"""
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+
+from . import ops, resnet18
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timeit(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return float(np.median(ts))
+
+
+def emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+def config1(iters, flush, hbm, tf, src):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.empty(1, 64, 56, 56, device="cuda").uniform_(-1, 1, generator=g)
+    w = torch.empty(64, 64, 3, 3, device="cuda").normal_(0, (2 / 576) ** 0.5, generator=g)
+    b = torch.empty(64, device="cuda").normal_(0, 0.01, generator=g)
+    out = torch.empty(1, 64, 56, 56, device="cuda")
+    flops = 2 * 64 * 56 * 56 * 64 * 9
+    for prec in ("fp32", "tf32", "bf16"):
+        ms = timeit(lambda: ops.nn_conv2d(x, w, b, (1, 1), (1, 1), relu=True, precision=prec, out=out), iters, flush)
+        emit(config=1, kernel=f"nn_conv2d+bias+relu {prec} (NCHW fp32 in/out, includes operand conversion)", ms=ms,
+             tflops=flops / ms / 1e9, frac_of_bf16_peak=flops / ms / 1e9 / tf, peak_source=src)
+
+
+def config2(iters, flush, hbm, tf, src):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.empty(32, 64, 112, 112, device="cuda").uniform_(-1, 1, generator=g)
+    res = torch.empty(32, 64, 56, 56, device="cuda").uniform_(-1, 1, generator=g)
+    out = torch.empty_like(res)
+    cases = [
+        ("max_pool2d_add_relu (fused chain)", 154.14e6, lambda: ops.max_pool2d_add_relu(x, res, (3, 3), (2, 2), (1, 1, 1, 1), out=out)),
+        ("nn_max_pool2d", 128.45e6, lambda: ops.nn_max_pool2d(x, (3, 3), (2, 2), (1, 1, 1, 1))),
+        ("add", 77.07e6, lambda: ops.add(res, out)),
+        ("nn_relu", 51.38e6, lambda: ops.nn_relu(res)),
+    ]
+    for name, nbytes, fn in cases:
+        ms = timeit(fn, iters, flush)
+        emit(config=2, kernel=name, ms=ms, algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, frac_of_hbm_peak=nbytes / ms / 1e6 / hbm,
+             peak_source=src)
+
+
+def config5(iters, flush, hbm, tf, src):
+    rng = np.random.default_rng(0)
+    N = 256
+    for name, cin, cout, k, s, p, h, _ in resnet18.CONV_SHAPES:
+        x = torch.from_numpy(np.clip(np.round(rng.normal(0, 32, (N, cin, h, h))), -128, 127).astype(np.int8)).cuda()
+        wf = rng.normal(0, np.sqrt(2.0 / (cin * k * k)), (cout, cin, k, k))
+        scale = np.abs(wf).reshape(cout, -1).max(axis=1) / 127.0
+        w = torch.from_numpy(np.clip(np.round(wf / scale[:, None, None, None]), -127, 127).astype(np.int8)).cuda()
+        b = torch.from_numpy(rng.integers(-1024, 1025, (cout,)).astype(np.int32)).cuda()
+        m = torch.from_numpy(rng.integers(2 ** 30, 2 ** 31, (cout,)).astype(np.int64).astype(np.int32)).cuda()
+        sh = torch.from_numpy(rng.integers(8, 16, (cout,)).astype(np.int32)).cuda()
+        oh = (h + 2 * p - k) // s + 1
+        ops_count = 2 * N * cout * oh * oh * cin * k * k
+        ms = timeit(lambda: ops.nn_conv2d_s8(x, w, b, m, sh, (s, s), (p, p), relu=True), max(3, iters // 4), flush)
+        same = bool(torch.equal(ops.nn_conv2d_s8(x, w, b, m, sh, (s, s), (p, p), relu=True),
+                                ops.nn_conv2d_s8(x, w, b, m, sh, (s, s), (p, p), relu=True, simt=True)))
+        emit(config=5, kernel=f"nn_conv2d_s8 {name} N={N} (NCHW int8 in/out, includes operand conversion)", ms=ms,
+             tops=ops_count / ms / 1e9, frac_of_2x_bf16_peak=ops_count / ms / 1e9 / (2 * tf), tcgen05_equals_cuda_core_kernel=same,
+             peak_source=src)
+    ops.device_status()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="all")
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    assert torch.cuda.is_available(), "needs a GPU"
+    hbm, tf, src = peaks()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for c, fn in (("1", config1), ("2", config2), ("5", config5)):
+        if args.config in ("all", c):
+            fn(args.iters, flush, hbm, tf, src)
+
+
+if __name__ == "__main__":
+    main()

@@ -37,6 +37,7 @@ _PLAN_SYMBOLS = {
     "kxc_b200_plan_value_shape": (i32, [vp, i32, ctypes.POINTER(i64)]),
     "kxc_b200_plan_num_launches": (i32, [vp]),
     "kxc_b200_plan_run": (i32, [vp, vpp, vp]),
+    "kxc_b200_plan_set_cuda_graph": (i32, [vp, i32]),
     "kxc_b200_plan_launch_info": (i32, [vp, i32, ctypes.c_char_p, i32, ctypes.POINTER(ctypes.c_double),
                                         ctypes.POINTER(ctypes.c_double)]),
     "kxc_b200_plan_run_timed": (i32, [vp, vpp, vp, ctypes.POINTER(ctypes.c_float), i32]),
@@ -66,7 +67,7 @@ def _attrs_c(call):
 
 
 class CompiledGraph:
-    def __init__(self, func: relay.Function, precision="bf16", device=None):
+    def __init__(self, func: relay.Function, precision="bf16", device=None, cuda_graph=False):
         self.lib = load()
         self.func = func
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -99,6 +100,8 @@ class CompiledGraph:
         rank = self.lib.kxc_b200_plan_value_shape(self.handle, out_id, shp)
         self.out_shape = tuple(shp[i] for i in range(rank))
         self.num_launches = self.lib.kxc_b200_plan_num_launches(self.handle)
+        if cuda_graph:
+            check("plan_set_cuda_graph", self.lib.kxc_b200_plan_set_cuda_graph(self.handle, 1))
         self._const_ptrs = [c.data.data_ptr() for c in self.constants]
         for c in self.constants:
             assert c.data.is_cuda and c.data.dtype == torch.float32 and c.data.is_contiguous()

@@ -74,6 +74,12 @@ int32_t kxc_b200_plan_num_launches(kxc_b200_plan* plan);
  * constant pointer changes (constants are immutable in the reference, include/relay/relay.h:120-125). */
 int32_t kxc_b200_plan_run(kxc_b200_plan* plan, void** packed_args, void* stream);
 
+/* Replay one run as a CUDA graph (off by default). With it on, the first run with a given packed-argument
+ * list executes normally (it packs the constants), the second captures the launches on `stream`, and later
+ * runs with the same pointers replay the captured graph with one launch call. Passing different pointers
+ * re-captures. The reference has no counterpart (its kernels are host loops). */
+int32_t kxc_b200_plan_set_cuda_graph(kxc_b200_plan* plan, int32_t enable);
+
 /* Measurement support (no reference counterpart: the reference only prints one wall-clock elapsed_ms,
  * test/onnx_importer_test.cpp:261-281). launch_info: a label, the algorithmic FLOPs and the compulsory
  * HBM bytes of launch `index`. run_timed: one run with a CUDA event between launches on `stream`;

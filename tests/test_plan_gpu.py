@@ -109,6 +109,33 @@ def test_single_conv_plan_matches_per_op(kxc, rng):
     assert np.abs(got - exp).max() <= 2e-4
 
 
+def test_plan_cuda_graph_replay_matches_eager(kxc, rng):
+    func = small_cnn(kxc, rng)
+    x1 = rng.normal(0, 1, (3, 8, 20, 20)).astype(f32)
+    x2 = rng.normal(0, 1, (3, 8, 20, 20)).astype(f32)
+    eager = kxc.plan.CompiledGraph(func, "bf16")
+    graphed = kxc.plan.CompiledGraph(func, "bf16", cuda_graph=True)
+    xin = torch.from_numpy(x1).cuda()
+    out = torch.empty(graphed.out_shape, device="cuda")
+    side = torch.cuda.Stream()  # capture needs a non-default stream (on the default stream the plan runs eagerly)
+    for stream in (side, torch.cuda.default_stream()):
+        for x in (x1, x2, x1):  # run 1 packs weights, run 2 captures, run 3 replays; same buffers each time
+            xin.copy_(torch.from_numpy(x))
+            torch.cuda.synchronize()
+            with torch.cuda.stream(stream):
+                graphed.run(xin, out=out)
+            torch.cuda.synchronize()
+            want = eager.run(torch.from_numpy(x).cuda()).cpu().numpy()
+            assert np.array_equal(out.cpu().numpy(), want)
+    other = torch.from_numpy(x2).cuda()  # different input pointer: re-capture, still right
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        got = graphed.run(other)
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), eager.run(other).cpu().numpy())
+    assert kxc.ops.device_status() == 0
+
+
 def test_plan_rejects_unsupported(kxc):
     R = kxc.relay
     xv = R.Var("input", (1, 8, 4, 4))
