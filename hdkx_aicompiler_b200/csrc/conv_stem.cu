@@ -20,6 +20,7 @@
 
 #include <cuda_bf16.h>
 
+#include <cmath>
 #include <mutex>
 
 #include "common.cuh"
@@ -220,6 +221,251 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __g
     if (threadIdx.x == 0 && *abort_ptr && p.status != nullptr) atomicExch(p.status, KXC_B200_ERR_DEVICE_WAIT);
 }
 
+// ------------------------------------------------------------------------------------------------------
+// Stem convolution + bias + ReLU + max_pool2d(3x3, stride 2, pad 1) in one kernel.
+//
+// The convolution's output (the largest activation of the network) never goes to HBM: the epilogue warps
+// write each finished conv row (bf16, after bias and ReLU, i.e. exactly the values the unfused kernel would
+// store) into a ring of 5 rows in shared memory and, after every second row, pool the three newest rows into
+// one output row. A strip is 9 conv rows (8s-1 .. 8s+7; the first one is recomputed from the strip above)
+// = 4 pooled rows. The pooling visits each window in the reference's rh -> rw order with explicit
+// compare-select, on the stored bf16 values, so the result is bit-identical to conv kernel + pool kernel.
+constexpr int kPoolStages = 2;
+constexpr int kPoolConvRows = kStripRows + 1;                          // 9 conv rows per strip
+constexpr int kPoolInRows = 2 * (kPoolConvRows - 1) + kMaxKH;          // 23 packed input rows
+constexpr int kPoolStripBytes = ((kPoolInRows * kMaxRowBytes + 4096 + 1023) / 1024) * 1024;
+constexpr int kRingRows = 5;
+constexpr int kRingRowBytes = 128 * 128;                               // 128 pixels x 64 channels bf16
+constexpr int kPoolSmemBytes = kWeightBytes + kPoolStages * kPoolStripBytes + kRingRows * kRingRowBytes + 1024;
+
+__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kThreads, 1) conv_stem_pool_kernel(const __grid_constant__ TcParams p) {
+    constexpr uint32_t kTmemCols = 2 * kBN;
+    constexpr uint32_t kIdesc = make_instr_desc(kFmtBF16, kAccF32, kBN);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_w;
+    __shared__ __align__(8) uint64_t bar_full[kPoolStages];
+    __shared__ __align__(8) uint64_t bar_empty[kPoolStages];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t w_smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t strip_smem = w_smem + kWeightBytes;
+    const uint32_t ring_smem = strip_smem + kPoolStages * kPoolStripBytes;
+
+    const int KH = p.taps_h;
+    const int row_bytes = p.aux_row_bytes;
+    const int Hp = p.aux_hp;
+    const int strips_per_image = p.OH / kStripRows;  // OH is a multiple of 8 for this kernel
+    const int total_strips = strips_per_image * p.N;
+    const uint8_t* in_base = static_cast<const uint8_t*>(p.aux_in);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar_w), 1);
+        for (int s = 0; s < kPoolStages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bar_acc_full[a]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[a]), 8);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    for (uint32_t i = threadIdx.x; i < (uint32_t)(kPoolStages * kPoolStripBytes / 16); i += kThreads) {
+        const uint32_t addr = strip_smem + i * 16;
+        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort_ptr = &abort_flag;
+
+    // Strip s of an image covers conv rows 8s-1 .. 8s+7 (local j = 0..8; j = 0 is skipped for s = 0, it is the
+    // pool's padding row) and packed input rows from max(16s-2, 0).
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t wbytes = (uint32_t)(KH * 4 * kBN * 16);
+            mbar_arrive_expect_tx(smem_u32(&bar_w), wbytes);
+            bulk_copy_g2s(w_smem, p.aux_w, wbytes, smem_u32(&bar_w));
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int strip = blockIdx.x; strip < total_strips; strip += gridDim.x) {
+                const int n = strip / strips_per_image;
+                const int s = strip - n * strips_per_image;
+                const int row0 = s > 0 ? 16 * s - 2 : 0;
+                int rows_in = (s > 0 ? 2 * (kPoolConvRows - 1) : 2 * (kPoolConvRows - 2)) + KH;
+                if (row0 + rows_in > Hp) rows_in = Hp - row0;
+                if (!mbar_wait_bounded(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr)) break;
+                const uint32_t full = smem_u32(&bar_full[stage]);
+                const uint32_t bytes = (uint32_t)(rows_in * row_bytes);
+                mbar_arrive_expect_tx(full, bytes);
+                bulk_copy_g2s(strip_smem + stage * kPoolStripBytes, in_base + ((size_t)n * Hp + row0) * row_bytes, bytes, full);
+                if (++stage == kPoolStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = mbar_wait_bounded(smem_u32(&bar_w), 0, abort_ptr);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            for (int strip = blockIdx.x; ok && strip < total_strips; strip += gridDim.x) {
+                const int s = strip % strips_per_image;
+                if (!mbar_wait_bounded(smem_u32(&bar_full[stage]), phase, abort_ptr)) break;
+                tc_fence_after_sync();
+                const uint32_t strip_base = strip_smem + stage * kPoolStripBytes;
+                for (int j = (s > 0 ? 0 : 1); j < kPoolConvRows; ++j) {
+                    if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kBN);
+                    const int in_row0 = s > 0 ? 2 * j : 2 * j - 2;  // local packed row of filter row 0
+                    for (int kh = 0; kh < KH; ++kh) {
+                        const uint32_t a_row = strip_base + (uint32_t)((in_row0 + kh) * row_bytes);
+                        const uint32_t b_tap = w_smem + (uint32_t)(kh * 4 * kBN * 16);
+#pragma unroll
+                        for (int m = 0; m < 2; ++m) {
+                            const uint64_t a_desc = make_desc_none(a_row + m * 32, 16, 128);
+                            const uint64_t b_desc = make_desc_none(b_tap + m * 2 * (kBN * 16), kBN * 16, 128);
+                            umma<MmaKind::F16>(d_tmem, a_desc, b_desc, kIdesc, (kh | m) != 0 ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(smem_u32(&bar_acc_full[acc]));
+                    acc ^= 1;
+                    if (acc == 0) acc_phase ^= 1u;
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&bar_empty[stage]));
+                if (++stage == kPoolStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int ow = quad * 32 + lane;
+        const int c0 = half * 32;
+        const int et = threadIdx.x - 64;  // 0..255 among the epilogue threads
+        const int POH = p.OH / 2, POW = p.OW / 2;
+        __nv_bfloat16* pooled = static_cast<__nv_bfloat16*>(p.out);
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        uint32_t ring_ctr = 0;  // ring slot of local conv row j is (ring_ctr + j) % kRingRows
+        bool ok = true;
+        bool first = true;
+        for (int strip = blockIdx.x; ok && strip < total_strips; strip += gridDim.x) {
+            const int n = strip / strips_per_image;
+            const int s = strip - n * strips_per_image;
+            // nobody may still be pooling the previous strip's rows when this strip's first rows are written
+            if (!first) epilogue_bar_sync();
+            first = false;
+            for (int j = (s > 0 ? 0 : 1); j < kPoolConvRows; ++j) {
+                ok = mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kBN + c0), v);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+
+                // conv row -> shared-memory ring: +bias, ReLU, round to bf16; 16-byte chunks XOR-swizzled by pixel
+                const uint32_t slot = (ring_ctr + (uint32_t)j) % kRingRows;
+                const uint32_t row_addr = ring_smem + slot * kRingRowBytes + (uint32_t)ow * 128u;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float f[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[q * 8 + e]);
+                    if (p.bias != nullptr) {
+                        const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + q * 8));
+                        const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + q * 8 + 4));
+                        f[0] = __fadd_rn(f[0], b0.x); f[1] = __fadd_rn(f[1], b0.y); f[2] = __fadd_rn(f[2], b0.z); f[3] = __fadd_rn(f[3], b0.w);
+                        f[4] = __fadd_rn(f[4], b1.x); f[5] = __fadd_rn(f[5], b1.y); f[6] = __fadd_rn(f[6], b1.z); f[7] = __fadd_rn(f[7], b1.w);
+                    }
+                    if (p.relu) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) f[e] = f[e] > 0.0f ? f[e] : 0.0f;
+                    }
+                    const uint32_t chunk = (uint32_t)(half * 4 + q) ^ ((uint32_t)ow & 7u);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + chunk * 16u), "r"(pack_bf16(f[0], f[1])),
+                                 "r"(pack_bf16(f[2], f[3])), "r"(pack_bf16(f[4], f[5])), "r"(pack_bf16(f[6], f[7]))
+                                 : "memory");
+                }
+
+                if ((j & 1) == 0 && j >= 2) {
+                    epilogue_bar_sync();  // rows j-2, j-1, j are complete
+                    const int ph = 4 * s + j / 2 - 1;
+                    for (int item = et; item < POW * 8; item += 256) {
+                        const int pw = item >> 3, g = item & 7;
+                        float m[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) m[e] = -INFINITY;
+#pragma unroll
+                        for (int rh = 0; rh < 3; ++rh) {
+                            const int lj = j - 2 + rh;
+                            const bool row_ok = !(s == 0 && lj == 0);  // conv row -1 is padding
+                            const uint32_t rslot = (ring_ctr + (uint32_t)lj) % kRingRows;
+#pragma unroll
+                            for (int rw = 0; rw < 3; ++rw) {
+                                const int col = 2 * pw - 1 + rw;
+                                float t[8];
+                                if (row_ok && col >= 0 && col < p.OW) {
+                                    uint32_t w0, w1, w2, w3;
+                                    const uint32_t a = ring_smem + rslot * kRingRowBytes + (uint32_t)col * 128u +
+                                                       (((uint32_t)g ^ ((uint32_t)col & 7u)) * 16u);
+                                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(a));
+                                    t[0] = bf16_lo(w0); t[1] = bf16_hi(w0); t[2] = bf16_lo(w1); t[3] = bf16_hi(w1);
+                                    t[4] = bf16_lo(w2); t[5] = bf16_hi(w2); t[6] = bf16_lo(w3); t[7] = bf16_hi(w3);
+                                } else {
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) t[e] = -1e30f;
+                                }
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) m[e] = (m[e] > t[e]) ? m[e] : t[e];
+                            }
+                        }
+                        uint4 o;
+                        o.x = pack_bf16(m[0], m[1]); o.y = pack_bf16(m[2], m[3]); o.z = pack_bf16(m[4], m[5]); o.w = pack_bf16(m[6], m[7]);
+                        *reinterpret_cast<uint4*>(pooled + ((((size_t)n * POH + ph) * POW + pw) * kBN) + g * 8) = o;
+                    }
+                }
+            }
+            ring_ctr = (ring_ctr + kPoolConvRows) % kRingRows;
+        }
+    }
+
+    if (*abort_ptr) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_ptr && p.status != nullptr) atomicExch(p.status, KXC_B200_ERR_DEVICE_WAIT);
+}
+
 // Stem weights in core-matrix order: [KH][4 k-chunks][64 cout][8] bf16, element e of chunk j = pixel 2j + e/4,
 // channel e%4; zero for kw >= KW or c >= C.
 __global__ void stem_pack_weights_core_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int O, int C,
@@ -259,6 +505,25 @@ int32_t stem_direct_setup(TcParams* p, const void* packed_in, const void* packed
     p->aux_hp = Hp;
     KXC_TRY(tc_status_word(&p->status));
     return KXC_B200_OK;
+}
+
+bool stem_pool_applicable(int OH, int OW, int pool_k, int pool_s, int pool_pad) {
+    return pool_k == 3 && pool_s == 2 && pool_pad == 1 && (OH % kStripRows) == 0 && (OW % 2) == 0 && OW <= 128;
+}
+
+int32_t stem_pool_launch(const TcParams& p, cudaStream_t stream) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(conv_stem_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPoolSmemBytes);
+    });
+    if (attr_err != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
+    if (!p.vec_ok || p.out == nullptr) return fail(KXC_B200_ERR_INVALID, "fused stem conv + pool: pointers must be 16-byte aligned");
+    const long long strips = (long long)(p.OH / kStripRows) * p.N;
+    if (strips <= 0) return KXC_B200_OK;
+    const int grid = (int)(strips < kNumSMs ? strips : kNumSMs);
+    conv_stem_pool_kernel<<<grid, kThreads, kPoolSmemBytes, stream>>>(p);
+    return check_launch("conv_stem_pool_kernel");
 }
 
 int32_t stem_direct_launch(const TcParams& p, cudaStream_t stream) {

@@ -11,5 +11,9 @@ size_t stem_direct_weight_bytes(int KH);
 int32_t stem_direct_pack_weights(const float* w, void* out, int O, int C, int KH, int KW, cudaStream_t s);
 int32_t stem_direct_setup(TcParams* p, const void* packed_in, const void* packed_w, int N, int OH, int OW, int KH, int Hp, int Wp);
 int32_t stem_direct_launch(const TcParams& p, cudaStream_t stream);
+// Fused variant: conv + bias + ReLU + max_pool2d(3x3, s2, p1); `p.out` is the POOLED bf16 NHWC tensor
+// [N, OH/2, OW/2, 64], p.OH / p.OW stay the convolution's output extent. Same setup as stem_direct_setup.
+bool stem_pool_applicable(int OH, int OW, int pool_k, int pool_s, int pool_pad);
+int32_t stem_pool_launch(const TcParams& p, cudaStream_t stream);
 
 }  // namespace kxc_b200

@@ -82,7 +82,8 @@ struct Step {
     int bias_const = -1;  // constant value id (fp32 user pointer), -1 = none
     bool relu = false;
     bool out_is_graph_output = false;
-    int direct = 0;  // 0 = implicit-GEMM kernel; 1 = direct 3x3 kernel (resident weights, one halo load per tile)
+    int direct = 0;  // 0 = implicit-GEMM kernel; 1 = direct 3x3 kernel; 2 = direct stem kernel
+    int fused_pool = 0;  // direct stem kernel only: the following max_pool2d(3x3, s2, p1) is computed in its epilogue
     // conv / gemm
     TcParams params{};
     TcConfig cfg{};
@@ -117,6 +118,15 @@ struct kxc_b200_plan {
     size_t arena_bytes = 0;
     void* weight_arena = nullptr;
     int device = -1;
+    // KXC_B200_PREC_FP32 plans: reference-layout (NCHW fp32) values, CUDA-core kernels in the reference's
+    // operation order, bit-exact end to end (see the "exact mode" section at the end of this file)
+    struct XStep {
+        std::string op;
+        int in0 = -1, in1 = -1, weight = -1, bias = -1, out = -1;
+        bool relu = false;
+        int node = -1;
+    };
+    std::vector<XStep> xsteps;
     // optional CUDA-graph replay of one run (launch-bound small batches): the graph captured for a given
     // packed-argument list is replayed while the caller keeps passing the same pointers
     bool use_graph = false;
@@ -258,10 +268,13 @@ int32_t setup_stem(kxc_b200_plan* pl, Step& st, int N, int C, int H, int W, int 
 
 }  // namespace
 
+static int32_t finalize_exact(kxc_b200_plan* pl);
+static int32_t run_exact(kxc_b200_plan* pl, void** packed_args, void* stream, cudaEvent_t* events);
+
 extern "C" int32_t kxc_b200_plan_create(int32_t precision, kxc_b200_plan** out) {
     if (!out) return fail(KXC_B200_ERR_INVALID, "plan_create: null out pointer");
-    if (precision != KXC_B200_PREC_BF16 && precision != KXC_B200_PREC_TF32)
-        return fail(KXC_B200_ERR_UNSUPPORTED, "plan_create: precision must be KXC_B200_PREC_BF16 or KXC_B200_PREC_TF32");
+    if (precision != KXC_B200_PREC_BF16 && precision != KXC_B200_PREC_TF32 && precision != KXC_B200_PREC_FP32)
+        return fail(KXC_B200_ERR_UNSUPPORTED, "plan_create: precision must be KXC_B200_PREC_BF16, _TF32 or _FP32");
     auto* pl = new (std::nothrow) kxc_b200_plan();
     if (!pl) return fail(KXC_B200_ERR_NOMEM, "plan_create: out of host memory");
     pl->precision = precision;
@@ -353,6 +366,7 @@ extern "C" int32_t kxc_b200_plan_value_shape(kxc_b200_plan* plan, int32_t value_
 
 extern "C" int32_t kxc_b200_plan_num_launches(kxc_b200_plan* plan) {
     if (!plan || !plan->finalized) return -KXC_B200_ERR_INVALID;
+    if (plan->precision == KXC_B200_PREC_FP32) return (int32_t)plan->xsteps.size();
     return (int32_t)plan->steps.size();
 }
 
@@ -364,6 +378,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
     KXC_TRY(infer_shapes(pl));
     if (!pl->find(pl->output_id)->consumers.empty())
         return fail(KXC_B200_ERR_UNSUPPORTED, "plan_finalize: the output value must not feed other kernels");
+    if (pl->precision == KXC_B200_PREC_FP32) return finalize_exact(pl);
     KXC_CUDA_TRY(cudaGetDevice(&pl->device));
     const TcDType dt = pl->dtype;
     const int eb = pl->eb();
@@ -409,8 +424,32 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
                 cur = pl->nodes[c].out;
                 emit_at = c;
             }
-            st.out = cur;
             st.N = (int)data->shape[0]; st.C = (int)data->shape[1]; st.H = (int)data->shape[2]; st.W = (int)data->shape[3];
+            {   // stem conv -> relu -> max_pool2d(3x3, s2, p1): pool inside the direct stem kernel's epilogue
+                const int pc = sole_consumer(pl, cur);
+                const char* e1 = getenv("KXC_B200_STEM_DIRECT");
+                const char* e2 = getenv("KXC_B200_STEM_POOL_FUSE");  // "0" keeps the separate pooling kernel
+                if (pc >= 0 && pl->nodes[pc].op == "nn_max_pool2d" && !pl->nodes[pc].fused_into_other && st.relu && st.in1 < 0 &&
+                    is_input(n.in[0]) && pl->nodes[pc].out != pl->output_id && (!e1 || atoi(e1) != 0) && (!e2 || atoi(e2) != 0) &&
+                    n.conv.strides[0] == 2 && n.conv.strides[1] == 2 && n.conv.dilation[0] == 1 && n.conv.dilation[1] == 1) {
+                    const auto& pa = pl->nodes[pc].pool;
+                    const int KHc = (int)w->shape[2], KWc = (int)w->shape[3];
+                    const int OHc = (int)conv_out_dim(st.H, KHc, 2, n.conv.padding[0], 1);
+                    const int OWc = (int)conv_out_dim(st.W, KWc, 2, n.conv.padding[1], 1);
+                    const int Wpc = (std::max(st.W + 2 * n.conv.padding[1], 2 * (OWc - 1) + 8) + 3) / 4 * 4;
+                    const bool pool_ok = pa.pool_size[0] == 3 && pa.pool_size[1] == 3 && pa.strides[0] == 2 && pa.strides[1] == 2 &&
+                                         pa.padding[0] == 1 && pa.padding[1] == 1 && pa.padding[2] == 1 && pa.padding[3] == 1 &&
+                                         pa.ceil_mode == 0;
+                    if (pool_ok && st.C <= 4 && KWc <= 8 && st.W >= 8 &&
+                        stem_direct_applicable(dt, st.C, (int)w->shape[0], KHc, KWc, OWc, Wpc) && stem_pool_applicable(OHc, OWc, 3, 2, 1)) {
+                        st.fused_pool = 1;
+                        pl->nodes[pc].fused_into_other = true;
+                        cur = pl->nodes[pc].out;
+                        emit_at = pc;
+                    }
+                }
+            }
+            st.out = cur;
             st.pool = {};  // unused
             // weight record
             PackedWeight pw;
@@ -666,10 +705,11 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
         if (st.kind == SKind::Conv) {
             PackedWeight& pw = pl->weights[st.weight];
             Value* ov = pl->find(st.out);
+            const int stem_oh = (int)conv_out_dim(st.H, pw.KH, 2, st.pad_h, 1), stem_ow = (int)conv_out_dim(st.W, pw.KW, 2, st.pad_w, 1);
             if (pw.mode == 1 && !st.out_is_graph_output) {
                 // the direct stem kernel writes bf16 NHWC only; its packed weights take the same number of bytes
                 const char* e = getenv("KXC_B200_STEM_DIRECT");  // "0" keeps the implicit-GEMM stem for A/B runs
-                if ((!e || atoi(e) != 0) && stem_direct_applicable(dt, st.C, pw.O, pw.KH, pw.KW, (int)ov->shape[3], st.Wp) &&
+                if ((!e || atoi(e) != 0) && stem_direct_applicable(dt, st.C, pw.O, pw.KH, pw.KW, stem_ow, st.Wp) &&
                     stem_direct_weight_bytes(pw.KH) <= pw.bytes)
                     pw.mode = 4;
             }
@@ -678,10 +718,10 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
                 return fail(KXC_B200_ERR_UNSUPPORTED, "plan: a residual convolution cannot be the graph output");
             if (!st.out_is_graph_output && (pw.O % lanes))
                 return fail(KXC_B200_ERR_UNSUPPORTED, "plan: %d output channels must be a multiple of %d", pw.O, lanes);
+            if (st.fused_pool && pw.mode != 4) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: fused stem pooling needs the direct stem kernel");
             if (pw.mode == 4) {
                 st.direct = 2;
-                KXC_TRY(stem_direct_setup(&st.params, pl->storage(st.in0), pw.ptr, st.N, (int)ov->shape[2], (int)ov->shape[3], pw.KH,
-                                          st.Hp, st.Wp));
+                KXC_TRY(stem_direct_setup(&st.params, pl->storage(st.in0), pw.ptr, st.N, stem_oh, stem_ow, pw.KH, st.Hp, st.Wp));
                 st.cfg = TcConfig{dt, 64, 64, om};
             } else if (pw.mode == 1) {
                 KXC_TRY(setup_stem(pl, st, st.N, st.C, st.H, st.W, pw.O, pw.KH, pw.KW, st.pad_h, st.pad_w, pl->storage(st.in0), pw.ptr, om));
@@ -723,6 +763,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
 
 static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream, cudaEvent_t* events) {
     if (!pl || !pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_run: plan is not finalized");
+    if (pl->precision == KXC_B200_PREC_FP32) return run_exact(pl, packed_args, stream, events);
     if (!packed_args) return fail(KXC_B200_ERR_INVALID, "plan_run: null packed_args");
     KXC_TRY(require_device());
     int dev = -1;
@@ -770,7 +811,7 @@ static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream
                 if (st.out_is_graph_output) p.out = out_ptr;
                 tc_finish_params(&p);
                 if (st.direct == 2) {
-                    KXC_TRY(stem_direct_launch(p, s));
+                    KXC_TRY(st.fused_pool ? stem_pool_launch(p, s) : stem_direct_launch(p, s));
                 } else if (st.direct == 1) {
                     KXC_TRY(direct3x3_launch(p, s));
                 } else {
@@ -848,7 +889,7 @@ extern "C" int32_t kxc_b200_plan_run(kxc_b200_plan* pl, void** packed_args, void
 extern "C" int32_t kxc_b200_plan_run_timed(kxc_b200_plan* pl, void** packed_args, void* stream, float* launch_ms,
                                            int32_t capacity) {
     if (!pl || !pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_run_timed: plan is not finalized");
-    const int n = (int)pl->steps.size();
+    const int n = pl->precision == KXC_B200_PREC_FP32 ? (int)pl->xsteps.size() : (int)pl->steps.size();
     if (!launch_ms || capacity < n) return fail(KXC_B200_ERR_INVALID, "plan_run_timed: need room for %d durations", n);
     std::vector<cudaEvent_t> ev(n + 1);
     for (auto& e : ev) KXC_CUDA_TRY(cudaEventCreate(&e));
@@ -882,6 +923,20 @@ const char* step_kind_name(SKind k) {
 
 extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, char* name, int32_t name_size,
                                              double* flops, double* bytes) {
+    if (pl && pl->finalized && pl->precision == KXC_B200_PREC_FP32) {
+        if (index < 0 || index >= (int)pl->xsteps.size()) return fail(KXC_B200_ERR_INVALID, "plan_launch_info: bad index");
+        const auto& xs = pl->xsteps[index];
+        double fl = 0.0;
+        if (xs.op == "nn_conv2d") {
+            const auto& o = pl->find(xs.out)->shape;
+            const auto& w = pl->find(xs.weight)->shape;
+            fl = 2.0 * (double)numel_of(o) * (double)(w[1] * w[2] * w[3]);
+        }
+        if (name && name_size > 0) snprintf(name, (size_t)name_size, "%s (fp32, reference order)%s", xs.op.c_str(), xs.relu ? " +relu" : "");
+        if (flops) *flops = fl;
+        if (bytes) *bytes = 0.0;
+        return KXC_B200_OK;
+    }
     if (!pl || !pl->finalized || index < 0 || index >= (int)pl->steps.size())
         return fail(KXC_B200_ERR_INVALID, "plan_launch_info: bad plan or index");
     const Step& st = pl->steps[index];
@@ -895,8 +950,9 @@ extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, c
             const double out_elems = (double)p.N * p.OH * p.OW * w.O;
             fl = 2.0 * out_elems * w.C * w.KH * w.KW;  // padded taps counted, as the reference executes them
             const double in_bytes = (w.mode == 1 || w.mode == 4) ? (double)st.N * st.Hp * st.Wp * 4 * eb : (double)st.N * st.H * st.W * st.cpad * eb;
-            by = in_bytes + (double)w.bytes + out_elems * (st.out_is_graph_output ? 4.0 : eb) + (st.in1 >= 0 ? out_elems * eb : 0.0) + 4.0 * w.O;
-            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d", st.direct == 2 ? "conv_stem_direct" : (st.direct ? "conv_direct" : "conv_igemm"), w.C, st.H, st.W, w.O, w.KH, w.KW,
+            by = in_bytes + (double)w.bytes + out_elems * (st.fused_pool ? 0.25 : 1.0) * (st.out_is_graph_output ? 4.0 : eb) +
+                 (st.in1 >= 0 ? out_elems * eb : 0.0) + 4.0 * w.O;
+            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d", st.direct == 2 ? (st.fused_pool ? "conv_stem_pool" : "conv_stem_direct") : (st.direct ? "conv_direct" : "conv_igemm"), w.C, st.H, st.W, w.O, w.KH, w.KW,
                      p.stride, st.in1 >= 0 ? " +res" : "", st.relu ? " +relu" : "", p.BNI, p.BH, p.BW, st.cfg.bn);
             break;
         }
@@ -936,5 +992,148 @@ extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, c
     if (name && name_size > 0) snprintf(name, (size_t)name_size, "%s", buf);
     if (flops) *flops = fl;
     if (bytes) *bytes = by;
+    return KXC_B200_OK;
+}
+
+// ---- exact mode (KXC_B200_PREC_FP32) -------------------------------------------------------------
+// Values keep the reference's own layout (NCHW / row-major fp32), so graph inputs, constants and the
+// output are used in place and nn_flatten is always a view. Every kernel is one of the bit-exact ones
+// (reference reduction order, separately rounded multiply and add); the fused epilogue performs the
+// same three IEEE operations, in the same order, that the reference's three loop nests perform. A whole
+// graph therefore reproduces the reference's CPU lowering bit for bit.
+static int32_t finalize_exact(kxc_b200_plan* pl) {
+    KXC_CUDA_TRY(cudaGetDevice(&pl->device));
+    pl->dtype = kTcTF32;  // 4-byte elements; no rounding kernel is used in this mode
+    for (size_t ni = 0; ni < pl->nodes.size(); ++ni) {
+        Node& n = pl->nodes[ni];
+        if (n.fused_into_other) continue;
+        kxc_b200_plan::XStep xs;
+        xs.op = n.op;
+        xs.node = (int)ni;
+        xs.in0 = n.in[0];
+        int cur = n.out;
+        if (n.op == "nn_conv2d") {
+            xs.weight = n.in[1];
+            xs.bias = n.in.size() == 3 ? n.in[2] : -1;
+            int c = sole_consumer(pl, cur);
+            if (c >= 0 && pl->nodes[c].op == "add" && !pl->nodes[c].fused_into_other) {
+                Node& a = pl->nodes[c];
+                const int other = a.in[0] == cur ? a.in[1] : a.in[0];
+                Value* ov = pl->find(other);
+                // the residual must already exist when this convolution runs
+                if (other != cur && (ov->kind != VKind::Intermediate || ov->producer < (int)ni) && ov->shape == pl->find(cur)->shape) {
+                    xs.in1 = other;
+                    a.fused_into_other = true;
+                    cur = a.out;
+                    c = sole_consumer(pl, cur);
+                }
+            }
+            if (c >= 0 && pl->nodes[c].op == "nn_relu" && !pl->nodes[c].fused_into_other) {
+                xs.relu = true;
+                pl->nodes[c].fused_into_other = true;
+                cur = pl->nodes[c].out;
+            }
+        } else if (n.op == "add") {
+            xs.in1 = n.in[1];
+            const int c = sole_consumer(pl, cur);
+            if (c >= 0 && pl->nodes[c].op == "nn_relu" && !pl->nodes[c].fused_into_other) {
+                xs.relu = true;
+                pl->nodes[c].fused_into_other = true;
+                cur = pl->nodes[c].out;
+            }
+        } else if (n.op == "nn_dense" || n.op == "nn_gemm") {
+            xs.weight = n.in[1];
+            xs.bias = n.op == "nn_gemm" ? n.in[2] : -1;
+        } else if (n.op == "nn_flatten") {
+            if (n.out != pl->output_id) {
+                pl->find(n.out)->alias_of = n.in[0];
+                continue;
+            }
+        }
+        xs.out = cur;
+        pl->xsteps.push_back(xs);
+    }
+    // storage: one arena block per materialised intermediate (no reuse: sizes are modest in this mode)
+    size_t top = 0;
+    for (auto& xs : pl->xsteps) {
+        if (pl->root_of(xs.out) == pl->root_of(pl->output_id)) continue;
+        Value* v = pl->find(xs.out);
+        v->offset = top;
+        v->bytes = align_up(std::max<size_t>((size_t)numel_of(v->shape) * 4, 16), 1024);
+        v->has_storage = true;
+        top += v->bytes;
+    }
+    pl->arena_bytes = std::max<size_t>(top, 1024);
+    KXC_CUDA_TRY(cudaMalloc(&pl->arena, pl->arena_bytes));
+    pl->finalized = true;
+    return KXC_B200_OK;
+}
+
+static int32_t run_exact(kxc_b200_plan* pl, void** packed_args, void* stream, cudaEvent_t* events) {
+    if (!packed_args) return fail(KXC_B200_ERR_INVALID, "plan_run: null packed_args");
+    KXC_TRY(require_device());
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t nargs = pl->inputs.size() + pl->constants.size();
+    for (size_t i = 0; i <= nargs; ++i)
+        if (!packed_args[i]) return fail(KXC_B200_ERR_INVALID, "plan_run: packed_args[%zu] is null", i);
+    void* out_ptr = packed_args[nargs];
+    auto ptr_of = [&](int id) -> void* {
+        if (id < 0) return nullptr;
+        const int root = pl->root_of(id);
+        Value* v = pl->find(root);
+        if (v->kind != VKind::Intermediate) return packed_args[v->arg_index];
+        if (root == pl->root_of(pl->output_id)) return out_ptr;
+        return static_cast<uint8_t*>(pl->arena) + v->offset;
+    };
+    size_t idx = 0;
+    if (events) KXC_CUDA_TRY(cudaEventRecord(events[0], s));
+    for (auto& xs : pl->xsteps) {
+        if (idx > 0 && events) KXC_CUDA_TRY(cudaEventRecord(events[idx], s));
+        ++idx;
+        const Node& n = pl->nodes[xs.node];
+        const auto& ish = pl->find(xs.in0)->shape;
+        const auto& osh = pl->find(xs.out)->shape;
+        if (xs.op == "nn_conv2d") {
+            const auto& w = pl->find(xs.weight)->shape;
+            ConvDims d{(int)ish[0], (int)ish[1], (int)ish[2], (int)ish[3], (int)w[0], (int)w[2], (int)w[3],
+                       n.conv.strides[0], n.conv.strides[1], n.conv.padding[0], n.conv.padding[1], n.conv.dilation[0],
+                       n.conv.dilation[1], (int)osh[2], (int)osh[3]};
+            KXC_TRY(conv2d_fp32_exact(static_cast<const float*>(ptr_of(xs.in0)), static_cast<const float*>(ptr_of(xs.weight)),
+                                      static_cast<const float*>(ptr_of(xs.bias)), static_cast<const float*>(ptr_of(xs.in1)),
+                                      static_cast<float*>(ptr_of(xs.out)), d, xs.relu ? 1 : 0, s));
+        } else if (xs.op == "add") {
+            kxc_b200_add_desc d{};
+            const auto& bsh = pl->find(xs.in1)->shape;
+            d.rank_a = (int)ish.size(); d.rank_b = (int)bsh.size(); d.relu = xs.relu ? 1 : 0;
+            for (size_t i = 0; i < ish.size(); ++i) d.shape_a[i] = ish[i];
+            for (size_t i = 0; i < bsh.size(); ++i) d.shape_b[i] = bsh[i];
+            void* a[3] = {ptr_of(xs.in0), ptr_of(xs.in1), ptr_of(xs.out)};
+            KXC_TRY(kxc_b200_add(a, &d, stream));
+        } else if (xs.op == "nn_relu") {
+            void* a[2] = {ptr_of(xs.in0), ptr_of(xs.out)};
+            KXC_TRY(kxc_b200_nn_relu(a, numel_of(osh), stream));
+        } else if (xs.op == "nn_max_pool2d") {
+            const auto& pa = n.pool;
+            kxc_b200_pool2d_desc d{(int)ish[0], (int)ish[1], (int)ish[2], (int)ish[3], pa.pool_size[0], pa.pool_size[1], pa.strides[0],
+                                   pa.strides[1], pa.padding[0], pa.padding[1], pa.padding[2], pa.padding[3], pa.ceil_mode};
+            void* a[2] = {ptr_of(xs.in0), ptr_of(xs.out)};
+            KXC_TRY(kxc_b200_nn_max_pool2d(a, &d, stream));
+        } else if (xs.op == "nn_global_avg_pool2d") {
+            void* a[2] = {ptr_of(xs.in0), ptr_of(xs.out)};
+            KXC_TRY(kxc_b200_nn_global_avg_pool2d(a, (int)ish[0], (int)ish[1], (int)ish[2], (int)ish[3], stream));
+        } else if (xs.op == "nn_flatten") {
+            void* a[2] = {ptr_of(xs.in0), ptr_of(xs.out)};
+            KXC_TRY(kxc_b200_nn_flatten(a, numel_of(osh), stream));
+        } else if (xs.op == "nn_dense" || xs.op == "nn_gemm") {
+            const bool gemm = xs.op == "nn_gemm";
+            kxc_b200_gemm_desc g{(int)ish[0], (int)osh[1], (int)ish[1], gemm ? n.gemm.alpha : 1.0f, gemm ? n.gemm.beta : 1.0f, 0,
+                                 gemm ? n.gemm.transB : 1, gemm ? 1 : 0, KXC_B200_PREC_FP32};
+            KXC_TRY(gemm_fp32_exact(static_cast<const float*>(ptr_of(xs.in0)), static_cast<const float*>(ptr_of(xs.weight)),
+                                    static_cast<const float*>(ptr_of(xs.bias)), static_cast<float*>(ptr_of(xs.out)), g, s));
+        } else {
+            return fail(KXC_B200_ERR_UNSUPPORTED, "plan: op '%s' is not supported", xs.op.c_str());
+        }
+    }
+    if (events) KXC_CUDA_TRY(cudaEventRecord(events[idx], s));
     return KXC_B200_OK;
 }

@@ -9,9 +9,9 @@ import ctypes
 import torch
 
 from . import _lib, relay
-from ._lib import PREC_BF16, PREC_TF32, check, i32, i64, load, packed, vp, vpp
+from ._lib import PREC_BF16, PREC_FP32, PREC_TF32, check, i32, i64, load, packed, vp, vpp
 
-PRECISIONS = {"bf16": PREC_BF16, "tf32": PREC_TF32}
+PRECISIONS = {"bf16": PREC_BF16, "tf32": PREC_TF32, "fp32": PREC_FP32}
 
 
 class Conv2dAttrsC(ctypes.Structure):

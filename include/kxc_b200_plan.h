@@ -49,8 +49,10 @@ typedef struct kxc_b200_gemm_attrs {
     int32_t transA, transB;
 } kxc_b200_gemm_attrs;
 
-/* precision: KXC_B200_PREC_BF16 (bf16 activations/weights, fp32 accumulate) or KXC_B200_PREC_TF32
- * (fp32 activations, tf32-rounded operands, fp32 accumulate). */
+/* precision: KXC_B200_PREC_BF16 (bf16 activations/weights, fp32 accumulate), KXC_B200_PREC_TF32 (fp32
+ * activations, tf32-rounded operands, fp32 accumulate) — both on the tensor cores — or KXC_B200_PREC_FP32:
+ * CUDA-core kernels in the reference's operation order on NCHW fp32 values, bit-identical to the reference's
+ * CPU lowering of the same graph. */
 int32_t kxc_b200_plan_create(int32_t precision, kxc_b200_plan** out);
 int32_t kxc_b200_plan_destroy(kxc_b200_plan* plan);
 

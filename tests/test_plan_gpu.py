@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import assert_close, ref_metric
+from conftest import assert_bit_exact, assert_close, ref_metric
 from oracle import graph as ograph
 from oracle import port
 
@@ -109,6 +109,24 @@ def test_single_conv_plan_matches_per_op(kxc, rng):
     assert np.abs(got - exp).max() <= 2e-4
 
 
+def test_fp32_plan_is_bit_exact(kxc, rng):
+    """KXC_B200_PREC_FP32 plans reproduce the reference arithmetic bit for bit: small CNN and full ResNet-18."""
+    func = small_cnn(kxc, rng)
+    x = rng.normal(0, 1, (3, 8, 20, 20)).astype(f32)
+    got, g = run_plan(kxc, func, x, "fp32")
+    assert_bit_exact(got, ograph.run(host_func(func), [x]), "small cnn fp32 plan")
+    assert g.num_launches == 6  # 3 fused convs, pool, gap, gemm (flatten is a view)
+
+    rs = kxc.resnet18
+    weights = rs.make_weights(seed=0)
+    N = 2
+    xr = np.random.default_rng(7).normal(0, 1, (N, 3, 224, 224)).astype(f32)
+    got, g = run_plan(kxc, rs.build(N, weights, to_constant=cuda_const), xr, "fp32")
+    exact = ograph.run(rs.build(N, weights), [xr], workers=8)
+    assert_bit_exact(got, exact, "resnet18 fp32 plan")
+    assert g.num_launches == 23  # 20 fused convs, max pool, gap, gemm
+
+
 def test_plan_cuda_graph_replay_matches_eager(kxc, rng):
     func = small_cnn(kxc, rng)
     x1 = rng.normal(0, 1, (3, 8, 20, 20)).astype(f32)
@@ -154,7 +172,8 @@ def test_resnet18_plan(kxc, precision):
     func = rs.build(N, weights, to_constant=cuda_const)
     got, g = run_plan(kxc, func, x, precision)
     assert got.shape == (N, 1000)
-    assert g.num_launches == 24  # stem pack + 20 fused convs + maxpool + gap + dense; flatten is a view
+    # stem pack + 20 fused convs (the stem one also does the max pool in bf16 mode) + gap + dense; flatten is a view
+    assert g.num_launches == (23 if precision == "bf16" else 24)
     hf = rs.build(N, weights)
     exact = ograph.run(hf, [x], workers=8)
     scale = float(np.abs(exact).max())
@@ -174,6 +193,35 @@ def test_resnet18_plan(kxc, precision):
     e_abs, _ = ref_metric(got, emu)
     print(f"resnet18 {precision}: vs same-rounding oracle max_abs={e_abs:.3e} normalised={e_abs / scale:.3e}")
     assert e_abs / scale <= (1e-2 if precision == "bf16" else 1e-3)
+
+
+def test_stem_pool_fusion_is_bit_identical(kxc, monkeypatch):
+    """stem conv -> relu -> max_pool2d fused into one kernel gives the same bits as conv kernel + pool kernel,
+    and both match the oracle on identically rounded operands."""
+    rs, R = kxc.resnet18, kxc.relay
+    weights = dict(rs.make_weights(seed=0))
+    N = 3
+    x = np.random.default_rng(12).normal(0, 1, (N, 3, 224, 224)).astype(f32)
+    w, b = weights["conv1.weight"], weights["conv1.bias"]
+
+    def build():
+        xv = R.Var("input", x.shape)
+        y = R.Call("nn_relu", [R.Call("nn_conv2d", [xv, R.Constant(cuda_const(w)), R.Constant(cuda_const(b))],
+                                      R.Conv2DAttrs((2, 2), (3, 3, 3, 3), (1, 1), 1))])
+        y = R.Call("nn_max_pool2d", [y], R.MaxPool2DAttrs((2, 2), (1, 1, 1, 1), (1, 1), (3, 3), "NCHW", False))
+        return R.Function([xv], R.Call("nn_relu", [y]))  # a trailing op so that the pool is not the graph output
+
+    monkeypatch.setenv("KXC_B200_STEM_POOL_FUSE", "1")
+    fused, gf = run_plan(kxc, build(), x, "bf16")
+    monkeypatch.setenv("KXC_B200_STEM_POOL_FUSE", "0")
+    unfused, gu = run_plan(kxc, build(), x, "bf16")
+    assert gf.num_launches == gu.num_launches - 1
+    assert any("conv_stem_pool" in l[0] for l in gf.launch_info())
+    assert np.array_equal(fused, unfused)
+    conv = port.round_bf16(port.relu(port.conv2d(port.round_bf16(x), port.round_bf16(w), b, (2, 2), (3, 3))))
+    exp = port.relu(port.max_pool2d(conv, (3, 3), (2, 2), (1, 1, 1, 1)))
+    # pooling picks stored bf16 values: only where the fp32 sums straddle a bf16 rounding boundary can a value differ
+    assert np.mean(fused != exp) < 1e-3 and np.abs(fused - exp).max() <= 2.0 ** -7 * np.abs(exp).max()
 
 
 @pytest.mark.parametrize("precision", ["bf16", "tf32"])
