@@ -38,31 +38,23 @@ constexpr int kHaloW = 16, kHaloH = kTileH + 2;
 constexpr int kHaloBytes = kHaloH * kHaloW * 128;  // 36864
 constexpr int kWeightBytes = kTaps * kBN * 128;    // 73728
 constexpr int kStages = 4;
+constexpr int kAccs = 4;               // TMEM accumulators: two tiles in flight on the tensor core + two being drained
 constexpr int kSmemBytes = kWeightBytes + kStages * kHaloBytes + 1024;
 
-// SWIZZLE_128B K-major descriptor with an explicit 8-row-group stride. The descriptor's base-offset field
-// stays 0 even when `addr` is not 1024-byte aligned: measured on B200, the swizzle phase the MMA applies
-// comes from the shared-memory address itself (a non-zero base offset for the shifted views gives wrong sums).
-__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t addr, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3ffff) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(sbo_bytes >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)kLayoutSw128 << 61;
-    return d;
-}
-
+// Descriptors: SWIZZLE_128B, K-major, explicit 8-row-group stride (2048 B for the halo views, 1024 B for the
+// weights). The descriptor's base-offset field stays 0 even when a view's start address is not 1024-byte aligned:
+// measured on B200, the swizzle phase the MMA applies comes from the shared-memory address itself (a non-zero
+// base offset for the shifted views gives wrong sums).
 __global__ void __launch_bounds__(kThreads, 1) conv3x3_direct_kernel(const __grid_constant__ TcParams p) {
-    constexpr uint32_t kTmemCols = 2 * kBN;
+    constexpr uint32_t kTmemCols = kAccs * kBN;
     constexpr uint32_t kIdesc = make_instr_desc(kFmtBF16, kAccF32, kBN);
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_w;
     __shared__ __align__(8) uint64_t bar_full[kStages];
     __shared__ __align__(8) uint64_t bar_empty[kStages];
-    __shared__ __align__(8) uint64_t bar_acc_full[2];
-    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ __align__(8) uint64_t bar_acc_full[kAccs];
+    __shared__ __align__(8) uint64_t bar_acc_empty[kAccs];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -78,7 +70,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_direct_kernel(const __gri
             mbar_init(smem_u32(&bar_full[s]), 1);
             mbar_init(smem_u32(&bar_empty[s]), 1);
         }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < kAccs; ++a) {
             mbar_init(smem_u32(&bar_acc_full[a]), 1);
             mbar_init(smem_u32(&bar_acc_empty[a]), 8);
         }
@@ -120,34 +112,58 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_direct_kernel(const __gri
     } else if (warp == 1) {
         if (lane == 0) {
             bool ok = mbar_wait_bounded(smem_u32(&bar_w), 0, abort_ptr);
+            const uint32_t a_hi = desc_hi(kHaloW * 128, kLayoutSw128), b_hi = desc_hi(1024, kLayoutSw128);
+            const uint32_t b_lo0 = desc_lo(w_smem, 16);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            // Consecutive MMAs into ONE accumulator form a dependent chain, and at N = 64 the chain latency (about
+            // twice the 32-cycle issue interval) is what bounds the kernel. Two tiles are therefore processed
+            // together, their MMAs alternating between two accumulators; each tile still sees its own 36 MMAs in
+            // the same order, so the sums are unchanged.
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += 2 * gridDim.x) {
+                const bool pair = tile + (int)gridDim.x < total_tiles;
+                const int acc1 = (acc + 1) & (kAccs - 1);
+                const int stage1 = stage + 1 == kStages ? 0 : stage + 1;
+                const uint32_t phase1 = stage + 1 == kStages ? phase ^ 1u : phase;
+                const uint32_t acc_phase1 = acc1 == 0 ? acc_phase ^ 1u : acc_phase;
                 if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr)) break;
                 if (!mbar_wait_bounded(smem_u32(&bar_full[stage]), phase, abort_ptr)) break;
+                if (pair) {
+                    if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[acc1]), acc_phase1 ^ 1u, abort_ptr)) break;
+                    if (!mbar_wait_bounded(smem_u32(&bar_full[stage1]), phase1, abort_ptr)) break;
+                }
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kBN);
-                const uint32_t halo = halo_smem + stage * kHaloBytes;
+                const uint32_t d0 = tmem_base + (uint32_t)(acc * kBN), d1 = tmem_base + (uint32_t)(acc1 * kBN);
+                // descriptor low words: base of the halo stage / of the resident weights, plus compile-time offsets
+                const uint32_t a0 = desc_lo(halo_smem + stage * kHaloBytes, 16), a1 = desc_lo(halo_smem + stage1 * kHaloBytes, 16);
 #pragma unroll
                 for (int kh = 0; kh < 3; ++kh) {
 #pragma unroll
                     for (int kw = 0; kw < 3; ++kw) {
-                        const uint32_t a_addr = halo + (uint32_t)((kh * kHaloW + kw) * 128);
-                        const uint64_t a_desc = make_desc_sw128(a_addr, kHaloW * 128);
-                        const uint64_t b_desc = make_desc_sw128(w_smem + (uint32_t)((kh * 3 + kw) * (kBN * 128)), 1024);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            umma<MmaKind::F16>(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), kIdesc,
-                                               (kh | kw | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < 4; ++k) {
+                            const uint32_t a_off = (uint32_t)(((kh * kHaloW + kw) * 128 + k * 32) >> 4);
+                            const uint32_t b_lo = b_lo0 + (uint32_t)((((kh * 3 + kw) * (kBN * 128)) + k * 32) >> 4);
+                            const uint32_t accum = (kh | kw | k) != 0 ? 1u : 0u;
+                            umma_f16_split(d0, a0 + a_off, a_hi, b_lo, b_hi, kIdesc, accum);
+                            if (pair) umma_f16_split(d1, a1 + a_off, a_hi, b_lo, b_hi, kIdesc, accum);
+                        }
                     }
                 }
                 umma_commit(smem_u32(&bar_empty[stage]));
                 umma_commit(smem_u32(&bar_acc_full[acc]));
-                if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                acc ^= 1;
-                if (acc == 0) acc_phase ^= 1u;
+                if (pair) {
+                    umma_commit(smem_u32(&bar_empty[stage1]));
+                    umma_commit(smem_u32(&bar_acc_full[acc1]));
+                }
+                const int used = pair ? 2 : 1;
+                for (int u = 0; u < used; ++u) {
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    acc = (acc + 1) & (kAccs - 1);
+                    if (acc == 0) acc_phase ^= 1u;
+                }
             }
         }
     } else {
@@ -184,7 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_direct_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));  // accumulator is in registers now
             if (valid) epilogue_fast_bf16(p, v, c0, pix, res, has_res);
-            acc ^= 1;
+            acc = (acc + 1) & (kAccs - 1);
             if (acc == 0) acc_phase ^= 1u;
         }
     }

@@ -43,17 +43,8 @@ constexpr int kStages = 3;
 constexpr int kWeightBytes = kMaxKH * 4 * kBN * 16;   // 28672
 constexpr int kSmemBytes = kWeightBytes + kStages * kStripBytes + 1024;
 
-// Unswizzled K-major descriptor: rows 16 B apart inside a core matrix (fixed by the layout), K chunks
-// `lbo` apart, 8-row groups `sbo` apart.
-__device__ __forceinline__ uint64_t make_desc_none(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3ffff) >> 4);
-    d |= (uint64_t)(lbo_bytes >> 4) << 16;
-    d |= (uint64_t)(sbo_bytes >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    return d;  // layout type 0 = no swizzle
-}
-
+// Descriptors: unswizzled K-major — rows 16 B apart inside a core matrix (fixed by the layout), K chunks
+// `leading byte offset` apart (16 B for the overlapping input rows, 1024 B for the weights), 8-row groups 128 B apart.
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
                  "r"(bytes), "r"(bar)
@@ -139,6 +130,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __g
     } else if (warp == 1) {
         if (lane == 0) {
             bool ok = mbar_wait_bounded(smem_u32(&bar_w), 0, abort_ptr);
+            const uint32_t ab_hi = desc_hi(128, 0);  // unswizzled, 8-row groups 128 B apart (A and B alike)
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -153,15 +145,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __g
                     if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kBN);
+                    uint32_t a_lo = desc_lo(strip_base + (uint32_t)(2 * rr * row_bytes), 16);
+                    uint32_t b_lo = desc_lo(w_smem, kBN * 16);
                     for (int kh = 0; kh < KH; ++kh) {
-                        const uint32_t a_row = strip_base + (uint32_t)((2 * rr + kh) * row_bytes);
-                        const uint32_t b_tap = w_smem + (uint32_t)(kh * 4 * kBN * 16);
-#pragma unroll
-                        for (int m = 0; m < 2; ++m) {
-                            const uint64_t a_desc = make_desc_none(a_row + m * 32, 16, 128);
-                            const uint64_t b_desc = make_desc_none(b_tap + m * 2 * (kBN * 16), kBN * 16, 128);
-                            umma<MmaKind::F16>(d_tmem, a_desc, b_desc, kIdesc, (kh | m) != 0 ? 1u : 0u);
-                        }
+                        umma_f16_split(d_tmem, a_lo, ab_hi, b_lo, ab_hi, kIdesc, kh != 0 ? 1u : 0u);
+                        umma_f16_split(d_tmem, a_lo + 2u, ab_hi, b_lo + (uint32_t)((2 * kBN * 16) >> 4), ab_hi, kIdesc, 1u);
+                        a_lo += (uint32_t)(row_bytes >> 4);
+                        b_lo += (uint32_t)((4 * kBN * 16) >> 4);
                     }
                     umma_commit(smem_u32(&bar_acc_full[acc]));
                     acc ^= 1;
@@ -320,6 +310,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_pool_kernel(const __gri
     } else if (warp == 1) {
         if (lane == 0) {
             bool ok = mbar_wait_bounded(smem_u32(&bar_w), 0, abort_ptr);
+            const uint32_t ab_hi = desc_hi(128, 0);  // unswizzled, 8-row groups 128 B apart (A and B alike)
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -334,15 +325,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_pool_kernel(const __gri
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kBN);
                     const int in_row0 = s > 0 ? 2 * j : 2 * j - 2;  // local packed row of filter row 0
+                    uint32_t a_lo = desc_lo(strip_base + (uint32_t)(in_row0 * row_bytes), 16);
+                    uint32_t b_lo = desc_lo(w_smem, kBN * 16);
                     for (int kh = 0; kh < KH; ++kh) {
-                        const uint32_t a_row = strip_base + (uint32_t)((in_row0 + kh) * row_bytes);
-                        const uint32_t b_tap = w_smem + (uint32_t)(kh * 4 * kBN * 16);
-#pragma unroll
-                        for (int m = 0; m < 2; ++m) {
-                            const uint64_t a_desc = make_desc_none(a_row + m * 32, 16, 128);
-                            const uint64_t b_desc = make_desc_none(b_tap + m * 2 * (kBN * 16), kBN * 16, 128);
-                            umma<MmaKind::F16>(d_tmem, a_desc, b_desc, kIdesc, (kh | m) != 0 ? 1u : 0u);
-                        }
+                        umma_f16_split(d_tmem, a_lo, ab_hi, b_lo, ab_hi, kIdesc, kh != 0 ? 1u : 0u);
+                        umma_f16_split(d_tmem, a_lo + 2u, ab_hi, b_lo + (uint32_t)((2 * kBN * 16) >> 4), ab_hi, kIdesc, 1u);
+                        a_lo += (uint32_t)(row_bytes >> 4);
+                        b_lo += (uint32_t)((4 * kBN * 16) >> 4);
                     }
                     umma_commit(smem_u32(&bar_acc_full[acc]));
                     acc ^= 1;
@@ -413,37 +402,35 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_pool_kernel(const __gri
                 if ((j & 1) == 0 && j >= 2) {
                     epilogue_bar_sync();  // rows j-2, j-1, j are complete
                     const int ph = 4 * s + j / 2 - 1;
+                    // The ring holds post-ReLU values: never NaN (NaN > 0 is false, so ReLU maps it to +0), never
+                    // negative, never -0. On such values the reference's fold `m = (m > v) ? m : v` from -inf, with
+                    // -1e30 for padding, is exactly the numeric maximum of the in-bounds taps, in any order, so packed
+                    // bf16 max instructions give the identical bits.
                     for (int item = et; item < POW * 8; item += 256) {
                         const int pw = item >> 3, g = item & 7;
-                        float m[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) m[e] = -INFINITY;
+                        const __nv_bfloat162 ninf = __halves2bfloat162(__ushort_as_bfloat16(0xff80), __ushort_as_bfloat16(0xff80));
+                        __nv_bfloat162 m0 = ninf, m1 = ninf, m2 = ninf, m3 = ninf;
 #pragma unroll
                         for (int rh = 0; rh < 3; ++rh) {
                             const int lj = j - 2 + rh;
-                            const bool row_ok = !(s == 0 && lj == 0);  // conv row -1 is padding
-                            const uint32_t rslot = (ring_ctr + (uint32_t)lj) % kRingRows;
+                            if (s == 0 && lj == 0) continue;  // conv row -1 is padding
+                            const uint32_t rbase = ring_smem + ((ring_ctr + (uint32_t)lj) % kRingRows) * kRingRowBytes;
 #pragma unroll
                             for (int rw = 0; rw < 3; ++rw) {
                                 const int col = 2 * pw - 1 + rw;
-                                float t[8];
-                                if (row_ok && col >= 0 && col < p.OW) {
-                                    uint32_t w0, w1, w2, w3;
-                                    const uint32_t a = ring_smem + rslot * kRingRowBytes + (uint32_t)col * 128u +
-                                                       (((uint32_t)g ^ ((uint32_t)col & 7u)) * 16u);
-                                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(a));
-                                    t[0] = bf16_lo(w0); t[1] = bf16_hi(w0); t[2] = bf16_lo(w1); t[3] = bf16_hi(w1);
-                                    t[4] = bf16_lo(w2); t[5] = bf16_hi(w2); t[6] = bf16_lo(w3); t[7] = bf16_hi(w3);
-                                } else {
-#pragma unroll
-                                    for (int e = 0; e < 8; ++e) t[e] = -1e30f;
-                                }
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) m[e] = (m[e] > t[e]) ? m[e] : t[e];
+                                if (col < 0 || col >= p.OW) continue;
+                                uint32_t w0, w1, w2, w3;
+                                const uint32_t a = rbase + (uint32_t)col * 128u + (((uint32_t)g ^ ((uint32_t)col & 7u)) * 16u);
+                                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(a));
+                                m0 = __hmax2(m0, *reinterpret_cast<__nv_bfloat162*>(&w0));
+                                m1 = __hmax2(m1, *reinterpret_cast<__nv_bfloat162*>(&w1));
+                                m2 = __hmax2(m2, *reinterpret_cast<__nv_bfloat162*>(&w2));
+                                m3 = __hmax2(m3, *reinterpret_cast<__nv_bfloat162*>(&w3));
                             }
                         }
                         uint4 o;
-                        o.x = pack_bf16(m[0], m[1]); o.y = pack_bf16(m[2], m[3]); o.z = pack_bf16(m[4], m[5]); o.w = pack_bf16(m[6], m[7]);
+                        o.x = *reinterpret_cast<uint32_t*>(&m0); o.y = *reinterpret_cast<uint32_t*>(&m1);
+                        o.z = *reinterpret_cast<uint32_t*>(&m2); o.w = *reinterpret_cast<uint32_t*>(&m3);
                         *reinterpret_cast<uint4*>(pooled + ((((size_t)n * POH + ph) * POW + pw) * kBN) + g * 8) = o;
                     }
                 }
@@ -519,6 +506,7 @@ int32_t stem_pool_launch(const TcParams& p, cudaStream_t stream) {
     });
     if (attr_err != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
     if (!p.vec_ok || p.out == nullptr) return fail(KXC_B200_ERR_INVALID, "fused stem conv + pool: pointers must be 16-byte aligned");
+    if (!p.relu) return fail(KXC_B200_ERR_INVALID, "fused stem conv + pool: the pooling shortcut relies on the ReLU in between");
     const long long strips = (long long)(p.OH / kStripRows) * p.N;
     if (strips <= 0) return KXC_B200_OK;
     const int grid = (int)(strips < kNumSMs ? strips : kNumSMs);
