@@ -219,4 +219,130 @@ __device__ __forceinline__ void epilogue_fast_bf16(const TcParams& p, const uint
     }
 }
 
+
+// ---- coalesced variant of the hot-path epilogue --------------------------------------------------
+// A thread owns one pixel's 32 channels (64 bytes); pixels of consecutive threads are Cout*2 bytes apart,
+// so a warp-wide 16-byte store of thread-owned data touches 32 different lines with 16 bytes each. The
+// request rate of such stores (and of the matching residual loads) is what bounds the epilogue. Here the
+// chunk passes through a per-warp staging tile in shared memory (32 rows x 64 B): global accesses are issued
+// "transposed" -- four neighbouring threads cover the 64 contiguous bytes of ONE pixel, a warp instruction
+// covers 8 pixels -- which divides the number of memory requests by four and writes whole 32-byte sectors.
+constexpr int kStageTileBytes = 32 * 64;  // 32-row staging tile (a 16-row tile is half of it)
+
+// byte offset of 16-byte piece `piece` (0..3) of row `row` (0..31) inside a staging tile; the XOR keeps both
+// the row-owner accesses and the transposed accesses free of bank conflicts
+__device__ __forceinline__ uint32_t stage_tile_off(int row, int piece) {
+    return (uint32_t)(row * 64 + ((piece ^ ((row >> 1) & 3)) << 4));
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
+// For the transposed accesses thread `lane` handles, in step j (0..3), piece (lane & 3) of row 8*j + (lane >> 2):
+// it needs those rows' pixel offsets and validity, which their owner threads hold.
+struct RowMap {
+    size_t pix[4];
+    uint32_t valid;  // bit j: row 8*j + (lane >> 2) is a real output pixel
+};
+__device__ __forceinline__ RowMap make_row_map(size_t pix, bool valid, int lane) {
+    RowMap m;
+    m.valid = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int src = 8 * j + (lane >> 2);
+        m.pix[j] = (size_t)__shfl_sync(0xffffffffu, (unsigned long long)pix, src);
+        m.valid |= (uint32_t)__shfl_sync(0xffffffffu, valid ? 1 : 0, src) << j;
+    }
+    return m;
+}
+// Residual pieces in the transposed arrangement (issued by the caller before it waits for the accumulator).
+__device__ __forceinline__ void residual_fetch_rows(const TcParams& p, const RowMap& m, int c0, int lane, uint4 (&res)[4]) {
+    const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.residual) + c0 + (lane & 3) * 8;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        res[j] = ((m.valid >> j) & 1u) ? __ldg(reinterpret_cast<const uint4*>(base + m.pix[j] * p.Cout)) : make_uint4(0, 0, 0, 0);
+}
+// Whole warp, converged. `tile` = shared-memory address of this warp's staging tile of kPassRows x 64 bytes.
+// kPassRows = 32: the warp's 32 rows pass through the tile at once; 16: in two halves (for kernels that can
+// spare only 1 KiB of shared memory per epilogue warp).
+template <int kPassRows>
+__device__ __forceinline__ void epilogue_coalesced_bf16(const TcParams& p, const uint32_t (&v)[32], int c0, uint32_t tile, int lane,
+                                                        const RowMap& m, const uint4 (&res)[4], bool has_res) {
+    static_assert(kPassRows == 32 || kPassRows == 16, "staging tile of 32 or 16 rows");
+    constexpr int kPasses = 32 / kPassRows;
+    constexpr int kSteps = 4 / kPasses;  // transposed steps (8 rows each) per pass
+    const int my_pass = lane / kPassRows;
+    const int my_row = lane % kPassRows;
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+    if (p.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + j));
+            f[j] = __fadd_rn(f[j], b.x);
+            f[j + 1] = __fadd_rn(f[j + 1], b.y);
+            f[j + 2] = __fadd_rn(f[j + 2], b.z);
+            f[j + 3] = __fadd_rn(f[j + 3], b.w);
+        }
+    }
+    if (has_res) {
+#pragma unroll
+        for (int h = 0; h < kPasses; ++h) {
+#pragma unroll
+            for (int js = 0; js < kSteps; ++js)
+                st_shared_v4(tile + stage_tile_off(8 * js + (lane >> 2), lane & 3), res[h * kSteps + js]);
+            __syncwarp();
+            if (kPasses == 1 || my_pass == h) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const uint4 r = ld_shared_v4(tile + stage_tile_off(my_row, g));
+                    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        f[g * 8 + 2 * k] = __fadd_rn(f[g * 8 + 2 * k], bf16_lo(w[k]));
+                        f[g * 8 + 2 * k + 1] = __fadd_rn(f[g * 8 + 2 * k + 1], bf16_hi(w[k]));
+                    }
+                }
+            }
+            // With one pass every thread next writes the row it has just read; with two, rows are shared
+            // between the halves of the warp, so the tile must be quiet before it is written again.
+            if (kPasses > 1) __syncwarp();
+        }
+    }
+    if (p.relu) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = f[j] > 0.0f ? f[j] : 0.0f;
+    }
+    uint4 o[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        o[g].x = pack_bf16(f[g * 8 + 0], f[g * 8 + 1]);
+        o[g].y = pack_bf16(f[g * 8 + 2], f[g * 8 + 3]);
+        o[g].z = pack_bf16(f[g * 8 + 4], f[g * 8 + 5]);
+        o[g].w = pack_bf16(f[g * 8 + 6], f[g * 8 + 7]);
+    }
+    __nv_bfloat16* base = static_cast<__nv_bfloat16*>(p.out) + c0 + (lane & 3) * 8;
+#pragma unroll
+    for (int h = 0; h < kPasses; ++h) {
+        if (kPasses == 1 || my_pass == h) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) st_shared_v4(tile + stage_tile_off(my_row, g), o[g]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int js = 0; js < kSteps; ++js) {
+            const int j = h * kSteps + js;
+            const uint4 q = ld_shared_v4(tile + stage_tile_off(8 * js + (lane >> 2), lane & 3));
+            if ((m.valid >> j) & 1u) *reinterpret_cast<uint4*>(base + m.pix[j] * p.Cout) = q;
+        }
+        __syncwarp();  // the tile may be overwritten (next pass / next chunk)
+    }
+}
+
 }  // namespace kxc_b200

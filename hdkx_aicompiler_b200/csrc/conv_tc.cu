@@ -18,6 +18,7 @@
 #include <cuda_bf16.h>
 #include <cudaTypedefs.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -32,24 +33,31 @@ using namespace sm100;
 constexpr int kTcThreads = 320;  // 2 control warps + 8 epilogue warps
 constexpr int kSmemLimit = 227 * 1024;
 
-template <int KB_BYTES, int BN>
+template <int KB_BYTES, int BN, int kCtas>
 struct StageGeom {
     static constexpr int kABytes = 128 * KB_BYTES;
-    static constexpr int kBBytes = BN * KB_BYTES;
+    static constexpr int kBBytes = (BN / kCtas) * KB_BYTES;  // a CTA of a pair holds half of the B tile's rows
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStagesRaw = (kSmemLimit - 2048) / kStageBytes;
+    static constexpr int kEpilogueBytes = 8 * kStageTileBytes;  // one staging tile per epilogue warp
+    static constexpr int kStagesRaw = (kSmemLimit - 2048 - kEpilogueBytes) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align the ring to 1024 B
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpilogueBytes + 1024;  // + slack to align the ring to 1024 B
 };
 
-template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode>
+// kCtas = 2: the CTAs of a cluster of two work as a pair on 256 output pixels x BN channels. Each loads its own
+// 128-pixel A tile and HALF of the B tile; the leader (cluster rank 0) issues tcgen05.mma.cta_group::2
+// (M = 256), which reads both CTAs' shared memory and writes each CTA's 128 rows into that CTA's TMEM.
+// Both CTAs' loads count on the leader's "full" barrier; commits arrive on both CTAs' barriers; the
+// peer's epilogue warps release accumulators on the leader's "accumulator empty" barrier.
+template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode, int kCtas>
 __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_constant__ TcParams p) {
-    using G = StageGeom<KB_BYTES, BN>;
+    using G = StageGeom<KB_BYTES, BN, kCtas>;
+    constexpr bool kPair = kCtas == 2;
     constexpr int kStages = G::kStages;
     constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators; 128, 256 or 512: a power of two
     constexpr uint32_t kIdesc =
         make_instr_desc(kKind == MmaKind::F16 ? kFmtBF16 : (kKind == MmaKind::TF32 ? kFmtTF32 : kFmtS8),
-                        kKind == MmaKind::I8 ? kAccS32 : kAccF32, BN);
+                        kKind == MmaKind::I8 ? kAccS32 : kAccF32, BN, 128u * kCtas);
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[kStages];
@@ -62,6 +70,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t cta_rank = kPair ? cluster_cta_rank() : 0u;
+    const bool leader = cta_rank == 0;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -71,22 +81,33 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&bar_acc_full[a]), 1);
-            mbar_init(smem_u32(&bar_acc_empty[a]), 8);  // one arrival per epilogue warp
+            mbar_init(smem_u32(&bar_acc_empty[a]), 8 * kCtas);  // one arrival per epilogue warp (of both CTAs)
         }
         mbar_fence_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
-        tmem_relinquish();
+        if constexpr (kPair) {
+            tmem_alloc_pair(smem_u32(&tmem_base_slot), kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abort_ptr = &abort_flag;
 
     const int num_kb = p.taps_h * p.taps_w * p.cblocks;
-    const int total_tiles = p.tiles_c * p.tiles_w * p.tiles_h * p.tiles_n;
+    // Work items: (channel tile, group of kCtas consecutive pixel tiles). A pair whose second pixel tile
+    // does not exist loads a box beyond the last image (all zeros) and stores nothing for it.
+    const int m_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
+    const int total_tiles = p.tiles_c * ((m_tiles + kCtas - 1) / kCtas);
+    const int first_tile = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int tile_step = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     const int rows_used = p.BW * p.BH * p.BNI;
 
     if (warp == 0) {
@@ -98,13 +119,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
                 int r = tile;
                 const int ct = r % p.tiles_c; r /= p.tiles_c;
+                r = r * kCtas + (int)cta_rank;
                 const int tw = r % p.tiles_w; r /= p.tiles_w;
                 const int th = r % p.tiles_h;
                 const int tn = r / p.tiles_h;
-                const int ow0 = tw * p.BW, oh0 = th * p.BH, n0 = tn * p.BNI, co0 = ct * BN;
+                const int ow0 = tw * p.BW, oh0 = th * p.BH, n0 = tn * p.BNI;
+                const int co0 = ct * BN + (int)cta_rank * (BN / kCtas);
                 int kb = 0;
                 for (int kh = 0; ok && kh < p.taps_h; ++kh) {
                     for (int kw = 0; ok && kw < p.taps_w; ++kw) {
@@ -124,9 +147,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                             }
                             const uint32_t full = smem_u32(&bar_full[stage]);
                             const uint32_t a_dst = ring + (uint32_t)stage * G::kStageBytes;
-                            mbar_arrive_expect_tx(full, tx_bytes);
-                            tma_load_4d(a_dst, &p.tmA[map], full, cb * p.kb_elems, cw, ch, n0);
-                            tma_load_2d(a_dst + G::kABytes, &p.tmB, full, kb * p.kb_elems, co0);
+                            if constexpr (kPair) {
+                                if (leader) mbar_arrive_expect_tx(full, 2u * tx_bytes);
+                                const uint32_t full0 = map_to_cta(full, 0);
+                                tma_load_4d_pair(a_dst, &p.tmA[map], full0, cb * p.kb_elems, cw, ch, n0);
+                                tma_load_2d_pair(a_dst + G::kABytes, &p.tmB, full0, kb * p.kb_elems, co0);
+                            } else {
+                                mbar_arrive_expect_tx(full, tx_bytes);
+                                tma_load_4d(a_dst, &p.tmA[map], full, cb * p.kb_elems, cw, ch, n0);
+                                tma_load_2d(a_dst + G::kABytes, &p.tmB, full, kb * p.kb_elems, co0);
+                            }
                             if (++stage == kStages) { stage = 0; phase ^= 1u; }
                         }
                     }
@@ -135,13 +165,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
+        if (lane == 0 && leader) {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
                 if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -157,14 +187,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
 #pragma unroll
                     for (int k = 0; k < KB_BYTES / 32; ++k) {
                         // advancing 32 bytes along K inside the swizzle span = +2 in the (addr >> 4) field
-                        umma<kKind>(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), kIdesc,
-                                    (kb | k) != 0 ? 1u : 0u);
+                        if constexpr (kPair)
+                            umma_pair<kKind>(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), kIdesc,
+                                             (kb | k) != 0 ? 1u : 0u);
+                        else
+                            umma<kKind>(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), kIdesc,
+                                        (kb | k) != 0 ? 1u : 0u);
                     }
-                    umma_commit(smem_u32(&bar_empty[stage]));
+                    if constexpr (kPair) umma_commit_pair(smem_u32(&bar_empty[stage]), 3);
+                    else umma_commit(smem_u32(&bar_empty[stage]));
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                umma_commit(smem_u32(&bar_acc_full[acc]));
+                if constexpr (kPair) umma_commit_pair(smem_u32(&bar_acc_full[acc]), 3);
+                else umma_commit(smem_u32(&bar_acc_full[acc]));
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1u;
             }
@@ -182,11 +218,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
         const int w_l = rem - h_l * p.BW;
         const bool fast = (kOutMode == kOutNHWC_BF16) && p.vec_ok && ((p.Cout & 31) == 0);
         const bool has_res = p.residual != nullptr;
+        const uint32_t stage_tile = ring + (uint32_t)(kStages * G::kStageBytes) + (uint32_t)((warp - 2) * kStageTileBytes);
         int acc = 0;
         uint32_t acc_phase = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
             int r = tile;
             const int ct = r % p.tiles_c; r /= p.tiles_c;
+            r = r * kCtas + (int)cta_rank;
             const int tw = r % p.tiles_w; r /= p.tiles_w;
             const int th = r % p.tiles_h;
             const int tn = r / p.tiles_h;
@@ -196,10 +234,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
             const int col0 = half * kChunksPerWarp * 32;  // first column of this warp inside the tile
             const int c_base = ct * BN + col0;
             uint4 res_cur[4] = {};
-            if (fast && has_res && valid && c_base < p.Cout) {
-                const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.residual) + pix * p.Cout + c_base);
-#pragma unroll
-                for (int g = 0; g < 4; ++g) res_cur[g] = __ldg(rp + g);
+            RowMap rows;
+            if (fast) {
+                rows = make_row_map(pix, valid, lane);
+                if (has_res && c_base < p.Cout) residual_fetch_rows(p, rows, c_base, lane, res_cur);
             }
             bool ok = mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
             ok = __all_sync(0xffffffffu, ok);
@@ -212,14 +250,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                 uint32_t v[32];
                 tmem_ld_32x32(t_addr + (uint32_t)(i * 32), v);
                 uint4 res_next[4] = {};
-                if (fast && has_res && valid && (i + 1 < kChunksPerWarp) && (c0 + 32 < p.Cout)) {
-                    const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.residual) + pix * p.Cout + c0 + 32);
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) res_next[g] = __ldg(rp + g);
-                }
+                if (fast && has_res && (i + 1 < kChunksPerWarp) && (c0 + 32 < p.Cout))
+                    residual_fetch_rows(p, rows, c0 + 32, lane, res_next);
                 tmem_ld_wait();
                 if (fast) {
-                    if (valid && c0 < p.Cout) epilogue_fast_bf16(p, v, c0, pix, res_cur, has_res);
+                    if (c0 < p.Cout) epilogue_coalesced_bf16<32>(p, v, c0, stage_tile, lane, rows, res_cur, has_res);
                 } else {
                     epilogue_chunk<kOutMode>(p, v, c0, valid, n, oh, ow);
                 }
@@ -228,7 +263,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+            if (lane == 0) {
+                if constexpr (kPair) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_acc_empty[acc]), 0));
+                else mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+            }
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
@@ -243,45 +281,78 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
     }
     tc_fence_before_sync();
     __syncthreads();
+    // Neither CTA of a pair may release its TMEM or shared memory while the other can still signal or read it.
+    if constexpr (kPair) cluster_sync_all();
     tc_fence_after_sync();
     if (warp == 1) {
         __syncwarp();
-        tmem_dealloc(tmem_base, kTmemCols);
+        if constexpr (kPair) tmem_dealloc_pair(tmem_base, kTmemCols);
+        else tmem_dealloc(tmem_base, kTmemCols);
     }
     if (threadIdx.x == 0 && *abort_ptr && p.status != nullptr) atomicExch(p.status, KXC_B200_ERR_DEVICE_WAIT);
 }
 
-template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode>
+template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode, int kCtas>
 int32_t launch_one(const TcParams& p, cudaStream_t stream) {
-    using G = StageGeom<KB_BYTES, BN>;
-    auto kernel = conv_igemm_kernel<kKind, KB_BYTES, BN, kOutMode>;
+    using G = StageGeom<KB_BYTES, BN, kCtas>;
+    auto kernel = conv_igemm_kernel<kKind, KB_BYTES, BN, kOutMode, kCtas>;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
+    static int max_units[64] = {0};  // per device: CTAs (kCtas = 1) or clusters of two (kCtas = 2) resident at once
     std::call_once(once, [&] {
         attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes);
     });
     if (attr_err != cudaSuccess)
         return fail(KXC_B200_ERR_CUDA, "cudaFuncSetAttribute(smem=%d): %s", G::kSmemBytes, cudaGetErrorString(attr_err));
-    const long long tiles = (long long)p.tiles_c * p.tiles_w * p.tiles_h * p.tiles_n;
+    const long long m_tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n;
+    const long long tiles = (long long)p.tiles_c * ((m_tiles + kCtas - 1) / kCtas);
     if (tiles <= 0) return KXC_B200_OK;
-    const int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
-    kernel<<<grid, kTcThreads, G::kSmemBytes, stream>>>(p);
+    if constexpr (kCtas == 1) {
+        const int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
+        kernel<<<grid, kTcThreads, G::kSmemBytes, stream>>>(p);
+    } else {
+        int dev = 0;
+        KXC_CUDA_TRY(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64) return fail(KXC_B200_ERR_INVALID, "device ordinal %d out of range", dev);
+        cudaLaunchConfig_t lc = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        lc.blockDim = dim3(kTcThreads);
+        lc.dynamicSmemBytes = G::kSmemBytes;
+        lc.stream = stream;
+        lc.attrs = attr;
+        lc.numAttrs = 1;
+        if (max_units[dev] == 0) {
+            lc.gridDim = dim3(kNumSMs);
+            int n = 0;
+            const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kernel, &lc);
+            if (e != cudaSuccess || n <= 0)
+                return fail(KXC_B200_ERR_CUDA, "cudaOccupancyMaxActiveClusters: %s (%d clusters)", cudaGetErrorString(e), n);
+            max_units[dev] = n < kNumSMs / 2 ? n : kNumSMs / 2;
+        }
+        const int clusters = (int)(tiles < max_units[dev] ? tiles : max_units[dev]);
+        lc.gridDim = dim3(2 * clusters);
+        KXC_CUDA_TRY(cudaLaunchKernelEx(&lc, kernel, p));
+    }
     return check_launch("conv_igemm_kernel");
 }
 
-template <MmaKind kKind, int KB_BYTES, int BN>
+template <MmaKind kKind, int KB_BYTES, int BN, int kCtas>
 int32_t launch_by_out(const TcConfig& cfg, const TcParams& p, cudaStream_t s) {
     if constexpr (kKind == MmaKind::I8) {
         switch (cfg.out_mode) {
-            case kOutNHWC_S8: return launch_one<kKind, KB_BYTES, BN, kOutNHWC_S8>(p, s);
-            case kOutNCHW_S8: return launch_one<kKind, KB_BYTES, BN, kOutNCHW_S8>(p, s);
+            case kOutNHWC_S8: return launch_one<kKind, KB_BYTES, BN, kOutNHWC_S8, kCtas>(p, s);
+            case kOutNCHW_S8: return launch_one<kKind, KB_BYTES, BN, kOutNCHW_S8, kCtas>(p, s);
             default: break;
         }
     } else {
         switch (cfg.out_mode) {
-            case kOutNHWC_BF16: return launch_one<kKind, KB_BYTES, BN, kOutNHWC_BF16>(p, s);
-            case kOutNHWC_F32: return launch_one<kKind, KB_BYTES, BN, kOutNHWC_F32>(p, s);
-            case kOutNCHW_F32: return launch_one<kKind, KB_BYTES, BN, kOutNCHW_F32>(p, s);
+            case kOutNHWC_BF16: return launch_one<kKind, KB_BYTES, BN, kOutNHWC_BF16, kCtas>(p, s);
+            case kOutNHWC_F32: return launch_one<kKind, KB_BYTES, BN, kOutNHWC_F32, kCtas>(p, s);
+            case kOutNCHW_F32: return launch_one<kKind, KB_BYTES, BN, kOutNCHW_F32, kCtas>(p, s);
             default: break;
         }
     }
@@ -290,10 +361,20 @@ int32_t launch_by_out(const TcConfig& cfg, const TcParams& p, cudaStream_t s) {
 
 template <MmaKind kKind, int KB_BYTES>
 int32_t launch_by_bn(const TcConfig& cfg, const TcParams& p, cudaStream_t s) {
+    if constexpr (KB_BYTES == 128) {
+        if (cfg.ctas == 2) {  // pairs exist for the wide tiles only (tc_setup_conv)
+            switch (cfg.bn) {
+                case 128: return launch_by_out<kKind, KB_BYTES, 128, 2>(cfg, p, s);
+                case 256: return launch_by_out<kKind, KB_BYTES, 256, 2>(cfg, p, s);
+                default: return fail(KXC_B200_ERR_INVALID, "tensor-core conv: no CTA-pair kernel for N tile %d", cfg.bn);
+            }
+        }
+    }
+    if (cfg.ctas != 1) return fail(KXC_B200_ERR_INVALID, "tensor-core conv: no CTA-pair kernel for %d-byte K blocks", KB_BYTES);
     switch (cfg.bn) {
-        case 64: return launch_by_out<kKind, KB_BYTES, 64>(cfg, p, s);
-        case 128: return launch_by_out<kKind, KB_BYTES, 128>(cfg, p, s);
-        case 256: return launch_by_out<kKind, KB_BYTES, 256>(cfg, p, s);
+        case 64: return launch_by_out<kKind, KB_BYTES, 64, 1>(cfg, p, s);
+        case 128: return launch_by_out<kKind, KB_BYTES, 128, 1>(cfg, p, s);
+        case 256: return launch_by_out<kKind, KB_BYTES, 256, 1>(cfg, p, s);
         default: return fail(KXC_B200_ERR_INVALID, "tensor-core conv: unsupported N tile %d", cfg.bn);
     }
 }
@@ -422,7 +503,18 @@ int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_m
     p->tiles_n = (N + p->BNI - 1) / p->BNI;
 
     int bn = Cout <= 64 ? 64 : (Cout <= 128 ? 128 : 256);
-    cfg->dtype = dtype; cfg->kb_bytes = kb_bytes; cfg->bn = bn; cfg->out_mode = out_mode;
+    // CTA pairs (tcgen05 cta_group::2): each CTA fetches half of the B tile, which relieves the L2 -> shared-memory
+    // fill rate that bounds the wide tiles. KXC_B200_CTA_PAIR=0 switches them off (for measurements).
+    static const bool pair_enabled = [] {
+        const char* e = getenv("KXC_B200_CTA_PAIR");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    const long long m_tiles = (long long)p->tiles_w * p->tiles_h * p->tiles_n;
+    // Measured: pairs gain 5-7 % with the 256-wide tile and lose 3-10 % with the 128-wide one (the pair's MMA is
+    // no faster there and the handshakes cross SMs), so only the 256-wide tile uses them. "2" forces them for 128 too.
+    static const bool pair_all = [] { const char* e = getenv("KXC_B200_CTA_PAIR"); return e != nullptr && e[0] == '2'; }();
+    const int ctas = (pair_enabled && bn >= (pair_all ? 128 : 256) && kb_bytes == 128 && m_tiles >= 2) ? 2 : 1;
+    cfg->dtype = dtype; cfg->kb_bytes = kb_bytes; cfg->bn = bn; cfg->out_mode = out_mode; cfg->ctas = ctas;
     p->tiles_c = (Cout + bn - 1) / bn;
 
     const uint32_t box[4] = {(uint32_t)p->kb_elems, (uint32_t)p->BW, (uint32_t)p->BH, (uint32_t)p->BNI};
@@ -449,7 +541,7 @@ int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_m
     const uint64_t ktot = (uint64_t)KH * KW * cpad;
     const uint64_t bdims[2] = {ktot, (uint64_t)Cout};
     const uint64_t bstrides[1] = {ktot * eb};
-    const uint32_t bbox[2] = {(uint32_t)p->kb_elems, (uint32_t)bn};
+    const uint32_t bbox[2] = {(uint32_t)p->kb_elems, (uint32_t)(bn / ctas)};
     KXC_TRY(tc_make_tmap(&p->tmB, dtype, 2, const_cast<void*>(w_packed), bdims, bstrides, bbox, kb_bytes));
     if (status_word != nullptr) {
         p->status = status_word;

@@ -60,6 +60,7 @@ struct TcConfig {
     int kb_bytes;  // 32, 64 or 128 (also the TMA/UMMA swizzle span)
     int bn;        // 64, 128 or 256
     TcOutMode out_mode;
+    int ctas = 1;  // 2: clusters of two CTAs share each B tile (tcgen05 cta_group::2, M = 256 per instruction)
 };
 
 // Sets vec_ok from the epilogue pointers; call after filling bias/residual/out.

@@ -952,15 +952,16 @@ extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, c
             const double in_bytes = (w.mode == 1 || w.mode == 4) ? (double)st.N * st.Hp * st.Wp * 4 * eb : (double)st.N * st.H * st.W * st.cpad * eb;
             by = in_bytes + (double)w.bytes + out_elems * (st.fused_pool ? 0.25 : 1.0) * (st.out_is_graph_output ? 4.0 : eb) +
                  (st.in1 >= 0 ? out_elems * eb : 0.0) + 4.0 * w.O;
-            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d", st.direct == 2 ? (st.fused_pool ? "conv_stem_pool" : "conv_stem_direct") : (st.direct ? "conv_direct" : "conv_igemm"), w.C, st.H, st.W, w.O, w.KH, w.KW,
-                     p.stride, st.in1 >= 0 ? " +res" : "", st.relu ? " +relu" : "", p.BNI, p.BH, p.BW, st.cfg.bn);
+            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d%s", st.direct == 2 ? (st.fused_pool ? "conv_stem_pool" : "conv_stem_direct") : (st.direct ? "conv_direct" : "conv_igemm"), w.C, st.H, st.W, w.O, w.KH, w.KW,
+                     p.stride, st.in1 >= 0 ? " +res" : "", st.relu ? " +relu" : "", p.BNI, p.BH, p.BW, st.cfg.bn,
+                     st.cfg.ctas == 2 ? " pair" : "");
             break;
         }
         case SKind::Gemm: {
             const PackedWeight& w = pl->weights[st.weight];
             fl = 2.0 * st.N * (double)w.O * w.C;
             by = (double)st.N * w.C * eb + (double)w.bytes + (double)st.N * w.O * (st.out_is_graph_output ? 4.0 : eb) + 4.0 * w.O;
-            snprintf(buf, sizeof(buf), "dense_igemm m%d k%d -> n%d bn%d", st.N, w.C, w.O, st.cfg.bn);
+            snprintf(buf, sizeof(buf), "dense_igemm m%d k%d -> n%d bn%d%s", st.N, w.C, w.O, st.cfg.bn, st.cfg.ctas == 2 ? " pair" : "");
             break;
         }
         case SKind::MaxPool:
