@@ -1,4 +1,5 @@
 // C-ABI entry points of libkxc_b200 that validate a descriptor and dispatch to a kernel family.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -9,6 +10,14 @@ namespace kxc_b200 {
 char* last_error_buffer() {
     static thread_local char buf[kLastErrorSize] = {0};
     return buf;
+}
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("KXC_B200_PDL");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    return on;
 }
 
 int32_t require_device() {

@@ -56,6 +56,37 @@ inline int64_t pool_out_dim(int64_t in, int64_t k, int64_t s, int64_t p0, int64_
     return ceil_mode ? ((num + s - 1) / s + 1) : (num / s + 1);
 }
 
+// Launch with optional programmatic dependent launch (the kernel must call sm100::pdl_wait() before it touches
+// memory other kernels produce or consume) and an optional cluster of `cluster_x` CTAs.
+// KXC_B200_PDL=0 in the environment launches everything fully serialized.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                                 int cluster_x, Args&&... args) {
+    cudaLaunchConfig_t lc = {};
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (pdl && pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    lc.gridDim = grid;
+    lc.blockDim = block;
+    lc.dynamicSmemBytes = smem;
+    lc.stream = stream;
+    lc.attrs = attr;
+    lc.numAttrs = n;
+    return cudaLaunchKernelEx(&lc, kernel, static_cast<KArgs>(args)...);
+}
+
 constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
 
 }  // namespace kxc_b200

@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_direct_kernel(const __gri
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abort_ptr = &abort_flag;
+    pdl_launch_dependents();
 
     const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
 
@@ -95,6 +96,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_direct_kernel(const __gri
             // resident weights: nine 64x64 tap blocks
             mbar_arrive_expect_tx(smem_u32(&bar_w), kWeightBytes);
             for (int t = 0; t < kTaps; ++t) tma_load_2d(w_smem + t * (kBN * 128), &p.tmB, smem_u32(&bar_w), t * kC, 0);
+            pdl_wait();  // the weights are constants; the activations come from the previous kernel
             int stage = 0;
             uint32_t phase = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
@@ -172,6 +174,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_direct_kernel(const __gri
         const int row = quad * 32 + lane;
         const int h_l = row >> 3, w_l = row & 7;
         const bool has_res = p.residual != nullptr;
+        pdl_wait();
         int acc = 0;
         uint32_t acc_phase = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
@@ -262,7 +265,7 @@ int32_t direct3x3_launch(const TcParams& p, cudaStream_t stream) {
     const long long tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n;
     if (tiles <= 0) return KXC_B200_OK;
     const int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
-    conv3x3_direct_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+    KXC_CUDA_TRY(launch_kernel(conv3x3_direct_kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, /*pdl=*/true, 1, p));
     return check_launch("conv3x3_direct_kernel");
 }
 

@@ -105,12 +105,14 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __g
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abort_ptr = &abort_flag;
+    pdl_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
             const uint32_t wbytes = (uint32_t)(KH * 4 * kBN * 16);
             mbar_arrive_expect_tx(smem_u32(&bar_w), wbytes);
-            bulk_copy_g2s(w_smem, p.aux_w, wbytes, smem_u32(&bar_w));
+            bulk_copy_g2s(w_smem, p.aux_w, wbytes, smem_u32(&bar_w));  // constants: no need to wait for the previous kernel
+            pdl_wait();
             int stage = 0;
             uint32_t phase = 0;
             for (int strip = blockIdx.x; strip < total_strips; strip += gridDim.x) {
@@ -168,6 +170,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __g
         const int ow = quad * 32 + lane;
         const int c0 = half * 32;
         const bool col_ok = ow < p.OW;
+        pdl_wait();
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -283,6 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_pool_kernel(const __gri
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abort_ptr = &abort_flag;
+    pdl_launch_dependents();
 
     // Strip s of an image covers conv rows 8s-1 .. 8s+7 (local j = 0..8; j = 0 is skipped for s = 0, it is the
     // pool's padding row) and packed input rows from max(16s-2, 0).
@@ -290,7 +294,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_pool_kernel(const __gri
         if (lane == 0) {
             const uint32_t wbytes = (uint32_t)(KH * 4 * kBN * 16);
             mbar_arrive_expect_tx(smem_u32(&bar_w), wbytes);
-            bulk_copy_g2s(w_smem, p.aux_w, wbytes, smem_u32(&bar_w));
+            bulk_copy_g2s(w_smem, p.aux_w, wbytes, smem_u32(&bar_w));  // constants: no need to wait for the previous kernel
+            pdl_wait();
             int stage = 0;
             uint32_t phase = 0;
             for (int strip = blockIdx.x; strip < total_strips; strip += gridDim.x) {
@@ -363,6 +368,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_pool_kernel(const __gri
         const int et = threadIdx.x - 64;  // 0..255 among the epilogue threads
         const int POH = p.OH / 2, POW = p.OW / 2;
         __nv_bfloat16* pooled = static_cast<__nv_bfloat16*>(p.out);
+        pdl_wait();
         int acc = 0;
         uint32_t acc_phase = 0;
         uint32_t ring_ctr = 0;  // ring slot of local conv row j is (ring_ctr + j) % kRingRows
@@ -523,7 +529,7 @@ int32_t stem_pool_launch(const TcParams& p, cudaStream_t stream) {
     const long long strips = (long long)(p.OH / kStripRows) * p.N;
     if (strips <= 0) return KXC_B200_OK;
     const int grid = (int)(strips < kNumSMs ? strips : kNumSMs);
-    conv_stem_pool_kernel<<<grid, kThreads, kPoolSmemBytes, stream>>>(p);
+    KXC_CUDA_TRY(launch_kernel(conv_stem_pool_kernel, dim3(grid), dim3(kThreads), kPoolSmemBytes, stream, /*pdl=*/true, 1, p));
     return check_launch("conv_stem_pool_kernel");
 }
 
@@ -538,7 +544,7 @@ int32_t stem_direct_launch(const TcParams& p, cudaStream_t stream) {
     const long long strips = (long long)((p.OH + kStripRows - 1) / kStripRows) * p.N;
     if (strips <= 0) return KXC_B200_OK;
     const int grid = (int)(strips < kNumSMs ? strips : kNumSMs);
-    conv_stem_direct_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+    KXC_CUDA_TRY(launch_kernel(conv_stem_direct_kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, /*pdl=*/true, 1, p));
     return check_launch("conv_stem_direct_kernel");
 }
 

@@ -100,6 +100,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abort_ptr = &abort_flag;
+    pdl_launch_dependents();  // the next kernel's CTAs may take over SMs this grid has left; they wait before touching memory
 
     const int num_kb = p.taps_h * p.taps_w * p.cblocks;
     // Work items: (channel tile, group of kCtas consecutive pixel tiles). A pair whose second pixel tile
@@ -116,6 +117,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
             tma_prefetch_desc(&p.tmB);
             tma_prefetch_desc(&p.tmA[0]);
             const uint32_t tx_bytes = (uint32_t)(rows_used * KB_BYTES + G::kBBytes);
+            pdl_wait();  // the activations come from the previous kernel
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -219,6 +221,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
         const bool fast = (kOutMode == kOutNHWC_BF16) && p.vec_ok && ((p.Cout & 31) == 0);
         const bool has_res = p.residual != nullptr;
         const uint32_t stage_tile = ring + (uint32_t)(kStages * G::kStageBytes) + (uint32_t)((warp - 2) * kStageTileBytes);
+        pdl_wait();  // residual reads and output writes must not overtake earlier kernels
         int acc = 0;
         uint32_t acc_phase = 0;
         for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
@@ -307,36 +310,33 @@ int32_t launch_one(const TcParams& p, cudaStream_t stream) {
     const long long m_tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n;
     const long long tiles = (long long)p.tiles_c * ((m_tiles + kCtas - 1) / kCtas);
     if (tiles <= 0) return KXC_B200_OK;
-    if constexpr (kCtas == 1) {
-        const int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
-        kernel<<<grid, kTcThreads, G::kSmemBytes, stream>>>(p);
-    } else {
+    int units = kNumSMs;
+    if constexpr (kCtas == 2) {
         int dev = 0;
         KXC_CUDA_TRY(cudaGetDevice(&dev));
         if (dev < 0 || dev >= 64) return fail(KXC_B200_ERR_INVALID, "device ordinal %d out of range", dev);
-        cudaLaunchConfig_t lc = {};
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        lc.blockDim = dim3(kTcThreads);
-        lc.dynamicSmemBytes = G::kSmemBytes;
-        lc.stream = stream;
-        lc.attrs = attr;
-        lc.numAttrs = 1;
         if (max_units[dev] == 0) {
+            cudaLaunchConfig_t lc = {};
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
             lc.gridDim = dim3(kNumSMs);
+            lc.blockDim = dim3(kTcThreads);
+            lc.dynamicSmemBytes = G::kSmemBytes;
+            lc.attrs = attr;
+            lc.numAttrs = 1;
             int n = 0;
             const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kernel, &lc);
             if (e != cudaSuccess || n <= 0)
                 return fail(KXC_B200_ERR_CUDA, "cudaOccupancyMaxActiveClusters: %s (%d clusters)", cudaGetErrorString(e), n);
             max_units[dev] = n < kNumSMs / 2 ? n : kNumSMs / 2;
         }
-        const int clusters = (int)(tiles < max_units[dev] ? tiles : max_units[dev]);
-        lc.gridDim = dim3(2 * clusters);
-        KXC_CUDA_TRY(cudaLaunchKernelEx(&lc, kernel, p));
+        units = max_units[dev];
     }
+    const int grid = kCtas * (int)(tiles < units ? tiles : units);
+    KXC_CUDA_TRY(launch_kernel(kernel, dim3(grid), dim3(kTcThreads), G::kSmemBytes, stream, /*pdl=*/true, kCtas, p));
     return check_launch("conv_igemm_kernel");
 }
 

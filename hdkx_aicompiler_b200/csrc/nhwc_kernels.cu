@@ -14,6 +14,7 @@
 #include <cmath>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace kxc_b200 {
 namespace {
@@ -162,6 +163,8 @@ __global__ void __launch_bounds__(kThreads) gap_nhwc_kernel(const T* __restrict_
     const int cg = C / L;
     const int64_t total = (int64_t)N * cg;
     const float div = (float)HW;
+    sm100::pdl_launch_dependents();
+    sm100::pdl_wait();
     for (int64_t lin = (int64_t)blockIdx.x * kThreads + threadIdx.x; lin < total; lin += (int64_t)gridDim.x * kThreads) {
         const int g = (int)(lin % cg);
         const int n = (int)(lin / cg);
@@ -169,7 +172,18 @@ __global__ void __launch_bounds__(kThreads) gap_nhwc_kernel(const T* __restrict_
 #pragma unroll
         for (int j = 0; j < L; ++j) s[j] = 0.0f;
         const T* p = x + (int64_t)n * HW * C + g * L;
-        for (int i = 0; i < HW; ++i) {
+        // eight pixels' loads in flight at a time; the additions keep the pixel order
+        int i = 0;
+        for (; i + 8 <= HW; i += 8) {
+            float v[8][L];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) Vec<T>::load(p + (int64_t)(i + u) * C, v[u]);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+#pragma unroll
+                for (int j = 0; j < L; ++j) s[j] = __fadd_rn(s[j], v[u][j]);
+        }
+        for (; i < HW; ++i) {
             float v[L];
             Vec<T>::load(p + (int64_t)i * C, v);
 #pragma unroll
@@ -244,6 +258,8 @@ __global__ void __launch_bounds__(kThreads) stem_pack_kernel(const float* __rest
     // 32 or 64 contiguous bytes stored
     const int wq = Wp / 4;
     const int64_t total = (int64_t)N * Hp * wq;
+    sm100::pdl_launch_dependents();
+    sm100::pdl_wait();  // the packed buffer may still be read by a kernel of the previous run
     for (int64_t lin = (int64_t)blockIdx.x * kThreads + threadIdx.x; lin < total; lin += (int64_t)gridDim.x * kThreads) {
         const int wp0 = (int)(lin % wq) * 4;
         int64_t t = lin / wq;
@@ -327,8 +343,10 @@ int32_t gap_nhwc(const void* x, void* out, TcDType dt, int N, int HW, int C, cud
     if (C % lanes != 0) return fail(KXC_B200_ERR_UNSUPPORTED, "NHWC global pool: %d channels is not a multiple of %d", C, lanes);
     const int64_t items = (int64_t)N * (C / lanes);
     if (items == 0) return KXC_B200_OK;
-    KXC_DISPATCH_ACT(dt, (gap_nhwc_kernel<T><<<grid_for(items, 16), kThreads, 0, s>>>(static_cast<const T*>(x),
-                                                                                    static_cast<T*>(out), N, HW, C)));
+    cudaError_t err = cudaSuccess;
+    KXC_DISPATCH_ACT(dt, (err = launch_kernel(gap_nhwc_kernel<T>, dim3(grid_for(items, 16)), dim3(kThreads), 0, s, /*pdl=*/true, 1,
+                                              static_cast<const T*>(x), static_cast<T*>(out), N, HW, C)));
+    if (err != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "gap_nhwc launch: %s", cudaGetErrorString(err));
     return check_launch("gap_nhwc");
 }
 
@@ -355,8 +373,10 @@ int32_t stem_pack(const float* x, void* out, TcDType dt, int N, int C, int H, in
     if (Wp % 4 != 0) return fail(KXC_B200_ERR_INVALID, "stem_pack: packed width %d must be a multiple of 4", Wp);
     const int64_t items = (int64_t)N * Hp * (Wp / 4);
     if (items == 0) return KXC_B200_OK;
-    KXC_DISPATCH_ACT(dt, (stem_pack_kernel<T><<<grid_for(items, 16), kThreads, 0, s>>>(x, static_cast<T*>(out), N, C, H, W, Hp, Wp,
-                                                                                     pad_h, pad_w)));
+    cudaError_t err = cudaSuccess;
+    KXC_DISPATCH_ACT(dt, (err = launch_kernel(stem_pack_kernel<T>, dim3(grid_for(items, 16)), dim3(kThreads), 0, s, /*pdl=*/true, 1, x,
+                                              static_cast<T*>(out), N, C, H, W, Hp, Wp, pad_h, pad_w)));
+    if (err != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "stem_pack launch: %s", cudaGetErrorString(err));
     return check_launch("stem_pack");
 }
 

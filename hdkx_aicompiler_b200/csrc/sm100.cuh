@@ -19,6 +19,15 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in
+// the stream is still running. pdl_wait() blocks until the predecessor grid has completed and its memory is
+// visible (a no-op without the attribute): every global access to data another kernel produces or consumes
+// comes after it. pdl_launch_dependents() lets the successor's CTAs be scheduled as soon as every CTA of this
+// grid has called it, so the successor's prologue overlaps this grid's tail.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier ----------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
