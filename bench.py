@@ -175,23 +175,54 @@ def main():
 
     gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
     host_in = torch.empty((per_gpu, 3, 224, 224), dtype=torch.float32).normal_(0, 1, generator=gen).pin_memory()
-    x = host_in.to(device, non_blocking=True)
-    logits = torch.empty(graph.out_shape, dtype=torch.float32, device=device)
-    gather = GatherToWorker0(graph.out_shape, torch.float32, device)
+    # Consecutive steps are pipelined the way a serving loop would run them: two input and two output buffers,
+    # the host->device copy of step i+1 (copy stream) and the gather / read-back of step i-1 (gather stream)
+    # overlap the kernels of step i (run stream). Every step's copies and its gather are still issued inside
+    # the timed region and are complete when it ends.
+    xs = [host_in.to(device, non_blocking=True), host_in.to(device, non_blocking=True)]
+    x = xs[0]
+    logits_buf = [torch.empty(graph.out_shape, dtype=torch.float32, device=device) for _ in range(2)]
+    logits = logits_buf[0]
+    gathers = [GatherToWorker0(graph.out_shape, torch.float32, device) for _ in range(2)]
     host_out = torch.empty((args.batch if rank == 0 else per_gpu, graph.out_shape[1]), dtype=torch.float32).pin_memory()
 
-    def step(from_host):
-        if from_host:
-            x.copy_(host_in, non_blocking=True)
-        graph.run(x, out=logits)
-        parts = gather(logits)  # GatherToWorker0: shards in rank order on rank 0
-        if from_host and rank == 0:
-            for r, part in enumerate(parts):
-                host_out[r * per_gpu:(r + 1) * per_gpu].copy_(part, non_blocking=True)
-
     run_stream = torch.cuda.Stream(device)  # a real stream: the legacy default stream cannot be graph-captured
+    copy_stream = torch.cuda.Stream(device)
+    gather_stream = torch.cuda.Stream(device)
     run_stream.wait_stream(torch.cuda.current_stream(device))
+    copy_stream.wait_stream(torch.cuda.current_stream(device))
+    gather_stream.wait_stream(torch.cuda.current_stream(device))
     torch.cuda.set_stream(run_stream)
+    x_free = [None, None]      # kernels that read xs[j] have finished
+    out_free = [None, None]    # gather / read-back of logits_buf[j] has finished
+    counter = [0]
+
+    def step(from_host):
+        j = counter[0] & 1
+        counter[0] += 1
+        if from_host:
+            with torch.cuda.stream(copy_stream):
+                if x_free[j] is not None:
+                    copy_stream.wait_event(x_free[j])
+                xs[j].copy_(host_in, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(copy_stream)
+            run_stream.wait_event(ready)
+        if out_free[j] is not None:
+            run_stream.wait_event(out_free[j])
+        graph.run(xs[j], out=logits_buf[j])
+        done = torch.cuda.Event()
+        done.record(run_stream)
+        x_free[j] = done
+        with torch.cuda.stream(gather_stream):
+            gather_stream.wait_event(done)
+            parts = gathers[j](logits_buf[j])  # GatherToWorker0: shards in rank order on rank 0
+            if from_host and rank == 0:
+                for r, part in enumerate(parts):
+                    host_out[r * per_gpu:(r + 1) * per_gpu].copy_(part, non_blocking=True)
+            fin = torch.cuda.Event()
+            fin.record(gather_stream)
+        out_free[j] = fin
 
     def timed(from_host, steps):
         for _ in range(warmup):
@@ -204,6 +235,8 @@ def main():
         e0.record()
         for _ in range(steps):
             step(from_host)
+        run_stream.wait_stream(gather_stream)  # the timed region ends when the last gather / read-back has finished
+        run_stream.wait_stream(copy_stream)
         e1.record()
         torch.cuda.synchronize()
         if world > 1:
@@ -252,7 +285,8 @@ def main():
         "config": {"workload": f"resnet18 inference, global batch {args.batch}, {args.precision} operands / fp32 accumulate, "
                                f"{per_gpu} images per GPU, weights replicated, logits gathered to rank 0",
                    "global_batch": args.batch, "per_gpu_batch": per_gpu, "parallelism": f"dp{world}",
-                   "l2": "inputs larger than L2 (616 MB of images and >1 GB of activations per step per GPU at N=1)"},
+                   "l2": "inputs larger than L2 (616 MB of images and >1 GB of activations per step per GPU at N=1)",
+                   "pipelining": "steps overlap: input copy of step i+1 and gather/read-back of step i-1 run beside the kernels of step i"},
         "clocks": clocks,
         "e2e": {"value": args.batch / (e2e_ms / args.steps / 1e3), "unit": UNIT,
                 "h2d_bytes_per_step": int(host_in.numel() * 4 * world), "d2h_bytes_per_step": int(args.batch * graph.out_shape[1] * 4)},

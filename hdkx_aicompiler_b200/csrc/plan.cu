@@ -128,13 +128,20 @@ struct kxc_b200_plan {
     };
     std::vector<XStep> xsteps;
     // optional CUDA-graph replay of one run (launch-bound small batches): the graph captured for a given
-    // packed-argument list is replayed while the caller keeps passing the same pointers
+    // packed-argument list is replayed whenever the caller passes the same pointers again; a few argument
+    // lists are remembered so that double-buffered inputs and outputs do not re-capture on every call
     bool use_graph = false;
-    std::vector<void*> graph_args;
-    cudaGraphExec_t graph_exec = nullptr;
+    static constexpr int kGraphSlots = 4;
+    struct GraphSlot {
+        std::vector<void*> args;
+        cudaGraphExec_t exec = nullptr;
+    };
+    GraphSlot graph_slots[kGraphSlots];
+    int graph_next_slot = 0;
 
     ~kxc_b200_plan() {
-        if (graph_exec) cudaGraphExecDestroy(graph_exec);
+        for (auto& g : graph_slots)
+            if (g.exec) cudaGraphExecDestroy(g.exec);
         if (arena) cudaFree(arena);
         if (weight_arena) cudaFree(weight_arena);
     }
@@ -855,12 +862,15 @@ extern "C" int32_t kxc_b200_plan_run(kxc_b200_plan* pl, void** packed_args, void
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // the legacy default stream cannot be captured: run eagerly there
     if (s == nullptr || s == cudaStreamLegacy) return plan_run_impl(pl, packed_args, stream, nullptr);
-    const bool same = pl->graph_exec != nullptr && pl->graph_args.size() == nargs &&
-                      std::equal(pl->graph_args.begin(), pl->graph_args.end(), packed_args);
-    if (!same) {
-        if (pl->graph_exec) {
-            cudaGraphExecDestroy(pl->graph_exec);
-            pl->graph_exec = nullptr;
+    kxc_b200_plan::GraphSlot* slot = nullptr;
+    for (auto& g : pl->graph_slots)
+        if (g.exec != nullptr && g.args.size() == nargs && std::equal(g.args.begin(), g.args.end(), packed_args)) slot = &g;
+    if (slot == nullptr) {
+        slot = &pl->graph_slots[pl->graph_next_slot];
+        pl->graph_next_slot = (pl->graph_next_slot + 1) % kxc_b200_plan::kGraphSlots;
+        if (slot->exec) {
+            cudaGraphExecDestroy(slot->exec);
+            slot->exec = nullptr;
         }
         cudaGraph_t graph = nullptr;
         if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
@@ -874,15 +884,15 @@ extern "C" int32_t kxc_b200_plan_run(kxc_b200_plan* pl, void** packed_args, void
             return rc;
         }
         if (e != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
-        const cudaError_t ie = cudaGraphInstantiate(&pl->graph_exec, graph, 0);
+        const cudaError_t ie = cudaGraphInstantiate(&slot->exec, graph, 0);
         cudaGraphDestroy(graph);
         if (ie != cudaSuccess) {
-            pl->graph_exec = nullptr;
+            slot->exec = nullptr;
             return fail(KXC_B200_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(ie));
         }
-        pl->graph_args.assign(packed_args, packed_args + nargs);
+        slot->args.assign(packed_args, packed_args + nargs);
     }
-    KXC_CUDA_TRY(cudaGraphLaunch(pl->graph_exec, s));
+    KXC_CUDA_TRY(cudaGraphLaunch(slot->exec, s));
     return KXC_B200_OK;
 }
 
