@@ -11,7 +11,8 @@ namespace kxc_b200 {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kUnroll = 4;
+constexpr int kUnroll = 8;     // relu: loads in flight per thread
+constexpr int kUnrollAdd = 6;  // add: pairs of loads in flight per thread
 constexpr int kBlocksPerSM = 8;
 
 __device__ __forceinline__ float relu1(float v) { return v > 0.0f ? v : 0.0f; }
@@ -26,19 +27,22 @@ __device__ __forceinline__ float4 add4(float4 a, float4 b) {
 __device__ __forceinline__ float4 ldg_stream(const float4* p) { return __ldcs(p); }
 __device__ __forceinline__ void stg_stream(float4* p, float4 v) { __stcs(p, v); }
 
+// Each sweep keeps kUnroll independent 16-byte loads per thread in flight; out-of-range slots are predicated off
+// instead of being handled by a second, one-load-at-a-time loop (these kernels run for ~10 us: a tail sweep
+// with a single load in flight costs a full memory round trip).
 template <bool kRelu>
 __global__ void __launch_bounds__(kThreads) relu_vec_kernel(const float4* __restrict__ x, float4* __restrict__ out,
                                                             int64_t nvec) {
     const int64_t stride = (int64_t)gridDim.x * kThreads;
-    int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nvec; i += kUnroll * stride) {
         float4 v[kUnroll];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) v[u] = ldg_stream(x + i + u * stride);
+        for (int u = 0; u < kUnroll; ++u)
+            if (i + u * stride < nvec) v[u] = ldg_stream(x + i + u * stride);
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) stg_stream(out + i + u * stride, relu4(v[u]));
+        for (int u = 0; u < kUnroll; ++u)
+            if (i + u * stride < nvec) stg_stream(out + i + u * stride, relu4(v[u]));
     }
-    for (; i < nvec; i += stride) stg_stream(out + i, relu4(ldg_stream(x + i)));
 }
 
 __global__ void relu_scalar_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t begin, int64_t n) {
@@ -50,23 +54,22 @@ template <bool kRelu>
 __global__ void __launch_bounds__(kThreads) add_vec_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
                                                            float4* __restrict__ out, int64_t nvec) {
     const int64_t stride = (int64_t)gridDim.x * kThreads;
-    int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
-        float4 va[kUnroll], vb[kUnroll];
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nvec; i += kUnrollAdd * stride) {
+        float4 va[kUnrollAdd], vb[kUnrollAdd];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            va[u] = ldg_stream(a + i + u * stride);
-            vb[u] = ldg_stream(b + i + u * stride);
+        for (int u = 0; u < kUnrollAdd; ++u) {
+            if (i + u * stride < nvec) {
+                va[u] = ldg_stream(a + i + u * stride);
+                vb[u] = ldg_stream(b + i + u * stride);
+            }
         }
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            float4 s = add4(va[u], vb[u]);
-            stg_stream(out + i + u * stride, kRelu ? relu4(s) : s);
+        for (int u = 0; u < kUnrollAdd; ++u) {
+            if (i + u * stride < nvec) {
+                const float4 s = add4(va[u], vb[u]);
+                stg_stream(out + i + u * stride, kRelu ? relu4(s) : s);
+            }
         }
-    }
-    for (; i < nvec; i += stride) {
-        float4 s = add4(ldg_stream(a + i), ldg_stream(b + i));
-        stg_stream(out + i, kRelu ? relu4(s) : s);
     }
 }
 

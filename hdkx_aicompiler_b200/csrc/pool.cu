@@ -191,8 +191,10 @@ int32_t launch_max_pool(const float* x, const float* res, float* out, const kxc_
                       aligned16(x) && aligned16(out) && (!kAddRelu || aligned16(res));
     if (fast) {
         const int64_t items = pd.planes * (pd.OH / 2) * (pd.OW / 4);
-        maxpool_3x3s2p1_kernel<kAddRelu><<<grid_for(items, kThreads, 8), kThreads, 0, s>>>(x, res, out, pd.planes, pd.H,
-                                                                                          pd.W, pd.OH, pd.OW);
+        // one item per thread (no grid-stride iterations) up to 64 blocks per SM: the hardware block scheduler
+        // balances these short kernels at a finer grain than a persistent loop would
+        maxpool_3x3s2p1_kernel<kAddRelu><<<grid_for(items, kThreads, 64), kThreads, 0, s>>>(x, res, out, pd.planes, pd.H,
+                                                                                           pd.W, pd.OH, pd.OW);
     } else {
         const int64_t items = pd.planes * pd.OH * pd.OW;
         pool_generic_kernel<true, kAddRelu><<<grid_for(items, kThreads, 8), kThreads, 0, s>>>(x, res, out, pd);

@@ -75,6 +75,12 @@ def config2(iters, flush, hbm, tf, src):
         ("add", 77.07e6, lambda: ops.add(res, out)),
         ("nn_relu", 51.38e6, lambda: ops.nn_relu(res)),
     ]
+    # the same byte counts moved by the driver's device-to-device copy, as the bar a kernel of this size can reach
+    for nbytes in (154.14e6, 128.45e6, 77.07e6, 51.38e6):
+        n = int(nbytes // 8)
+        src_t = torch.empty(n, dtype=torch.float32, device="cuda").normal_()
+        dst_t = torch.empty_like(src_t)
+        cases.append((f"reference: copy_ of {nbytes / 2e6:.1f} MB (same bytes read + written)", nbytes, lambda d=dst_t, s_=src_t: d.copy_(s_)))
     for name, nbytes, fn in cases:
         ms = timeit(fn, iters, flush)
         emit(config=2, kernel=name, ms=ms, algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, frac_of_hbm_peak=nbytes / ms / 1e6 / hbm,
