@@ -260,8 +260,16 @@ __device__ __forceinline__ RowMap make_row_map(size_t pix, bool valid, int lane)
     }
     return m;
 }
+// What one output tensor's epilogue needs (a kernel with two outputs has two of these).
+struct EpiParams {
+    const float* bias;     // fp32, may be null
+    const void* residual;  // bf16 NHWC like the output, may be null
+    void* out;             // bf16 NHWC
+    int Cout;
+    int relu;
+};
 // Residual pieces in the transposed arrangement (issued by the caller before it waits for the accumulator).
-__device__ __forceinline__ void residual_fetch_rows(const TcParams& p, const RowMap& m, int c0, int lane, uint4 (&res)[4]) {
+__device__ __forceinline__ void residual_fetch_rows(const EpiParams& p, const RowMap& m, int c0, int lane, uint4 (&res)[4]) {
     const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.residual) + c0 + (lane & 3) * 8;
 #pragma unroll
     for (int j = 0; j < 4; ++j)
@@ -271,7 +279,7 @@ __device__ __forceinline__ void residual_fetch_rows(const TcParams& p, const Row
 // kPassRows = 32: the warp's 32 rows pass through the tile at once; 16: in two halves (for kernels that can
 // spare only 1 KiB of shared memory per epilogue warp).
 template <int kPassRows>
-__device__ __forceinline__ void epilogue_coalesced_bf16(const TcParams& p, const uint32_t (&v)[32], int c0, uint32_t tile, int lane,
+__device__ __forceinline__ void epilogue_coalesced_bf16(const EpiParams& p, const uint32_t (&v)[32], int c0, uint32_t tile, int lane,
                                                         const RowMap& m, const uint4 (&res)[4], bool has_res) {
     static_assert(kPassRows == 32 || kPassRows == 16, "staging tile of 32 or 16 rows");
     constexpr int kPasses = 32 / kPassRows;

@@ -49,12 +49,19 @@ struct StageGeom {
 // (M = 256), which reads both CTAs' shared memory and writes each CTA's 128 rows into that CTA's TMEM.
 // Both CTAs' loads count on the leader's "full" barrier; commits arrive on both CTAs' barriers; the
 // peer's epilogue warps release accumulators on the leader's "accumulator empty" barrier.
-template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode, int kCtas>
+//
+// kDual: a second output, the 1x1 convolution of the same stride over the same input (TcParams::tmB2 ...). Its
+// reduction is appended to the K loop as `cblocks` extra stages that load the centre tap's pixels again together
+// with the second weight tensor's rows and accumulate into a second TMEM accumulator; the epilogue drains both.
+template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode, int kCtas, bool kDual = false>
 __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_constant__ TcParams p) {
     using G = StageGeom<KB_BYTES, BN, kCtas>;
     constexpr bool kPair = kCtas == 2;
     constexpr int kStages = G::kStages;
-    constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators; 128, 256 or 512: a power of two
+    constexpr int kAccCols = kDual ? 2 * BN : BN;  // TMEM columns of one accumulator buffer (main [+ second output])
+    constexpr uint32_t kTmemCols = 2 * kAccCols;   // two buffers; 128, 256 or 512: a power of two
+    static_assert(kTmemCols <= 512, "TMEM has 512 columns");
+    static_assert(!kDual || (!kPair && kOutMode == kOutNHWC_BF16), "the dual kernel exists for single CTAs and bf16 NHWC output");
     constexpr uint32_t kIdesc =
         make_instr_desc(kKind == MmaKind::F16 ? kFmtBF16 : (kKind == MmaKind::TF32 ? kFmtTF32 : kFmtS8),
                         kKind == MmaKind::I8 ? kAccS32 : kAccF32, BN, 128u * kCtas);
@@ -102,7 +109,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
     volatile int* abort_ptr = &abort_flag;
     pdl_launch_dependents();  // the next kernel's CTAs may take over SMs this grid has left; they wait before touching memory
 
-    const int num_kb = p.taps_h * p.taps_w * p.cblocks;
+    const int num_kb_main = p.taps_h * p.taps_w * p.cblocks;
+    const int num_kb = num_kb_main + (kDual ? p.cblocks : 0);
     // Work items: (channel tile, group of kCtas consecutive pixel tiles). A pair whose second pixel tile
     // does not exist loads a box beyond the last image (all zeros) and stores nothing for it.
     const int m_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
@@ -116,6 +124,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
         if (lane == 0) {
             tma_prefetch_desc(&p.tmB);
             tma_prefetch_desc(&p.tmA[0]);
+            if constexpr (kDual) tma_prefetch_desc(&p.tmB2);
             const uint32_t tx_bytes = (uint32_t)(rows_used * KB_BYTES + G::kBBytes);
             pdl_wait();  // the activations come from the previous kernel
             int stage = 0;
@@ -163,6 +172,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                         }
                     }
                 }
+                if constexpr (kDual) {
+                    // second output: the centre tap's pixels (the 1x1 convolution's only tap) against tmB2
+                    const int dh = (p.taps_h / 2) * p.dil_h - p.pad_h, dw = (p.taps_w / 2) * p.dil_w - p.pad_w;  // 0, 0
+                    int map = 0, ch = oh0 + dh, cw = ow0 + dw;
+                    if (p.stride == 2) {
+                        const int hp = dh & 1, wp = dw & 1;
+                        map = hp * 2 + wp;
+                        ch = oh0 + ((dh - hp) >> 1);
+                        cw = ow0 + ((dw - wp) >> 1);
+                    }
+                    for (int cb = 0; ok && cb < p.cblocks; ++cb) {
+                        if (!mbar_wait_bounded(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t full = smem_u32(&bar_full[stage]);
+                        const uint32_t a_dst = ring + (uint32_t)stage * G::kStageBytes;
+                        mbar_arrive_expect_tx(full, tx_bytes);
+                        tma_load_4d(a_dst, &p.tmA[map], full, cb * p.kb_elems, cw, ch, n0);
+                        tma_load_2d(a_dst + G::kABytes, &p.tmB2, full, cb * p.kb_elems, co0);
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    }
+                }
             }
         }
     } else if (warp == 1) {
@@ -176,8 +208,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
             for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
                 if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr)) break;
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                const uint32_t d_main = tmem_base + (uint32_t)(acc * kAccCols);
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    const bool second = kDual && kb >= num_kb_main;
+                    const uint32_t d_tmem = second ? d_main + (uint32_t)BN : d_main;
+                    const int kb_local = second ? kb - num_kb_main : kb;
                     if (!mbar_wait_bounded(smem_u32(&bar_full[stage]), phase, abort_ptr)) {
                         ok = false;
                         break;
@@ -191,10 +226,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                         // advancing 32 bytes along K inside the swizzle span = +2 in the (addr >> 4) field
                         if constexpr (kPair)
                             umma_pair<kKind>(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), kIdesc,
-                                             (kb | k) != 0 ? 1u : 0u);
+                                             (kb_local | k) != 0 ? 1u : 0u);
                         else
                             umma<kKind>(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), kIdesc,
-                                        (kb | k) != 0 ? 1u : 0u);
+                                        (kb_local | k) != 0 ? 1u : 0u);
                     }
                     if constexpr (kPair) umma_commit_pair(smem_u32(&bar_empty[stage]), 3);
                     else umma_commit(smem_u32(&bar_empty[stage]));
@@ -220,6 +255,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
         const int w_l = rem - h_l * p.BW;
         const bool fast = (kOutMode == kOutNHWC_BF16) && p.vec_ok && ((p.Cout & 31) == 0);
         const bool has_res = p.residual != nullptr;
+        const EpiParams ep = {p.bias, p.residual, p.out, p.Cout, p.relu};
         const uint32_t stage_tile = ring + (uint32_t)(kStages * G::kStageBytes) + (uint32_t)((warp - 2) * kStageTileBytes);
         pdl_wait();  // residual reads and output writes must not overtake earlier kernels
         int acc = 0;
@@ -240,13 +276,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
             RowMap rows;
             if (fast) {
                 rows = make_row_map(pix, valid, lane);
-                if (has_res && c_base < p.Cout) residual_fetch_rows(p, rows, c_base, lane, res_cur);
+                if (has_res && c_base < p.Cout) residual_fetch_rows(ep, rows, c_base, lane, res_cur);
             }
             bool ok = mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + col0);
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols + col0);
 #pragma unroll 1
             for (int i = 0; i < kChunksPerWarp; ++i) {
                 const int c0 = c_base + i * 32;
@@ -254,15 +290,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                 tmem_ld_32x32(t_addr + (uint32_t)(i * 32), v);
                 uint4 res_next[4] = {};
                 if (fast && has_res && (i + 1 < kChunksPerWarp) && (c0 + 32 < p.Cout))
-                    residual_fetch_rows(p, rows, c0 + 32, lane, res_next);
+                    residual_fetch_rows(ep, rows, c0 + 32, lane, res_next);
                 tmem_ld_wait();
                 if (fast) {
-                    if (c0 < p.Cout) epilogue_coalesced_bf16<32>(p, v, c0, stage_tile, lane, rows, res_cur, has_res);
+                    if (c0 < p.Cout) epilogue_coalesced_bf16<32>(ep, v, c0, stage_tile, lane, rows, res_cur, has_res);
                 } else {
                     epilogue_chunk<kOutMode>(p, v, c0, valid, n, oh, ow);
                 }
 #pragma unroll
                 for (int g = 0; g < 4; ++g) res_cur[g] = res_next[g];
+            }
+            if constexpr (kDual) {
+                // second output: same rows and channels from the accumulator next to the main one; no residual
+                const EpiParams ep2 = {p.bias2, nullptr, p.out2, p.Cout, p.relu2};
+                const uint4 none[4] = {};
+#pragma unroll 1
+                for (int i = 0; i < kChunksPerWarp; ++i) {
+                    const int c0 = c_base + i * 32;
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_addr + (uint32_t)(BN + i * 32), v);
+                    tmem_ld_wait();
+                    if (c0 < p.Cout) epilogue_coalesced_bf16<32>(ep2, v, c0, stage_tile, lane, rows, none, false);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -295,10 +344,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
     if (threadIdx.x == 0 && *abort_ptr && p.status != nullptr) atomicExch(p.status, KXC_B200_ERR_DEVICE_WAIT);
 }
 
-template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode, int kCtas>
+template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode, int kCtas, bool kDual = false>
 int32_t launch_one(const TcParams& p, cudaStream_t stream) {
     using G = StageGeom<KB_BYTES, BN, kCtas>;
-    auto kernel = conv_igemm_kernel<kKind, KB_BYTES, BN, kOutMode, kCtas>;
+    auto kernel = conv_igemm_kernel<kKind, KB_BYTES, BN, kOutMode, kCtas, kDual>;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     static int max_units[64] = {0};  // per device: CTAs (kCtas = 1) or clusters of two (kCtas = 2) resident at once
@@ -361,6 +410,14 @@ int32_t launch_by_out(const TcConfig& cfg, const TcParams& p, cudaStream_t s) {
 
 template <MmaKind kKind, int KB_BYTES>
 int32_t launch_by_bn(const TcConfig& cfg, const TcParams& p, cudaStream_t s) {
+    if constexpr (KB_BYTES == 128 && kKind == MmaKind::F16) {
+        if (cfg.dual) {
+            if (cfg.bn != 128 || cfg.ctas != 1 || cfg.out_mode != kOutNHWC_BF16 || !p.vec_ok || (p.Cout & 31) != 0)
+                return fail(KXC_B200_ERR_INVALID, "tensor-core conv: the two-output kernel needs a 128-wide tile, bf16 NHWC output and aligned pointers");
+            return launch_one<kKind, KB_BYTES, 128, kOutNHWC_BF16, 1, true>(p, s);
+        }
+    }
+    if (cfg.dual) return fail(KXC_B200_ERR_INVALID, "tensor-core conv: no two-output kernel for this configuration");
     if constexpr (KB_BYTES == 128) {
         if (cfg.ctas == 2) {  // pairs exist for the wide tiles only (tc_setup_conv)
             switch (cfg.bn) {
@@ -475,6 +532,31 @@ int32_t tc_status_word(int** out) {
         KXC_CUDA_TRY(cudaMemset(words[dev], 0, sizeof(int)));
     }
     *out = words[dev];
+    return KXC_B200_OK;
+}
+
+bool tc_dual_applicable(TcDType dtype, TcOutMode out_mode, int cpad, int Cout, int KH, int KW, int stride, int pad_h, int pad_w,
+                        int dil_h, int dil_w) {
+    // the second output's only tap must be the main filter's centre tap
+    return dtype == kTcBF16 && out_mode == kOutNHWC_BF16 && (cpad * 2) % 128 == 0 && Cout % 32 == 0 && (KH & 1) && (KW & 1) &&
+           dil_h == 1 && dil_w == 1 && pad_h == KH / 2 && pad_w == KW / 2 && (stride == 1 || stride == 2);
+}
+
+int32_t tc_setup_dual(TcParams* p, TcConfig* cfg, const void* act_nhwc, const void* w_packed, const void* w2_packed, int N,
+                      int H, int W, int cpad, int Cout, int KH, int KW, int stride, int pad_h, int pad_w) {
+    KXC_TRY(tc_setup_conv(p, cfg, kTcBF16, kOutNHWC_BF16, act_nhwc, w_packed, N, H, W, cpad, Cout, KH, KW, stride, pad_h, pad_w, 1, 1));
+    // the two accumulators of a buffer share TMEM: 128-wide tiles, single CTAs
+    const int bn = 128;
+    cfg->bn = bn; cfg->ctas = 1; cfg->dual = 1;
+    p->tiles_c = (Cout + bn - 1) / bn;
+    const uint64_t ktot = (uint64_t)KH * KW * cpad;
+    const uint64_t bdims[2] = {ktot, (uint64_t)Cout};
+    const uint64_t bstrides[1] = {ktot * 2};
+    const uint32_t bbox[2] = {(uint32_t)p->kb_elems, (uint32_t)bn};
+    KXC_TRY(tc_make_tmap(&p->tmB, kTcBF16, 2, const_cast<void*>(w_packed), bdims, bstrides, bbox, 128));
+    const uint64_t b2dims[2] = {(uint64_t)cpad, (uint64_t)Cout};
+    const uint64_t b2strides[1] = {(uint64_t)cpad * 2};
+    KXC_TRY(tc_make_tmap(&p->tmB2, kTcBF16, 2, const_cast<void*>(w2_packed), b2dims, b2strides, bbox, 128));
     return KXC_B200_OK;
 }
 

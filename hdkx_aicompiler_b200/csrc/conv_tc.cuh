@@ -53,6 +53,13 @@ struct alignas(64) TcParams {
     const void* aux_in;
     const void* aux_w;
     int aux_row_bytes, aux_hp;
+    // second output of the dual kernel: a 1x1 convolution of the same stride over the same input (the residual
+    // branch's downsample next to a block's first 3x3 stride-2 convolution); its reduction runs as extra K blocks
+    // over the centre tap's pixels into a second accumulator
+    CUtensorMap tmB2;
+    const float* bias2;
+    void* out2;
+    int relu2;
 };
 
 struct TcConfig {
@@ -61,6 +68,7 @@ struct TcConfig {
     int bn;        // 64, 128 or 256
     TcOutMode out_mode;
     int ctas = 1;  // 2: clusters of two CTAs share each B tile (tcgen05 cta_group::2, M = 256 per instruction)
+    int dual = 0;  // 1: also computes the 1x1 convolution described by tmB2 / bias2 / out2 / relu2
 };
 
 // Sets vec_ok from the epilogue pointers; call after filling bias/residual/out.
@@ -89,6 +97,14 @@ int32_t tc_status_word(int** out);
 int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_mode, const void* act_nhwc,
                       const void* w_packed, int N, int H, int W, int cpad, int Cout, int KH, int KW, int stride, int pad_h,
                       int pad_w, int dil_h, int dil_w, int* status_word = nullptr);
+
+// Whether a KHxKW convolution (stride, padding, dilation as given) can carry a 1x1 convolution of the same stride
+// and no padding as its second output, and the setup of that second output (call after tc_setup_conv, which it
+// re-runs with the dual kernel's 128-wide tile).
+bool tc_dual_applicable(TcDType dtype, TcOutMode out_mode, int cpad, int Cout, int KH, int KW, int stride, int pad_h, int pad_w,
+                        int dil_h, int dil_w);
+int32_t tc_setup_dual(TcParams* p, TcConfig* cfg, const void* act_nhwc, const void* w_packed, const void* w2_packed, int N,
+                      int H, int W, int cpad, int Cout, int KH, int KW, int stride, int pad_h, int pad_w);
 
 inline int tc_elem_bytes(TcDType t) { return t == kTcBF16 ? 2 : (t == kTcTF32 ? 4 : 1); }
 // Channel padding the tensor-core path needs for `c` input channels: one K block per tap must be

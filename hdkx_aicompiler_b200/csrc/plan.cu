@@ -84,6 +84,9 @@ struct Step {
     bool out_is_graph_output = false;
     int direct = 0;  // 0 = implicit-GEMM kernel; 1 = direct 3x3 kernel; 2 = direct stem kernel
     int fused_pool = 0;  // direct stem kernel only: the following max_pool2d(3x3, s2, p1) is computed in its epilogue
+    // second output (two-output implicit-GEMM kernel): a 1x1 convolution of the same stride over the same input
+    int weight2 = -1, bias2_const = -1, out2 = -1;
+    bool relu2 = false;
     // conv / gemm
     TcParams params{};
     TcConfig cfg{};
@@ -556,6 +559,68 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
     }
     std::stable_sort(pending.begin(), pending.end(), [](const auto& a, const auto& b) { return a.first < b.first; });
 
+    // ---- a block's first convolution and the 1x1 convolution of its residual branch read the same tensor with
+    // the same stride: compute both in one launch (the 1x1's only tap is the other filter's centre tap) ----
+    {
+        const char* e = getenv("KXC_B200_DUAL_CONV");  // "0" keeps two launches (A/B runs)
+        const bool enabled = dt == kTcBF16 && !(e && atoi(e) == 0);
+        auto geom = [&](const Step& st, int* kh, int* kw, int* stride, int* o) {
+            const PackedWeight& pw = pl->weights[st.weight];
+            *kh = pw.KH; *kw = pw.KW; *o = pw.O; *stride = st.pool.strides[0];
+        };
+        for (size_t a = 0; enabled && a < pending.size(); ++a) {
+            Step& A = pending[a].second;
+            if (A.kind != SKind::Conv || A.in1 >= 0 || A.fused_pool || A.weight2 >= 0 || is_input(A.in0) || A.Hp == 1) continue;
+            int akh, akw, as, ao;
+            geom(A, &akh, &akw, &as, &ao);
+            if (akh * akw == 1 || A.pool.strides[0] != A.pool.strides[1]) continue;
+            if (!tc_dual_applicable(dt, kOutNHWC_BF16, A.cpad, ao, akh, akw, as, A.pad_h, A.pad_w, A.pool.pool_size[0], A.pool.pool_size[1])) continue;
+            if (direct3x3_applicable(dt, A.C, ao, akh, akw, as, A.pad_h, A.pad_w, 1, 1, (int)pl->find(A.out)->shape[3])) continue;
+            if (pl->root_of(A.out) == pl->root_of(pl->output_id)) continue;
+            {   // The two accumulators limit the tile to 128 channels and single CTAs. Measured at 1024 images: for
+                // Cout = 128 one launch instead of two saves 25 % (0.260 -> 0.195 ms), for Cout >= 256 losing the 256-wide
+                // paired tile costs more than the second launch (0.145 -> 0.164 ms); with few tiles (128 images per
+                // GPU) the second launch's fixed cost dominates again (0.042 -> 0.031 ms).
+                const Value* ov = pl->find(A.out);
+                int bw, bh, bni;
+                tc_pick_tile(A.N, (int)ov->shape[2], (int)ov->shape[3], &bw, &bh, &bni);
+                const long long m_tiles = (long long)(((int)ov->shape[3] + bw - 1) / bw) * (((int)ov->shape[2] + bh - 1) / bh) *
+                                          ((A.N + bni - 1) / bni);
+                if (ao > 128 && m_tiles > 256) continue;
+            }
+            for (size_t b = 0; b < pending.size(); ++b) {
+                if (b == a) continue;
+                Step& B = pending[b].second;
+                if (B.kind != SKind::Conv || B.in0 != A.in0 || B.in1 >= 0 || B.fused_pool || B.weight2 >= 0) continue;
+                int bkh, bkw, bs, bo;
+                geom(B, &bkh, &bkw, &bs, &bo);
+                if (bkh != 1 || bkw != 1 || bs != as || B.pool.strides[0] != B.pool.strides[1] || bo != ao || B.pad_h != 0 || B.pad_w != 0 ||
+                    B.cpad != A.cpad || pl->root_of(B.out) == pl->root_of(pl->output_id))
+                    continue;
+                // B's result now appears where A is emitted: every user of it must come later
+                const int at = std::min(pending[a].first, pending[b].first);
+                bool ok = true;
+                for (size_t c = 0; c < pending.size(); ++c) {
+                    if (c == a || c == b) continue;
+                    const Step& U = pending[c].second;
+                    if ((U.in0 == B.out || U.in1 == B.out || U.in0 == A.out || U.in1 == A.out) && pending[c].first <= std::max(pending[a].first, pending[b].first)) ok = false;
+                }
+                if (!ok) continue;
+                A.weight2 = B.weight;
+                A.bias2_const = B.bias_const;
+                A.out2 = B.out;
+                A.relu2 = B.relu;
+                // emit at the later of the two positions: both only need the shared input, which is alive until then
+                pending[a].first = std::max(pending[a].first, pending[b].first);
+                (void)at;
+                pending.erase(pending.begin() + b);
+                if (b < a) --a;
+                break;
+            }
+        }
+        std::stable_sort(pending.begin(), pending.end(), [](const auto& x, const auto& y) { return x.first < y.first; });
+    }
+
     // input conversion steps go first
     for (auto& pr : pending) {
         Step& st = pr.second;
@@ -649,6 +714,11 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
             if (v->id >= 0) v->bytes = (size_t)numel_of(v->shape) * eb;
             touch(st.out);
         }
+        if (st.out2 != -1) {
+            Value* v = pl->find(st.out2);
+            v->bytes = (size_t)numel_of(v->shape) * eb;
+            touch(st.out2);
+        }
     }
     // greedy arena assignment with reuse of dead blocks
     struct Block { size_t off, size; };
@@ -656,8 +726,10 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
     size_t top = 0;
     for (size_t si = 0; si < pl->steps.size(); ++si) {
         Step& st = pl->steps[si];
-        if (st.out != -1 && !st.out_is_graph_output) {
-            Value* v = pl->find(st.out);
+        for (int which = 0; which < 2; ++which) {
+            const int oid = which == 0 ? ((st.out != -1 && !st.out_is_graph_output) ? st.out : -1) : st.out2;
+            if (oid == -1) continue;
+            Value* v = pl->find(oid);
             if (v->alias_of < 0 && !v->has_storage) {
                 const size_t need = align_up(std::max<size_t>(v->bytes, 16), 1024);
                 int best = -1;
@@ -743,6 +815,11 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
                     st.direct = 1;
                     KXC_TRY(direct3x3_setup(&st.params, pl->storage(st.in0), pw.ptr, st.N, st.H, st.W));
                     st.cfg = TcConfig{dt, 128, 64, om};
+                } else if (st.weight2 >= 0) {
+                    KXC_TRY(tc_setup_dual(&st.params, &st.cfg, pl->storage(st.in0), pw.ptr, pl->weights[st.weight2].ptr, st.N, st.H, st.W,
+                                          st.cpad, pw.O, pw.KH, pw.KW, st.pool.strides[0], st.pad_h, st.pad_w));
+                    st.params.out2 = pl->storage(st.out2);
+                    st.params.relu2 = st.relu2 ? 1 : 0;
                 } else
                 KXC_TRY(tc_setup_conv(&st.params, &st.cfg, dt, om, pl->storage(st.in0), pw.ptr, st.N, st.H, st.W, st.cpad, pw.O,
                                       pw.KH, pw.KW, st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0], st.pool.pool_size[1]));
@@ -815,8 +892,10 @@ static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream
             case SKind::Gemm: {
                 TcParams p = st.params;
                 p.bias = st.bias_const >= 0 ? static_cast<const float*>(arg_of(st.bias_const)) : nullptr;
+                p.bias2 = st.bias2_const >= 0 ? static_cast<const float*>(arg_of(st.bias2_const)) : nullptr;
                 if (st.out_is_graph_output) p.out = out_ptr;
                 tc_finish_params(&p);
+                if (st.weight2 >= 0 && ((reinterpret_cast<uintptr_t>(p.bias2) | reinterpret_cast<uintptr_t>(p.out2)) & 15u)) p.vec_ok = 0;
                 if (st.direct == 2) {
                     KXC_TRY(st.fused_pool ? stem_pool_launch(p, s) : stem_direct_launch(p, s));
                 } else if (st.direct == 1) {
@@ -959,12 +1038,13 @@ extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, c
             const TcParams& p = st.params;
             const double out_elems = (double)p.N * p.OH * p.OW * w.O;
             fl = 2.0 * out_elems * w.C * w.KH * w.KW;  // padded taps counted, as the reference executes them
+            if (st.weight2 >= 0) fl += 2.0 * out_elems * w.C;  // the 1x1 convolution computed by the same launch
             const double in_bytes = (w.mode == 1 || w.mode == 4) ? (double)st.N * st.Hp * st.Wp * 4 * eb : (double)st.N * st.H * st.W * st.cpad * eb;
             by = in_bytes + (double)w.bytes + out_elems * (st.fused_pool ? 0.25 : 1.0) * (st.out_is_graph_output ? 4.0 : eb) +
                  (st.in1 >= 0 ? out_elems * eb : 0.0) + 4.0 * w.O;
             snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d%s", st.direct == 2 ? (st.fused_pool ? "conv_stem_pool" : "conv_stem_direct") : (st.direct ? "conv_direct" : "conv_igemm"), w.C, st.H, st.W, w.O, w.KH, w.KW,
                      p.stride, st.in1 >= 0 ? " +res" : "", st.relu ? " +relu" : "", p.BNI, p.BH, p.BW, st.cfg.bn,
-                     st.cfg.ctas == 2 ? " pair" : "");
+                     st.cfg.ctas == 2 ? " pair" : (st.weight2 >= 0 ? " +1x1 second output" : ""));
             break;
         }
         case SKind::Gemm: {

@@ -172,8 +172,9 @@ def test_resnet18_plan(kxc, precision):
     func = rs.build(N, weights, to_constant=cuda_const)
     got, g = run_plan(kxc, func, x, precision)
     assert got.shape == (N, 1000)
-    # stem pack + 20 fused convs (the stem one also does the max pool in bf16 mode) + gap + dense; flatten is a view
-    assert g.num_launches == (23 if precision == "bf16" else 24)
+    # stem pack + 20 fused convs (in bf16 mode the stem one also does the max pool and each of the three 1x1
+    # downsample convolutions rides in its block's first 3x3 launch) + gap + dense; flatten is a view
+    assert g.num_launches == (20 if precision == "bf16" else 24)
     hf = rs.build(N, weights)
     exact = ograph.run(hf, [x], workers=8)
     scale = float(np.abs(exact).max())
@@ -222,6 +223,42 @@ def test_stem_pool_fusion_is_bit_identical(kxc, monkeypatch):
     exp = port.relu(port.max_pool2d(conv, (3, 3), (2, 2), (1, 1, 1, 1)))
     # pooling picks stored bf16 values: only where the fp32 sums straddle a bf16 rounding boundary can a value differ
     assert np.mean(fused != exp) < 1e-3 and np.abs(fused - exp).max() <= 2.0 ** -7 * np.abs(exp).max()
+
+
+@pytest.mark.parametrize("cin,cout,hw", [(64, 128, 56), (128, 256, 28), (64, 64, 30)])
+def test_downsample_block_two_output_kernel_is_bit_identical(kxc, monkeypatch, cin, cout, hw):
+    """A ResNet downsample block: conv3x3(s2)+relu and the residual branch's conv1x1(s2) read the same tensor and
+    are computed by ONE launch (second accumulator over the centre tap); the bits equal those of two launches."""
+    R = kxc.relay
+    rng = np.random.default_rng(21)
+    N = 3
+    x = rng.normal(0, 1, (N, cin, hw, hw)).astype(f32)
+    w0 = rng.normal(0, (2 / (cin * 9)) ** 0.5, (cin, cin, 3, 3)).astype(f32)   # a layer in front: the shared tensor is internal
+    w1 = rng.normal(0, (2 / (cin * 9)) ** 0.5, (cout, cin, 3, 3)).astype(f32)
+    w2 = rng.normal(0, (2 / (cout * 9)) ** 0.5, (cout, cout, 3, 3)).astype(f32)
+    wd = rng.normal(0, (2 / cin) ** 0.5, (cout, cin, 1, 1)).astype(f32)
+    b0, b1, b2, bd = (rng.normal(0, 0.1, (c,)).astype(f32) for c in (cin, cout, cout, cout))
+
+    def build(to):
+        xv = R.Var("input", x.shape)
+        conv = lambda d, w, b, s, p: R.Call("nn_conv2d", [d, R.Constant(to(w)), R.Constant(to(b))],
+                                            R.Conv2DAttrs((s, s), (p, p, p, p), (1, 1), 1))
+        t = R.Call("nn_relu", [conv(xv, w0, b0, 1, 1)])
+        y = R.Call("nn_relu", [conv(t, w1, b1, 2, 1)])
+        y = conv(y, w2, b2, 1, 1)
+        d = conv(t, wd, bd, 2, 0)
+        out = R.Call("nn_relu", [R.Call("add", [y, d])])
+        return R.Function([xv], R.Call("nn_global_avg_pool2d", [out]))
+
+    monkeypatch.setenv("KXC_B200_DUAL_CONV", "1")
+    fused, gf = run_plan(kxc, build(cuda_const), x, "bf16")
+    monkeypatch.setenv("KXC_B200_DUAL_CONV", "0")
+    unfused, gu = run_plan(kxc, build(cuda_const), x, "bf16")
+    assert gf.num_launches == gu.num_launches - 1
+    assert any("second output" in l[0] for l in gf.launch_info())
+    assert np.array_equal(fused, unfused)
+    emu = ograph.run(build(lambda a: a), [x], operand_round=port.round_bf16, workers=4)
+    assert_close(fused, emu, 2e-2, "downsample block vs same-rounding oracle")
 
 
 @pytest.mark.parametrize("precision", ["bf16", "tf32"])
