@@ -33,9 +33,10 @@ using namespace sm100;
 constexpr int kTcThreads = 320;  // 2 control warps + 8 epilogue warps
 constexpr int kSmemLimit = 227 * 1024;
 
-template <int KB_BYTES, int BN, int kCtas>
+template <int KB_BYTES, int BN, int kCtas, int kMT = 1>
 struct StageGeom {
-    static constexpr int kABytes = 128 * KB_BYTES;
+    static constexpr int kATileBytes = 128 * KB_BYTES;
+    static constexpr int kABytes = kMT * kATileBytes;  // kMT pixel tiles share one B tile
     static constexpr int kBBytes = (BN / kCtas) * KB_BYTES;  // a CTA of a pair holds half of the B tile's rows
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kEpilogueBytes = 8 * kStageTileBytes;  // one staging tile per epilogue warp
@@ -53,13 +54,21 @@ struct StageGeom {
 // kDual: a second output, the 1x1 convolution of the same stride over the same input (TcParams::tmB2 ...). Its
 // reduction is appended to the K loop as `cblocks` extra stages that load the centre tap's pixels again together
 // with the second weight tensor's rows and accumulate into a second TMEM accumulator; the epilogue drains both.
-template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode, int kCtas, bool kDual = false>
+//
+// kMT = 2: a work item is TWO pixel tiles per CTA against one B tile. Their MMAs alternate between two
+// accumulators, which gives the tensor core two independent accumulate chains (a pair's M = 256 instruction has
+// a long dependent-issue latency) and halves the B traffic per pixel.
+template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode, int kCtas, bool kDual = false, int kMT = 1>
 __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_constant__ TcParams p) {
-    using G = StageGeom<KB_BYTES, BN, kCtas>;
+    using G = StageGeom<KB_BYTES, BN, kCtas, kMT>;
+    static_assert(!(kDual && kMT != 1), "the two-output kernel works on one pixel tile at a time");
     constexpr bool kPair = kCtas == 2;
     constexpr int kStages = G::kStages;
-    constexpr int kAccCols = kDual ? 2 * BN : BN;  // TMEM columns of one accumulator buffer (main [+ second output])
-    constexpr uint32_t kTmemCols = 2 * kAccCols;   // two buffers; 128, 256 or 512: a power of two
+    constexpr int kAccCols = (kDual ? 2 : kMT) * BN;  // TMEM columns of one accumulator buffer
+    // two accumulator buffers (the epilogue of one work item overlaps the next item's main loop) where TMEM's 512
+    // columns allow it, else one
+    constexpr int kBufs = 2 * kAccCols <= 512 ? 2 : 1;
+    constexpr uint32_t kTmemCols = kBufs * kAccCols;  // 128, 256 or 512: a power of two
     static_assert(kTmemCols <= 512, "TMEM has 512 columns");
     static_assert(!kDual || (!kPair && kOutMode == kOutNHWC_BF16), "the dual kernel exists for single CTAs and bf16 NHWC output");
     constexpr uint32_t kIdesc =
@@ -114,7 +123,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
     // Work items: (channel tile, group of kCtas consecutive pixel tiles). A pair whose second pixel tile
     // does not exist loads a box beyond the last image (all zeros) and stores nothing for it.
     const int m_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
-    const int total_tiles = p.tiles_c * ((m_tiles + kCtas - 1) / kCtas);
+    const int total_tiles = p.tiles_c * ((m_tiles + kCtas * kMT - 1) / (kCtas * kMT));
     const int first_tile = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int tile_step = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     const int rows_used = p.BW * p.BH * p.BNI;
@@ -125,31 +134,34 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
             tma_prefetch_desc(&p.tmB);
             tma_prefetch_desc(&p.tmA[0]);
             if constexpr (kDual) tma_prefetch_desc(&p.tmB2);
-            const uint32_t tx_bytes = (uint32_t)(rows_used * KB_BYTES + G::kBBytes);
+            const uint32_t tx_bytes = (uint32_t)(kMT * rows_used * KB_BYTES + G::kBBytes);
             pdl_wait();  // the activations come from the previous kernel
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
-                int r = tile;
-                const int ct = r % p.tiles_c; r /= p.tiles_c;
-                r = r * kCtas + (int)cta_rank;
-                const int tw = r % p.tiles_w; r /= p.tiles_w;
-                const int th = r % p.tiles_h;
-                const int tn = r / p.tiles_h;
-                const int ow0 = tw * p.BW, oh0 = th * p.BH, n0 = tn * p.BNI;
+                const int ct = tile % p.tiles_c;
+                int ow0[kMT], oh0[kMT], n0[kMT];
+#pragma unroll
+                for (int t = 0; t < kMT; ++t) {
+                    int r = ((tile / p.tiles_c) * kCtas + (int)cta_rank) * kMT + t;
+                    const int tw = r % p.tiles_w; r /= p.tiles_w;
+                    const int th = r % p.tiles_h;
+                    const int tn = r / p.tiles_h;
+                    ow0[t] = tw * p.BW; oh0[t] = th * p.BH; n0[t] = tn * p.BNI;
+                }
                 const int co0 = ct * BN + (int)cta_rank * (BN / kCtas);
                 int kb = 0;
                 for (int kh = 0; ok && kh < p.taps_h; ++kh) {
                     for (int kw = 0; ok && kw < p.taps_w; ++kw) {
                         const int dh = kh * p.dil_h - p.pad_h;
                         const int dw = kw * p.dil_w - p.pad_w;
-                        int map = 0, ch = oh0 + dh, cw = ow0 + dw;
+                        int map = 0, ch = dh, cw = dw;  // offsets of this tap's box from the tile's first pixel
                         if (p.stride == 2) {
                             const int hp = dh & 1, wp = dw & 1;
                             map = hp * 2 + wp;
-                            ch = oh0 + ((dh - hp) >> 1);
-                            cw = ow0 + ((dw - wp) >> 1);
+                            ch = (dh - hp) >> 1;
+                            cw = (dw - wp) >> 1;
                         }
                         for (int cb = 0; cb < p.cblocks; ++cb, ++kb) {
                             if (!mbar_wait_bounded(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr)) {
@@ -161,11 +173,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                             if constexpr (kPair) {
                                 if (leader) mbar_arrive_expect_tx(full, 2u * tx_bytes);
                                 const uint32_t full0 = map_to_cta(full, 0);
-                                tma_load_4d_pair(a_dst, &p.tmA[map], full0, cb * p.kb_elems, cw, ch, n0);
+#pragma unroll
+                                for (int t = 0; t < kMT; ++t)
+                                    tma_load_4d_pair(a_dst + t * G::kATileBytes, &p.tmA[map], full0, cb * p.kb_elems, ow0[t] + cw,
+                                                     oh0[t] + ch, n0[t]);
                                 tma_load_2d_pair(a_dst + G::kABytes, &p.tmB, full0, kb * p.kb_elems, co0);
                             } else {
                                 mbar_arrive_expect_tx(full, tx_bytes);
-                                tma_load_4d(a_dst, &p.tmA[map], full, cb * p.kb_elems, cw, ch, n0);
+#pragma unroll
+                                for (int t = 0; t < kMT; ++t)
+                                    tma_load_4d(a_dst + t * G::kATileBytes, &p.tmA[map], full, cb * p.kb_elems, ow0[t] + cw, oh0[t] + ch,
+                                                n0[t]);
                                 tma_load_2d(a_dst + G::kABytes, &p.tmB, full, kb * p.kb_elems, co0);
                             }
                             if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -175,12 +193,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                 if constexpr (kDual) {
                     // second output: the centre tap's pixels (the 1x1 convolution's only tap) against tmB2
                     const int dh = (p.taps_h / 2) * p.dil_h - p.pad_h, dw = (p.taps_w / 2) * p.dil_w - p.pad_w;  // 0, 0
-                    int map = 0, ch = oh0 + dh, cw = ow0 + dw;
+                    int map = 0, ch = oh0[0] + dh, cw = ow0[0] + dw;
                     if (p.stride == 2) {
                         const int hp = dh & 1, wp = dw & 1;
                         map = hp * 2 + wp;
-                        ch = oh0 + ((dh - hp) >> 1);
-                        cw = ow0 + ((dw - wp) >> 1);
+                        ch = oh0[0] + ((dh - hp) >> 1);
+                        cw = ow0[0] + ((dw - wp) >> 1);
                     }
                     for (int cb = 0; ok && cb < p.cblocks; ++cb) {
                         if (!mbar_wait_bounded(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr)) {
@@ -190,7 +208,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                         const uint32_t full = smem_u32(&bar_full[stage]);
                         const uint32_t a_dst = ring + (uint32_t)stage * G::kStageBytes;
                         mbar_arrive_expect_tx(full, tx_bytes);
-                        tma_load_4d(a_dst, &p.tmA[map], full, cb * p.kb_elems, cw, ch, n0);
+                        tma_load_4d(a_dst, &p.tmA[map], full, cb * p.kb_elems, cw, ch, n0[0]);
                         tma_load_2d(a_dst + G::kABytes, &p.tmB2, full, cb * p.kb_elems, co0);
                         if (++stage == kStages) { stage = 0; phase ^= 1u; }
                     }
@@ -223,13 +241,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                     const uint64_t b_desc = make_smem_desc(a_addr + G::kABytes, KB_BYTES);
 #pragma unroll
                     for (int k = 0; k < KB_BYTES / 32; ++k) {
-                        // advancing 32 bytes along K inside the swizzle span = +2 in the (addr >> 4) field
-                        if constexpr (kPair)
-                            umma_pair<kKind>(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), kIdesc,
-                                             (kb_local | k) != 0 ? 1u : 0u);
-                        else
-                            umma<kKind>(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), kIdesc,
-                                        (kb_local | k) != 0 ? 1u : 0u);
+#pragma unroll
+                        for (int t = 0; t < kMT; ++t) {
+                            // advancing 32 bytes along K inside the swizzle span = +2 in the (addr >> 4) field;
+                            // the next pixel tile of the stage is kATileBytes further on
+                            const uint64_t a_k = a_desc + (uint64_t)(2 * k) + (uint64_t)(t * (G::kATileBytes >> 4));
+                            const uint32_t d_t = d_tmem + (uint32_t)(t * BN);
+                            if constexpr (kPair)
+                                umma_pair<kKind>(d_t, a_k, b_desc + (uint64_t)(2 * k), kIdesc, (kb_local | k) != 0 ? 1u : 0u);
+                            else
+                                umma<kKind>(d_t, a_k, b_desc + (uint64_t)(2 * k), kIdesc, (kb_local | k) != 0 ? 1u : 0u);
+                        }
                     }
                     if constexpr (kPair) umma_commit_pair(smem_u32(&bar_empty[stage]), 3);
                     else umma_commit(smem_u32(&bar_empty[stage]));
@@ -238,8 +260,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                 if (!ok) break;
                 if constexpr (kPair) umma_commit_pair(smem_u32(&bar_acc_full[acc]), 3);
                 else umma_commit(smem_u32(&bar_acc_full[acc]));
-                acc ^= 1;
-                if (acc == 0) acc_phase ^= 1u;
+                if (++acc == kBufs) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
             }
         }
     } else {
@@ -260,10 +284,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
         pdl_wait();  // residual reads and output writes must not overtake earlier kernels
         int acc = 0;
         uint32_t acc_phase = 0;
-        for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
-            int r = tile;
-            const int ct = r % p.tiles_c; r /= p.tiles_c;
-            r = r * kCtas + (int)cta_rank;
+        bool alive = true;
+        for (int tile = first_tile; alive && tile < total_tiles; tile += tile_step) {
+          const int ct = tile % p.tiles_c;
+#pragma unroll 1
+          for (int t = 0; t < kMT; ++t) {
+            int r = ((tile / p.tiles_c) * kCtas + (int)cta_rank) * kMT + t;
             const int tw = r % p.tiles_w; r /= p.tiles_w;
             const int th = r % p.tiles_h;
             const int tn = r / p.tiles_h;
@@ -278,11 +304,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                 rows = make_row_map(pix, valid, lane);
                 if (has_res && c_base < p.Cout) residual_fetch_rows(ep, rows, c_base, lane, res_cur);
             }
-            bool ok = mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols + col0);
+            if (t == 0) {
+                bool ok = mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    alive = false;
+                    break;
+                }
+                tc_fence_after_sync();
+            }
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccCols + t * BN + col0);
 #pragma unroll 1
             for (int i = 0; i < kChunksPerWarp; ++i) {
                 const int c0 = c_base + i * 32;
@@ -313,14 +344,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                     if (c0 < p.Cout) epilogue_coalesced_bf16<32>(ep2, v, c0, stage_tile, lane, rows, none, false);
                 }
             }
+          }  // pixel tiles of the work item
+            if (!alive) break;
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
                 if constexpr (kPair) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_acc_empty[acc]), 0));
                 else mbar_arrive(smem_u32(&bar_acc_empty[acc]));
             }
-            acc ^= 1;
-            if (acc == 0) acc_phase ^= 1u;
+            if (++acc == kBufs) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
         }
     }
 
@@ -344,10 +379,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
     if (threadIdx.x == 0 && *abort_ptr && p.status != nullptr) atomicExch(p.status, KXC_B200_ERR_DEVICE_WAIT);
 }
 
-template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode, int kCtas, bool kDual = false>
+template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode, int kCtas, bool kDual = false, int kMT = 1>
 int32_t launch_one(const TcParams& p, cudaStream_t stream) {
-    using G = StageGeom<KB_BYTES, BN, kCtas>;
-    auto kernel = conv_igemm_kernel<kKind, KB_BYTES, BN, kOutMode, kCtas, kDual>;
+    using G = StageGeom<KB_BYTES, BN, kCtas, kMT>;
+    auto kernel = conv_igemm_kernel<kKind, KB_BYTES, BN, kOutMode, kCtas, kDual, kMT>;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     static int max_units[64] = {0};  // per device: CTAs (kCtas = 1) or clusters of two (kCtas = 2) resident at once
@@ -357,7 +392,7 @@ int32_t launch_one(const TcParams& p, cudaStream_t stream) {
     if (attr_err != cudaSuccess)
         return fail(KXC_B200_ERR_CUDA, "cudaFuncSetAttribute(smem=%d): %s", G::kSmemBytes, cudaGetErrorString(attr_err));
     const long long m_tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n;
-    const long long tiles = (long long)p.tiles_c * ((m_tiles + kCtas - 1) / kCtas);
+    const long long tiles = (long long)p.tiles_c * ((m_tiles + kCtas * kMT - 1) / (kCtas * kMT));
     if (tiles <= 0) return KXC_B200_OK;
     int units = kNumSMs;
     if constexpr (kCtas == 2) {
@@ -418,6 +453,15 @@ int32_t launch_by_bn(const TcConfig& cfg, const TcParams& p, cudaStream_t s) {
         }
     }
     if (cfg.dual) return fail(KXC_B200_ERR_INVALID, "tensor-core conv: no two-output kernel for this configuration");
+    if constexpr (KB_BYTES == 128 && kKind == MmaKind::F16) {
+        if (cfg.mt == 2) {
+            if (cfg.bn != 128 || cfg.out_mode != kOutNHWC_BF16)
+                return fail(KXC_B200_ERR_INVALID, "tensor-core conv: two pixel tiles per work item exist for the 128-wide bf16 NHWC kernel");
+            return cfg.ctas == 2 ? launch_one<kKind, KB_BYTES, 128, kOutNHWC_BF16, 2, false, 2>(p, s)
+                                 : launch_one<kKind, KB_BYTES, 128, kOutNHWC_BF16, 1, false, 2>(p, s);
+        }
+    }
+    if (cfg.mt != 1) return fail(KXC_B200_ERR_INVALID, "tensor-core conv: no multi-tile kernel for this configuration");
     if constexpr (KB_BYTES == 128) {
         if (cfg.ctas == 2) {  // pairs exist for the wide tiles only (tc_setup_conv)
             switch (cfg.bn) {
@@ -597,6 +641,15 @@ int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_m
     static const bool pair_all = [] { const char* e = getenv("KXC_B200_CTA_PAIR"); return e != nullptr && e[0] == '2'; }();
     const int ctas = (pair_enabled && bn >= (pair_all ? 128 : 256) && kb_bytes == 128 && m_tiles >= 2) ? 2 : 1;
     cfg->dtype = dtype; cfg->kb_bytes = kb_bytes; cfg->bn = bn; cfg->out_mode = out_mode; cfg->ctas = ctas;
+    // Two pixel tiles per work item for the 128-wide bf16 tile: measured 0.285/0.277/0.284 -> 0.231/0.221/0.234 ms on the
+    // 128->128 layers (the tensor core then sits on its operand-fetch bound: 8 KB per instruction at ~64 B/clk). With the
+    // 256-wide tile TMEM holds only one buffer of two accumulators and the lost epilogue overlap costs more than the
+    // second chain brings (0.168 -> 0.211 ms), so that form is not instantiated. KXC_B200_MT=1 switches it off.
+    static const bool mt_enabled = [] {
+        const char* e = getenv("KXC_B200_MT");
+        return !(e != nullptr && e[0] == '1');
+    }();
+    cfg->mt = (mt_enabled && bn == 128 && dtype == kTcBF16 && out_mode == kOutNHWC_BF16 && kb_bytes == 128 && m_tiles >= 2 * ctas) ? 2 : 1;
     p->tiles_c = (Cout + bn - 1) / bn;
 
     const uint32_t box[4] = {(uint32_t)p->kb_elems, (uint32_t)p->BW, (uint32_t)p->BH, (uint32_t)p->BNI};

@@ -69,6 +69,7 @@ struct TcConfig {
     TcOutMode out_mode;
     int ctas = 1;  // 2: clusters of two CTAs share each B tile (tcgen05 cta_group::2, M = 256 per instruction)
     int dual = 0;  // 1: also computes the 1x1 convolution described by tmB2 / bias2 / out2 / relu2
+    int mt = 1;    // 2: two pixel tiles per work item share each B tile (two accumulate chains in flight)
 };
 
 // Sets vec_ok from the epilogue pointers; call after filling bias/residual/out.

@@ -1044,7 +1044,7 @@ extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, c
                  (st.in1 >= 0 ? out_elems * eb : 0.0) + 4.0 * w.O;
             snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d%s", st.direct == 2 ? (st.fused_pool ? "conv_stem_pool" : "conv_stem_direct") : (st.direct ? "conv_direct" : "conv_igemm"), w.C, st.H, st.W, w.O, w.KH, w.KW,
                      p.stride, st.in1 >= 0 ? " +res" : "", st.relu ? " +relu" : "", p.BNI, p.BH, p.BW, st.cfg.bn,
-                     st.cfg.ctas == 2 ? " pair" : (st.weight2 >= 0 ? " +1x1 second output" : ""));
+                     st.cfg.ctas == 2 ? " pair" : (st.weight2 >= 0 ? " +1x1 second output" : (st.cfg.mt == 2 ? " x2 tiles" : "")));
             break;
         }
         case SKind::Gemm: {
