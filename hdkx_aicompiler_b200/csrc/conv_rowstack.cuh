@@ -1,0 +1,18 @@
+// 3x3 stride-1 convolution for 64 -> 64 channel bf16 NHWC layers with the three filter rows stacked along the MMA's
+// N dimension (12 instructions of N = 192 per tile instead of 36 of N = 64). See conv_rowstack.cu.
+#pragma once
+
+#include "conv_tc.cuh"
+
+namespace kxc_b200 {
+
+bool rowstack3x3_applicable(TcDType dtype, int C, int O, int KH, int KW, int stride, int pad_h, int pad_w, int dil_h, int dil_w,
+                            int H, int W);
+// Fills geometry and tensor maps of `p` (epilogue pointers are the caller's, as for tc_setup_conv).
+int32_t rowstack3x3_setup(TcParams* p, const void* act_nhwc, const void* w_packed, int N, int H, int W);
+// Builds the tensor maps of the residual (loads) and output (stores) tensors from p->residual / p->out; call once
+// those pointers are final, before the first launch.
+int32_t rowstack3x3_bind(TcParams* p);
+int32_t rowstack3x3_launch(const TcParams& p, cudaStream_t stream);
+
+}  // namespace kxc_b200

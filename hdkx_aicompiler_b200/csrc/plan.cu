@@ -29,6 +29,7 @@
 
 #include "common.cuh"
 #include "conv_direct.cuh"
+#include "conv_rowstack.cuh"
 #include "conv_stem.cuh"
 #include "conv_tc.cuh"
 #include "layout.cuh"
@@ -809,7 +810,14 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
                     return fail(KXC_B200_ERR_UNSUPPORTED, "plan: nn_conv2d with different strides in h and w");
                 const char* dmode = getenv("KXC_B200_DIRECT3X3");  // "0" selects the implicit-GEMM kernel for A/B runs
                 const int direct_mode = dmode ? atoi(dmode) : 1;
-                if (direct_mode > 0 && !st.out_is_graph_output &&
+                const char* rmode = getenv("KXC_B200_ROWSTACK");  // "0" keeps the tap-by-tap direct kernel (A/B runs)
+                if (direct_mode > 0 && (!rmode || atoi(rmode) != 0) && !st.out_is_graph_output &&
+                    rowstack3x3_applicable(dt, st.C, pw.O, pw.KH, pw.KW, st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0],
+                                           st.pool.pool_size[1], st.H, st.W)) {
+                    st.direct = 3;
+                    KXC_TRY(rowstack3x3_setup(&st.params, pl->storage(st.in0), pw.ptr, st.N, st.H, st.W));
+                    st.cfg = TcConfig{dt, 128, 64, om};
+                } else if (direct_mode > 0 && !st.out_is_graph_output &&
                     direct3x3_applicable(dt, st.C, pw.O, pw.KH, pw.KW, st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0],
                                          st.pool.pool_size[1], (int)ov->shape[3])) {
                     st.direct = 1;
@@ -828,6 +836,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
             st.params.round_out_tf32 = (!st.out_is_graph_output && dt == kTcTF32) ? 1 : 0;
             st.params.residual = st.in1 >= 0 ? pl->storage(st.in1) : nullptr;
             st.params.out = st.out_is_graph_output ? nullptr : pl->storage(st.out);
+            if (st.direct == 3) KXC_TRY(rowstack3x3_bind(&st.params));
             (void)ov;
         } else if (st.kind == SKind::Gemm) {
             const PackedWeight& pw = pl->weights[st.weight];
@@ -898,6 +907,8 @@ static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream
                 if (st.weight2 >= 0 && ((reinterpret_cast<uintptr_t>(p.bias2) | reinterpret_cast<uintptr_t>(p.out2)) & 15u)) p.vec_ok = 0;
                 if (st.direct == 2) {
                     KXC_TRY(st.fused_pool ? stem_pool_launch(p, s) : stem_direct_launch(p, s));
+                } else if (st.direct == 3) {
+                    KXC_TRY(rowstack3x3_launch(p, s));
                 } else if (st.direct == 1) {
                     KXC_TRY(direct3x3_launch(p, s));
                 } else {
@@ -1042,7 +1053,7 @@ extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, c
             const double in_bytes = (w.mode == 1 || w.mode == 4) ? (double)st.N * st.Hp * st.Wp * 4 * eb : (double)st.N * st.H * st.W * st.cpad * eb;
             by = in_bytes + (double)w.bytes + out_elems * (st.fused_pool ? 0.25 : 1.0) * (st.out_is_graph_output ? 4.0 : eb) +
                  (st.in1 >= 0 ? out_elems * eb : 0.0) + 4.0 * w.O;
-            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d%s", st.direct == 2 ? (st.fused_pool ? "conv_stem_pool" : "conv_stem_direct") : (st.direct ? "conv_direct" : "conv_igemm"), w.C, st.H, st.W, w.O, w.KH, w.KW,
+            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d%s", st.direct == 2 ? (st.fused_pool ? "conv_stem_pool" : "conv_stem_direct") : (st.direct == 3 ? "conv_rowstack" : (st.direct ? "conv_direct" : "conv_igemm")), w.C, st.H, st.W, w.O, w.KH, w.KW,
                      p.stride, st.in1 >= 0 ? " +res" : "", st.relu ? " +relu" : "", p.BNI, p.BH, p.BW, st.cfg.bn,
                      st.cfg.ctas == 2 ? " pair" : (st.weight2 >= 0 ? " +1x1 second output" : (st.cfg.mt == 2 ? " x2 tiles" : "")));
             break;

@@ -137,6 +137,41 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap
         : "memory");
 }
 
+// ---- TMA store (shared -> global, tiled) and the bulk async-group bookkeeping of the issuing thread ----------
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(m)),
+                 "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest kPending groups of this thread have finished READING their shared-memory source
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+// all groups of this thread are complete (their global writes performed)
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// generic-proxy writes to shared memory become visible to the async proxy (TMA)
+__device__ __forceinline__ void fence_proxy_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// barrier among `count` threads of the CTA (ids 1..15; id 0 is __syncthreads)
+__device__ __forceinline__ void named_barrier(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// the same, and every thread learns whether ANY of them passed a true predicate (a uniform decision to leave a loop)
+__device__ __forceinline__ bool named_barrier_or(int id, int count, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %3, 0;\n\t"
+        "bar.red.or.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(id), "r"(count), "r"((uint32_t)pred)
+        : "memory");
+    return r != 0;
+}
+
 // ---- tensor memory -----------------------------------------------------------------------------
 // Whole-warp, converged. `ncols` is a power of two in [32, 512]; the base address lands in shared memory.
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {

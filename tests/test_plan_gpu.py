@@ -261,6 +261,50 @@ def test_downsample_block_two_output_kernel_is_bit_identical(kxc, monkeypatch, c
     assert_close(fused, emu, 2e-2, "downsample block vs same-rounding oracle")
 
 
+@pytest.mark.parametrize("n,h,w", [(2, 56, 56), (3, 30, 20), (1, 7, 5), (2, 14, 8), (1, 15, 9)])
+def test_64_channel_3x3_kernels_agree(kxc, monkeypatch, n, h, w):
+    """Two 64 -> 64 3x3 layers (+bias, +relu, the second with a residual) through the row-stacked kernel (three filter
+    rows per MMA, rows recombined in the epilogue), the tap-by-tap direct kernel and the general implicit-GEMM kernel:
+    same operands and fp32 accumulation, only the summation order differs; all against the same-rounding oracle.
+    Ragged sizes exercise the zero-filled borders and the partial last tiles."""
+    R = kxc.relay
+    rng = np.random.default_rng(5)
+    x = rng.uniform(-1, 1, (n, 64, h, w)).astype(f32)
+    ws = [rng.normal(0, (2 / 576) ** 0.5, (64, 64, 3, 3)).astype(f32) for _ in range(3)]
+    bs = [rng.normal(0, 0.1, (64,)).astype(f32) for _ in range(3)]
+
+    def build(to):
+        xv = R.Var("input", x.shape)
+        conv = lambda d, i: R.Call("nn_conv2d", [d, R.Constant(to(ws[i])), R.Constant(to(bs[i]))],
+                                   R.Conv2DAttrs((1, 1), (1, 1, 1, 1), (1, 1), 1))
+        y0 = R.Call("nn_relu", [conv(xv, 0)])
+        y1 = R.Call("nn_relu", [conv(y0, 1)])
+        y2 = R.Call("nn_relu", [R.Call("add", [conv(y1, 2), y0])])
+        return R.Function([xv], R.Call("nn_relu", [y2]))  # a trailing op: y2 stays an internal NHWC tensor
+
+    outs = {}
+    for name, env in (("rowstack", {"KXC_B200_ROWSTACK": "1", "KXC_B200_DIRECT3X3": "1"}),
+                      ("direct", {"KXC_B200_ROWSTACK": "0", "KXC_B200_DIRECT3X3": "1"}),
+                      ("igemm", {"KXC_B200_ROWSTACK": "0", "KXC_B200_DIRECT3X3": "0"})):
+        for k, v in env.items():
+            monkeypatch.setenv(k, v)
+        outs[name], g = run_plan(kxc, build(cuda_const), x, "bf16")
+        kinds = [l[0].split()[0] for l in g.launch_info()]
+        if name == "rowstack":
+            assert kinds.count("conv_rowstack") == 3
+        elif name == "igemm":
+            assert "conv_rowstack" not in kinds and "conv_direct" not in kinds
+    emu = ograph.run(build(lambda a: a), [x], operand_round=port.round_bf16, workers=4)
+    scale = float(np.abs(emu).max())
+    for name, got in outs.items():
+        err = float(np.abs(got - emu).max())
+        assert err <= 2e-2 * scale, f"{name}: max_abs {err:.3e} against the same-rounding oracle (scale {scale:.2f})"
+    # the three kernels see identical bf16 operands; their outputs differ by summation order and the bf16 rounding of
+    # the intermediate activations it can flip
+    assert float(np.abs(outs["rowstack"] - outs["igemm"]).max()) <= 2e-2 * scale
+    assert float(np.abs(outs["direct"] - outs["igemm"]).max()) <= 2e-2 * scale
+
+
 @pytest.mark.parametrize("precision", ["bf16", "tf32"])
 def test_resnet18_stem_plan(kxc, precision):
     """The packed-stem path alone (7x7 stride-2 convolution over 3 channels + bias + relu): against the oracle on
