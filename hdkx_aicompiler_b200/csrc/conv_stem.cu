@@ -217,21 +217,24 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __g
 // ------------------------------------------------------------------------------------------------------
 // Stem convolution + bias + ReLU + max_pool2d(3x3, stride 2, pad 1) in one kernel.
 //
-// The convolution's output (the largest activation of the network) never goes to HBM: the epilogue warps
-// write each finished conv row (bf16, after bias and ReLU, i.e. exactly the values the unfused kernel would
-// store) into a ring of 5 rows in shared memory and, after every second row, pool the three newest rows into
-// one output row. A strip is 9 conv rows (8s-1 .. 8s+7; the first one is recomputed from the strip above)
-// = 4 pooled rows. The pooling visits each window in the reference's rh -> rw order with explicit
-// compare-select, on the stored bf16 values, so the result is bit-identical to conv kernel + pool kernel.
-constexpr int kPoolStages = 2;
+// The convolution's output (the largest activation of the network) never goes to HBM, nor to shared memory: an
+// epilogue thread holds one conv pixel's 32 channels as 16 packed bf16 pairs (after bias, ReLU and rounding, i.e.
+// exactly the values the unfused kernel would store) and pools in registers. Horizontally the window of pooled
+// column pw is conv columns 2pw-1, 2pw, 2pw+1: the thread of the even column takes its neighbours' values with
+// two warp shuffles per register (the one neighbour that lives in another warp, the left one of a warp's first
+// column, comes through a 64-byte shared-memory slot). Vertically the three conv rows of a pooled row arrive one
+// after the other, so a running maximum suffices. A strip is 9 conv rows (8s-1 .. 8s+7; the first one is
+// recomputed from the strip above) = 4 pooled rows.
+// After ReLU no value is NaN (NaN > 0 is false, so ReLU maps it to +0), negative or -0. On such values the
+// reference's fold `m = (m > v) ? m : v` from -inf, with -1e30 for padding, is exactly the numeric maximum of the
+// in-bounds taps in any order, and 0 is a neutral element: packed bf16 max instructions give the identical bits
+// as conv kernel + pool kernel.
+constexpr int kPoolStages = 3;
 constexpr int kPoolConvRows = kStripRows + 1;                          // 9 conv rows per strip
 constexpr int kPoolInRows = 2 * (kPoolConvRows - 1) + kMaxKH;          // 23 packed input rows
 constexpr int kPoolStripBytes = ((kPoolInRows * kMaxRowBytes + 4096 + 1023) / 1024) * 1024;
-constexpr int kRingRows = 5;
-constexpr int kRingRowBytes = 128 * 128;                               // 128 pixels x 64 channels bf16
-constexpr int kPoolSmemBytes = kWeightBytes + kPoolStages * kPoolStripBytes + kRingRows * kRingRowBytes + 1024;
-
-__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+constexpr int kExchBytes = 2 * 2 * 4 * 64;  // [row parity][channel half][quadrant] x 64 bytes: a warp's last column
+constexpr int kPoolSmemBytes = kWeightBytes + kPoolStages * kPoolStripBytes + kExchBytes + 1024;
 
 __global__ void __launch_bounds__(kThreads, 1) conv_stem_pool_kernel(const __grid_constant__ TcParams p) {
     constexpr uint32_t kTmemCols = 4 * kBN;  // two rows in flight on the tensor core + two being drained
@@ -250,7 +253,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_pool_kernel(const __gri
     const int lane = threadIdx.x & 31;
     const uint32_t w_smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t strip_smem = w_smem + kWeightBytes;
-    const uint32_t ring_smem = strip_smem + kPoolStages * kPoolStripBytes;
+    const uint32_t exch_smem = strip_smem + kPoolStages * kPoolStripBytes;
 
     const int KH = p.taps_h;
     const int row_bytes = p.aux_row_bytes;
@@ -365,96 +368,105 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_pool_kernel(const __gri
         const int half = (warp - 2) >> 2;
         const int ow = quad * 32 + lane;
         const int c0 = half * 32;
-        const int et = threadIdx.x - 64;  // 0..255 among the epilogue threads
         const int POH = p.OH / 2, POW = p.OW / 2;
         __nv_bfloat16* pooled = static_cast<__nv_bfloat16*>(p.out);
+        const bool centre = (lane & 1) == 0 && ow < p.OW;  // even conv columns are the pooling windows' centres
+        float bias[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) bias[e] = p.bias != nullptr ? __ldg(p.bias + c0 + e) : 0.0f;
         pdl_wait();
         int acc = 0;
         uint32_t acc_phase = 0;
-        uint32_t ring_ctr = 0;  // ring slot of local conv row j is (ring_ctr + j) % kRingRows
+        uint32_t row_ctr = 0;  // conv rows handled so far (parity picks the exchange slot)
         bool ok = true;
-        bool first = true;
         for (int strip = blockIdx.x; ok && strip < total_strips; strip += gridDim.x) {
             const int n = strip / strips_per_image;
             const int s = strip - n * strips_per_image;
-            // nobody may still be pooling the previous strip's rows when this strip's first rows are written
-            if (!first) epilogue_bar_sync();
-            first = false;
-            for (int j = (s > 0 ? 0 : 1); j < kPoolConvRows; ++j) {
-                ok = mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after_sync();
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kBN + c0), v);
-                tmem_ld_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
-                acc = (acc + 1) & 3;
-                if (acc == 0) acc_phase ^= 1u;
-
-                // conv row -> shared-memory ring: +bias, ReLU, round to bf16; 16-byte chunks XOR-swizzled by pixel
-                const uint32_t slot = (ring_ctr + (uint32_t)j) % kRingRows;
-                const uint32_t row_addr = ring_smem + slot * kRingRowBytes + (uint32_t)ow * 128u;
+            uint32_t vmax[16];  // running maximum over the conv rows of the current pooled row (0 is neutral)
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    float f[8];
+            for (int e = 0; e < 16; ++e) vmax[e] = 0u;
+            for (int j = (s > 0 ? 0 : 1); j < kPoolConvRows; ++j, ++row_ctr) {
+                // A wait that runs out must not leave some warps behind at the barrier below: the failure is carried
+                // to the barrier, where the four warps of this channel half learn of it and leave together.
+                bool bad = !__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr));
+                uint32_t pk[16];
+                if (!bad) {
+                    tc_fence_after_sync();
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kBN + c0), v);
+                    tmem_ld_wait();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+                    acc = (acc + 1) & 3;
+                    if (acc == 0) acc_phase ^= 1u;
+                    // +bias, ReLU, round to bf16: the values the unfused convolution kernel stores
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[q * 8 + e]);
-                    if (p.bias != nullptr) {
-                        const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + q * 8));
-                        const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + q * 8 + 4));
-                        f[0] = __fadd_rn(f[0], b0.x); f[1] = __fadd_rn(f[1], b0.y); f[2] = __fadd_rn(f[2], b0.z); f[3] = __fadd_rn(f[3], b0.w);
-                        f[4] = __fadd_rn(f[4], b1.x); f[5] = __fadd_rn(f[5], b1.y); f[6] = __fadd_rn(f[6], b1.z); f[7] = __fadd_rn(f[7], b1.w);
-                    }
-                    if (p.relu) {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) f[e] = f[e] > 0.0f ? f[e] : 0.0f;
-                    }
-                    const uint32_t chunk = (uint32_t)(half * 4 + q) ^ ((uint32_t)ow & 7u);
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + chunk * 16u), "r"(pack_bf16(f[0], f[1])),
-                                 "r"(pack_bf16(f[2], f[3])), "r"(pack_bf16(f[4], f[5])), "r"(pack_bf16(f[6], f[7]))
-                                 : "memory");
-                }
-
-                if ((j & 1) == 0 && j >= 2) {
-                    epilogue_bar_sync();  // rows j-2, j-1, j are complete
-                    const int ph = 4 * s + j / 2 - 1;
-                    // The ring holds post-ReLU values: never NaN (NaN > 0 is false, so ReLU maps it to +0), never
-                    // negative, never -0. On such values the reference's fold `m = (m > v) ? m : v` from -inf, with
-                    // -1e30 for padding, is exactly the numeric maximum of the in-bounds taps, in any order, so packed
-                    // bf16 max instructions give the identical bits.
-                    for (int item = et; item < POW * 8; item += 256) {
-                        const int pw = item >> 3, g = item & 7;
-                        const __nv_bfloat162 ninf = __halves2bfloat162(__ushort_as_bfloat16(0xff80), __ushort_as_bfloat16(0xff80));
-                        __nv_bfloat162 m0 = ninf, m1 = ninf, m2 = ninf, m3 = ninf;
-#pragma unroll
-                        for (int rh = 0; rh < 3; ++rh) {
-                            const int lj = j - 2 + rh;
-                            if (s == 0 && lj == 0) continue;  // conv row -1 is padding
-                            const uint32_t rbase = ring_smem + ((ring_ctr + (uint32_t)lj) % kRingRows) * kRingRowBytes;
-#pragma unroll
-                            for (int rw = 0; rw < 3; ++rw) {
-                                const int col = 2 * pw - 1 + rw;
-                                if (col < 0 || col >= p.OW) continue;
-                                uint32_t w0, w1, w2, w3;
-                                const uint32_t a = rbase + (uint32_t)col * 128u + (((uint32_t)g ^ ((uint32_t)col & 7u)) * 16u);
-                                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(a));
-                                m0 = __hmax2(m0, *reinterpret_cast<__nv_bfloat162*>(&w0));
-                                m1 = __hmax2(m1, *reinterpret_cast<__nv_bfloat162*>(&w1));
-                                m2 = __hmax2(m2, *reinterpret_cast<__nv_bfloat162*>(&w2));
-                                m3 = __hmax2(m3, *reinterpret_cast<__nv_bfloat162*>(&w3));
-                            }
+                    for (int e = 0; e < 16; ++e) {
+                        float a = __fadd_rn(__uint_as_float(v[2 * e]), bias[2 * e]);
+                        float b = __fadd_rn(__uint_as_float(v[2 * e + 1]), bias[2 * e + 1]);
+                        if (p.relu) {
+                            a = a > 0.0f ? a : 0.0f;
+                            b = b > 0.0f ? b : 0.0f;
                         }
-                        uint4 o;
-                        o.x = *reinterpret_cast<uint32_t*>(&m0); o.y = *reinterpret_cast<uint32_t*>(&m1);
-                        o.z = *reinterpret_cast<uint32_t*>(&m2); o.w = *reinterpret_cast<uint32_t*>(&m3);
-                        *reinterpret_cast<uint4*>(pooled + ((((size_t)n * POH + ph) * POW + pw) * kBN) + g * 8) = o;
+                        pk[e] = pack_bf16(a, b);
                     }
+                    if (ow >= p.OW) {  // columns beyond the image (the M = 128 tile is wider) must not win a maximum
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) pk[e] = 0u;
+                    }
+                    if (lane == 31) {  // the left neighbour of the next quadrant's first column
+                        const uint32_t slot = exch_smem + ((((row_ctr & 1u) * 2u + (uint32_t)half) * 4u + (uint32_t)quad) * 64u);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g)
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(slot + g * 16u), "r"(pk[4 * g]), "r"(pk[4 * g + 1]),
+                                         "r"(pk[4 * g + 2]), "r"(pk[4 * g + 3])
+                                         : "memory");
+                    }
+                }
+                if (named_barrier_or(1 + half, 128, bad)) {
+                    ok = false;
+                    break;
+                }
+                // horizontal maximum over columns ow-1, ow, ow+1 (meaningful in the centre threads)
+                uint32_t left[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) left[e] = __shfl_up_sync(0xffffffffu, pk[e], 1);
+                if (lane == 0) {
+                    if (quad == 0) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) left[e] = 0u;  // column -1 is padding
+                    } else {
+                        const uint32_t slot = exch_smem + ((((row_ctr & 1u) * 2u + (uint32_t)half) * 4u + (uint32_t)(quad - 1)) * 64u);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g)
+                            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(left[4 * g]), "=r"(left[4 * g + 1]), "=r"(left[4 * g + 2]), "=r"(left[4 * g + 3])
+                                         : "r"(slot + g * 16u));
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const uint32_t right = __shfl_down_sync(0xffffffffu, pk[e], 1);
+                    __nv_bfloat162 m = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&left[e]), *reinterpret_cast<__nv_bfloat162*>(&pk[e]));
+                    m = __hmax2(m, *reinterpret_cast<const __nv_bfloat162*>(&right));
+                    left[e] = *reinterpret_cast<uint32_t*>(&m);  // this row's horizontal maximum
+                    m = __hmax2(m, *reinterpret_cast<__nv_bfloat162*>(&vmax[e]));
+                    vmax[e] = *reinterpret_cast<uint32_t*>(&m);
+                }
+                // local rows 0, 2, 4, 6, 8 are conv rows 8s-1, 8s+1, ...: the last row of one pooled row and the first
+                // of the next
+                if ((j & 1) == 0) {
+                    if (j >= 2 && centre) {
+                        const int ph = 4 * s + j / 2 - 1;
+                        uint4* dst = reinterpret_cast<uint4*>(pooled + ((((size_t)n * POH + ph) * POW + (ow >> 1)) * kBN) + c0);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) dst[g] = make_uint4(vmax[4 * g], vmax[4 * g + 1], vmax[4 * g + 2], vmax[4 * g + 3]);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) vmax[e] = left[e];  // the running maximum restarts with this row
                 }
             }
-            ring_ctr = (ring_ctr + kPoolConvRows) % kRingRows;
         }
     }
 
