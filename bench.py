@@ -18,6 +18,7 @@ cpu_baseline  the reference compiler's own CPU lowering (oracle/_ref) on a bound
 --impl reference times that CPU path alone, on all host cores (independent batch shards per core).
 """
 import argparse
+import collections
 import json
 import os
 import subprocess
@@ -29,6 +30,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 GLOBAL_BATCH = 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of the tensor-core launches of one bf16 plan run, per image, from the ncu
+# capture summarised in profiles/conv_direct_stem_pool_igemm_b128_ncu_full.md (taken at 128 images; it grows with the batch)
+NCU_DRAM_BYTES_PER_IMAGE = 6.03e6
+
 METRIC = "resnet18_inference_throughput"
 UNIT = "img/s"
 
@@ -292,8 +297,14 @@ def main():
                 "h2d_bytes_per_step": int(host_in.numel() * 4 * world), "d2h_bytes_per_step": int(args.batch * graph.out_shape[1] * 4)},
         "gpu_launches": int(graph.num_launches * args.steps),
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
-                     "frac": achieved / peaks["tflops_sustained"], "traffic": None, "peak_source": peaks["source"],
-                     "kernel": "tensor-core convolution kernels: conv_stem_pool + 4 conv3x3_direct + 15 conv_igemm + 1 dense launch per step",
+                     "frac": achieved / peaks["tflops_sustained"],
+                     "traffic": NCU_DRAM_BYTES_PER_IMAGE * per_gpu if args.precision == "bf16" else None,
+                     "traffic_note": "dram read+write bytes of the same launches from an ncu capture at 128 images, "
+                                     "scaled by the per-GPU batch (profiles/conv_direct_stem_pool_igemm_b128_ncu_full.md); "
+                                     "algorithmic bytes: %.2f GB" % (sum(b for n, f, b in info if n.startswith(("conv_", "dense_"))) / 1e9),
+                     "peak_source": peaks["source"],
+                     "kernel": "all tensor-core launches of a step: " + ", ".join(
+                         f"{c} x {k}" for k, c in sorted(collections.Counter(n.split()[0] for n, _, _, _ in tc).items())),
                      "flops_per_step_per_gpu": tc_flops, "ms_per_step_in_kernel": tc_ms},
         "launches": layers,
     }
