@@ -629,6 +629,12 @@ int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_m
     p->tiles_n = (N + p->BNI - 1) / p->BNI;
 
     int bn = Cout <= 64 ? 64 : (Cout <= 128 ? 128 : 256);
+    // A launch with a handful of tiles (the dense layer of a small batch: 1 pixel tile x 4 channel tiles) is bound by
+    // the latency of each CTA's own operand stream: narrower tiles spread the weight rows over more SMs.
+    {
+        const long long mt = (long long)p->tiles_w * p->tiles_h * p->tiles_n;
+        while (bn > 64 && mt * ((Cout + bn - 1) / bn) < 32) bn /= 2;
+    }
     // CTA pairs (tcgen05 cta_group::2): each CTA fetches half of the B tile, which relieves the L2 -> shared-memory
     // fill rate that bounds the wide tiles. KXC_B200_CTA_PAIR=0 switches them off (for measurements).
     static const bool pair_enabled = [] {

@@ -11,6 +11,7 @@
 
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cmath>
 
 #include "common.cuh"
@@ -157,41 +158,62 @@ __global__ void __launch_bounds__(kThreads) maxpool3x3s2p1_nhwc_kernel(const T* 
     }
 }
 
+// Global average over the pixels of NHWC activations, the pixels of an (image, channel group) dealt to the block's
+// eight warps: every warp sums its pixels (all loads in flight at once), the partial sums meet in shared memory and
+// are added in warp order. The summation order differs from the reference's sequential walk (tensor-core plans
+// compare with a tolerance; the bit-exact fp32 plan uses the NCHW kernel in pool.cu).
 template <typename T>
-__global__ void __launch_bounds__(kThreads) gap_nhwc_kernel(const T* __restrict__ x, T* __restrict__ out, int N, int HW, int C) {
+__global__ void __launch_bounds__(kThreads) gap_nhwc_split_kernel(const T* __restrict__ x, T* __restrict__ out, int N, int HW,
+                                                                  int C) {
     constexpr int L = Vec<T>::kLanes;
+    constexpr int kParts = kThreads / 32;
+    __shared__ float part_sum[kParts][32][L];
     const int cg = C / L;
     const int64_t total = (int64_t)N * cg;
+    const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
     const float div = (float)HW;
     sm100::pdl_launch_dependents();
     sm100::pdl_wait();
-    for (int64_t lin = (int64_t)blockIdx.x * kThreads + threadIdx.x; lin < total; lin += (int64_t)gridDim.x * kThreads) {
-        const int g = (int)(lin % cg);
-        const int n = (int)(lin / cg);
+    for (int64_t base = (int64_t)blockIdx.x * 32; base < total; base += (int64_t)gridDim.x * 32) {
+        const int64_t lin = base + lane;
         float s[L];
 #pragma unroll
         for (int j = 0; j < L; ++j) s[j] = 0.0f;
-        const T* p = x + (int64_t)n * HW * C + g * L;
-        // eight pixels' loads in flight at a time; the additions keep the pixel order
-        int i = 0;
-        for (; i + 8 <= HW; i += 8) {
-            float v[8][L];
+        if (lin < total) {
+            const int g = (int)(lin % cg);
+            const int n = (int)(lin / cg);
+            const T* p = x + (int64_t)n * HW * C + g * L;
+            for (int i0 = part; i0 < HW; i0 += 8 * kParts) {
+                float v[8][L];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) Vec<T>::load(p + (int64_t)(i + u) * C, v[u]);
+                for (int u = 0; u < 8; ++u) {
+                    const int i = i0 + u * kParts;
+                    if (i < HW) {
+                        Vec<T>::load(p + (int64_t)i * C, v[u]);
+                    } else {
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
+                        for (int j = 0; j < L; ++j) v[u][j] = 0.0f;
+                    }
+                }
 #pragma unroll
-                for (int j = 0; j < L; ++j) s[j] = __fadd_rn(s[j], v[u][j]);
+                for (int u = 0; u < 8; ++u)
+#pragma unroll
+                    for (int j = 0; j < L; ++j) s[j] = __fadd_rn(s[j], v[u][j]);
+            }
         }
-        for (; i < HW; ++i) {
-            float v[L];
-            Vec<T>::load(p + (int64_t)i * C, v);
 #pragma unroll
-            for (int j = 0; j < L; ++j) s[j] = __fadd_rn(s[j], v[j]);
+        for (int j = 0; j < L; ++j) part_sum[part][lane][j] = s[j];
+        __syncthreads();
+        if (part == 0 && lin < total) {
+#pragma unroll
+            for (int q = 1; q < kParts; ++q)
+#pragma unroll
+                for (int j = 0; j < L; ++j) s[j] = __fadd_rn(s[j], part_sum[q][lane][j]);
+#pragma unroll
+            for (int j = 0; j < L; ++j) s[j] = __fdiv_rn(s[j], div);
+            Vec<T>::store(out + lin * L, s);
         }
-#pragma unroll
-        for (int j = 0; j < L; ++j) s[j] = __fdiv_rn(s[j], div);
-        Vec<T>::store(out + lin * L, s);
+        __syncthreads();
     }
 }
 
@@ -344,7 +366,8 @@ int32_t gap_nhwc(const void* x, void* out, TcDType dt, int N, int HW, int C, cud
     const int64_t items = (int64_t)N * (C / lanes);
     if (items == 0) return KXC_B200_OK;
     cudaError_t err = cudaSuccess;
-    KXC_DISPATCH_ACT(dt, (err = launch_kernel(gap_nhwc_kernel<T>, dim3(grid_for(items, 16)), dim3(kThreads), 0, s, /*pdl=*/true, 1,
+    const int blocks = (int)std::min<int64_t>((items + 31) / 32, (int64_t)kNumSMs * 16);
+    KXC_DISPATCH_ACT(dt, (err = launch_kernel(gap_nhwc_split_kernel<T>, dim3(blocks), dim3(kThreads), 0, s, /*pdl=*/true, 1,
                                               static_cast<const T*>(x), static_cast<T*>(out), N, HW, C)));
     if (err != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "gap_nhwc launch: %s", cudaGetErrorString(err));
     return check_launch("gap_nhwc");
