@@ -19,9 +19,17 @@
 //   dense OUT X W | gemm OUT A B C alpha beta transA transB
 // The function's parameters are the `in` tensors in declaration order; its result is the last OUT.
 // Each op may appear once per function: CodeGenC names buffers after the op (codegen_c.cc:38-46).
+//
+// Usage: ref_emit --import <spec.json> <params.bin>   (JSON on stdout)
+//   Loads a "kxc.onnx_import.v1" graph with the reference's own importer (LoadONNXImportSpec,
+//   src/frontend/onnx_importer.cc:410-520), runs its InferTypePass and prints the resulting Relay function as the
+//   reference sees it: inputs, calls in post order (operator name, arguments, attributes as its Attrs objects hold
+//   them, inferred output shape) and the result. The Python side feeds that one description to both the CPU checker
+//   and the GPU executor, so both compute the graph the reference's importer built.
 
 #include <cstdint>
 #include <cstdlib>
+#include <functional>
 #include <iostream>
 #include <map>
 #include <sstream>
@@ -30,6 +38,7 @@
 #include <vector>
 
 #include "codegen/codegen_c.h"
+#include "frontend/onnx_importer.h"
 #include "relay/op.h"
 #include "relay/relay.h"
 #include "relay/transforms/infer_type.h"
@@ -67,9 +76,102 @@ kxc::Array<int64_t> ToArray(const std::vector<int64_t>& v) {
     return a;
 }
 
+std::string JsonInts(const std::vector<int64_t>& v) {
+    std::string s = "[";
+    for (size_t i = 0; i < v.size(); ++i) s += (i ? "," : "") + std::to_string(v[i]);
+    return s + "]";
+}
+std::string JsonInts(const kxc::Array<int64_t>& a) {
+    std::vector<int64_t> v;
+    for (size_t i = 0; i < a.size(); ++i) v.push_back(a[i]);
+    return JsonInts(v);
+}
+
+std::string AttrsJson(const std::string& op, const kxc::ObjectRef& attrs) {
+    using namespace kxc::relay;
+    std::ostringstream os;
+    if (op == "nn_conv2d") {
+        const auto* a = attrs.As<Conv2DAttrsNode>();
+        if (!a) throw std::runtime_error("nn_conv2d without Conv2DAttrs");
+        os << "{\"strides\":" << JsonInts(a->strides) << ",\"padding\":" << JsonInts(a->padding) << ",\"dilation\":"
+           << JsonInts(a->dilation) << ",\"groups\":" << a->groups << "}";
+    } else if (op == "nn_max_pool2d" || op == "nn_avg_pool2d") {
+        const auto* a = attrs.As<MaxPool2DAttrsNode>();
+        if (!a) throw std::runtime_error(op + " without MaxPool2DAttrs");
+        os << "{\"pool_size\":" << JsonInts(a->pool_size) << ",\"strides\":" << JsonInts(a->strides) << ",\"padding\":"
+           << JsonInts(a->padding) << ",\"dilation\":" << JsonInts(a->dilation) << ",\"ceil_mode\":" << (a->ceil_mode ? 1 : 0) << "}";
+    } else if (op == "nn_gemm") {
+        const auto* a = attrs.As<GemmAttrsNode>();
+        if (!a) throw std::runtime_error("nn_gemm without GemmAttrs");
+        std::ostringstream f;
+        f.precision(9);
+        f << "{\"alpha\":" << a->alpha << ",\"beta\":" << a->beta << ",\"transA\":" << a->transA << ",\"transB\":" << a->transB << "}";
+        os << f.str();
+    } else if (op == "nn_flatten") {
+        const auto* a = attrs.As<FlattenAttrsNode>();
+        os << "{\"axis\":" << (a ? a->axis : 1) << "}";
+    } else {
+        os << "{}";
+    }
+    return os.str();
+}
+
+int DumpImported(const std::string& json_path, const std::string& params_path) {
+    kxc::frontend::ImportedONNXModel m = kxc::frontend::LoadONNXImportSpec(json_path, params_path);
+    kxc::Function func = kxc::relay::InferTypePass(m.function);
+    std::map<const void*, std::string> param_of;  // constant storage -> parameter name
+    for (const auto& kv : m.params) param_of[kv.second->dl_tensor.data] = kv.first;
+    std::map<const kxc::Object*, int> id_of;
+    std::ostringstream nodes;
+    int next_id = 0;
+    auto shape_of = [](const kxc::Expr& e) -> std::string {
+        const auto* tt = e.checked_type().As<kxc::TensorTypeNode>();
+        if (!tt) throw std::runtime_error("non-tensor value in the imported function");
+        return JsonInts(tt->shape);
+    };
+    std::function<std::string(const kxc::Expr&)> ref = [&](const kxc::Expr& e) -> std::string {
+        if (const auto* v = e.As<kxc::VarNode>()) return "{\"var\":\"" + v->vid->name_hint + "\"}";
+        if (const auto* c = e.As<kxc::ConstantNode>()) {
+            auto it = param_of.find(c->data->dl_tensor.data);
+            if (it == param_of.end()) throw std::runtime_error("constant that is not a parameter of the spec");
+            return "{\"param\":\"" + it->second + "\"}";
+        }
+        const auto* call = e.As<kxc::CallNode>();
+        if (!call) throw std::runtime_error("unsupported expression kind in the imported function");
+        auto done = id_of.find(call);
+        if (done != id_of.end()) return "{\"node\":" + std::to_string(done->second) + "}";
+        const auto* op = call->op.As<kxc::relay::OpNode>();
+        if (!op) throw std::runtime_error("call of a non-operator");
+        std::string args;
+        for (size_t i = 0; i < call->args.size(); ++i) args += (i ? "," : "") + ref(call->args[i]);
+        const int id = next_id++;
+        id_of[call] = id;
+        nodes << (id ? ",\n" : "") << "  {\"id\":" << id << ",\"op\":\"" << op->name << "\",\"args\":[" << args
+              << "],\"attrs\":" << AttrsJson(op->name, call->attrs) << ",\"shape\":" << shape_of(e) << "}";
+        return "{\"node\":" + std::to_string(id) + "}";
+    };
+    const std::string result = ref(func->body);
+    std::cout << "{\"inputs\":[";
+    for (size_t i = 0; i < func->params.size(); ++i) {
+        const auto* tt = func->params[i]->type_annotation.As<kxc::TensorTypeNode>();
+        std::cout << (i ? "," : "") << "{\"name\":\"" << func->params[i]->vid->name_hint << "\",\"shape\":"
+                  << (tt ? JsonInts(tt->shape) : std::string("[]")) << ",\"dtype\":\"" << (tt ? tt->dtype : "") << "\"}";
+    }
+    std::cout << "],\n \"nodes\":[\n" << nodes.str() << "\n ],\n \"result\":" << result << "}\n";
+    return 0;
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
+    if (argc == 4 && std::string(argv[1]) == "--import") {
+        try {
+            return DumpImported(argv[2], argv[3]);
+        } catch (const std::exception& e) {
+            std::cerr << "ref_emit: " << e.what() << "\n";
+            return 1;
+        }
+    }
     if (argc != 3) {
         std::cerr << "usage: ref_emit <symbol> \"<stmt>;...\"\n";
         return 2;
