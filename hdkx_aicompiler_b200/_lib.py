@@ -34,6 +34,14 @@ class AddDesc(ctypes.Structure):
     _fields_ = [("rank_a", i32), ("rank_b", i32), ("shape_a", i64 * 6), ("shape_b", i64 * 6), ("relu", i32)]
 
 
+class SoftmaxDesc(ctypes.Structure):
+    _fields_ = [("rank", i32), ("shape", i64 * 6), ("axis", i32)]
+
+
+class ReduceDesc(ctypes.Structure):
+    _fields_ = [("rank", i32), ("shape", i64 * 6), ("num_axes", i32), ("axes", i32 * 6), ("keepdims", i32)]
+
+
 class Pool2dDesc(ctypes.Structure):
     _fields_ = [(n, i32) for n in ("n", "c", "h", "w", "kh", "kw", "stride_h", "stride_w", "pad_top", "pad_left",
                                    "pad_bottom", "pad_right", "ceil_mode")]
@@ -60,6 +68,8 @@ SYMBOLS = {
     "kxc_b200_nn_avg_pool2d": (i32, [vpp, ctypes.POINTER(Pool2dDesc), vp]),
     "kxc_b200_max_pool2d_add_relu": (i32, [vpp, ctypes.POINTER(Pool2dDesc), vp]),
     "kxc_b200_nn_global_avg_pool2d": (i32, [vpp, i32, i32, i32, i32, vp]),
+    "kxc_b200_softmax": (i32, [vpp, ctypes.POINTER(SoftmaxDesc), vp]),
+    "kxc_b200_reduce_mean": (i32, [vpp, ctypes.POINTER(ReduceDesc), vp]),
     "kxc_b200_nn_flatten": (i32, [vpp, i64, vp]),
     "kxc_b200_nn_gemm": (i32, [vpp, ctypes.POINTER(GemmDesc), vp]),
 }

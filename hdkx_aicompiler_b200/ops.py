@@ -195,6 +195,31 @@ def nn_global_avg_pool2d(x):
     return out
 
 
+def softmax(x, axis=-1):
+    """softmax along `axis` (only the last axis: see include/kxc_b200.h)."""
+    x = _req(x, torch.float32, "softmax")
+    if not 1 <= x.dim() <= 6:
+        raise ValueError("softmax expects rank 1..6")
+    desc = _lib.SoftmaxDesc(x.dim(), (_lib.i64 * 6)(*x.shape), int(axis))
+    out = torch.empty_like(x)
+    check("softmax", load().kxc_b200_softmax(packed(x.data_ptr(), out.data_ptr()), desc, _stream(x)))
+    return out
+
+
+def reduce_mean(x, axes, keepdims=True):
+    """Mean over `axes`, summed sequentially in the reference's order (bit-exact)."""
+    x = _req(x, torch.float32, "reduce_mean")
+    if not 1 <= x.dim() <= 6:
+        raise ValueError("reduce_mean expects rank 1..6")
+    axes = [int(a) for a in axes]
+    norm = sorted(a % x.dim() for a in axes)
+    oshape = [1 if d in norm else n for d, n in enumerate(x.shape) if keepdims or d not in norm]
+    desc = _lib.ReduceDesc(x.dim(), (_lib.i64 * 6)(*x.shape), len(axes), (_lib.i32 * 6)(*axes), 1 if keepdims else 0)
+    out = torch.empty(oshape, dtype=torch.float32, device=x.device)
+    check("reduce_mean", load().kxc_b200_reduce_mean(packed(x.data_ptr(), out.data_ptr()), desc, _stream(x)))
+    return out
+
+
 def nn_flatten(x):
     x = _req(x, torch.float32, "nn_flatten")
     out = torch.empty((x.shape[0], x.numel() // max(x.shape[0], 1)), dtype=torch.float32, device=x.device)

@@ -139,6 +139,29 @@ int32_t kxc_b200_nn_avg_pool2d(void** packed_args, const kxc_b200_pool2d_desc* d
  * packed_args = { x[N,C,H,W], residual[N,C,OH,OW], out[N,C,OH,OW] } */
 int32_t kxc_b200_max_pool2d_add_relu(void** packed_args, const kxc_b200_pool2d_desc* desc, void* stream);
 
+/* softmax — SoftmaxCompute (src/relay/op/nn/softmax.cc:44-70): exp, sum along the axis in index order, divide; no
+ * subtraction of the maximum. packed_args = { x, out } of the same shape. Only the last axis is accepted: for any other
+ * axis the reference's keepdims reduction (include/te/topi/reduction.h:47-58) indexes elements of other rows. */
+typedef struct kxc_b200_softmax_desc {
+    int32_t rank;
+    int64_t shape[6];
+    int32_t axis; /* negative values count from the end */
+} kxc_b200_softmax_desc;
+int32_t kxc_b200_softmax(void** packed_args, const kxc_b200_softmax_desc* desc, void* stream);
+
+/* reduce_mean — ReduceMeanCompute (src/relay/op/tensor/reduce.cc:81-99): sequential sum over the reduced axes (nested
+ * loops in ascending axis order), then / (float)count. packed_args = { x, out }; out holds the kept dimensions in
+ * order (with extent-1 dimensions in place of the reduced ones when keepdims is set). keepdims = 1 is accepted only when
+ * the reduced axes are the trailing ones (elsewhere the reference's reduction reads the wrong elements). Bit-exact. */
+typedef struct kxc_b200_reduce_desc {
+    int32_t rank;
+    int64_t shape[6];
+    int32_t num_axes;
+    int32_t axes[6];
+    int32_t keepdims;
+} kxc_b200_reduce_desc;
+int32_t kxc_b200_reduce_mean(void** packed_args, const kxc_b200_reduce_desc* desc, void* stream);
+
 /* nn_global_avg_pool2d — topi::global_avg_pool2d (include/te/topi/nn.h:260-287).
  * packed_args = { x[N,C,H,W], out[N,C,1,1] }. The sum runs sequentially over (h,w) per plane, like
  * the reference, so the result is bit-exact. */

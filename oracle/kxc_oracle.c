@@ -214,6 +214,46 @@ int32_t kxc_oracle_global_avg_pool2d_f32(const float* x, float* out, int64_t N, 
     return 0;
 }
 
+/* ---- softmax: src/relay/op/nn/softmax.cc:44-70. e = exp(x) elementwise (expf of the C library), s = 0; s = s + e over
+ * the axis in index order; out = e / s. No subtraction of the maximum. x is viewed as [outer, len, inner]. */
+int32_t kxc_oracle_softmax_f32(const float* x, float* out, int64_t outer, int64_t len, int64_t inner) {
+    for (int64_t o = 0; o < outer; ++o)
+        for (int64_t i = 0; i < inner; ++i) {
+            const float* xp = x + o * len * inner + i;
+            float* op = out + o * len * inner + i;
+            float s = 0.0f;
+            for (int64_t k = 0; k < len; ++k) s = s + expf(xp[k * inner]);
+            for (int64_t k = 0; k < len; ++k) op[k * inner] = expf(xp[k * inner]) / s;
+        }
+    return 0;
+}
+
+/* ---- reduce_mean: src/relay/op/tensor/reduce.cc:81-99 over topi::sum (include/te/topi/reduction.h:23-70). s = 0;
+ * s = s + x with the reduced axes as nested loops in ascending axis order; out = s / (float)count. `reduce[d]` marks
+ * the reduced dimensions of the rank-`rank` row-major input; the output is the kept dimensions in order. */
+int32_t kxc_oracle_reduce_mean_f32(const float* x, float* out, int32_t rank, const int64_t* shape, const int32_t* reduce) {
+    int64_t stride[8], kept[8], red[8];
+    int nk = 0, nr = 0;
+    int64_t st = 1, count = 1, nout = 1;
+    if (rank < 0 || rank > 8) return 1;
+    for (int d = rank - 1; d >= 0; --d) { stride[d] = st; st *= shape[d]; }
+    for (int d = 0; d < rank; ++d) {
+        if (reduce[d]) { red[nr++] = d; count *= shape[d]; } else { kept[nk++] = d; nout *= shape[d]; }
+    }
+    for (int64_t o = 0; o < nout; ++o) {
+        int64_t rem = o, base = 0;
+        for (int j = nk - 1; j >= 0; --j) { base += (rem % shape[kept[j]]) * stride[kept[j]]; rem /= shape[kept[j]]; }
+        float s = 0.0f;
+        for (int64_t r = 0; r < count; ++r) {
+            int64_t rr = r, off = base;
+            for (int j = nr - 1; j >= 0; --j) { off += (rr % shape[red[j]]) * stride[red[j]]; rr /= shape[red[j]]; }
+            s = s + x[off];
+        }
+        out[o] = s / (float)count;
+    }
+    return 0;
+}
+
 /* ---- nn_dense: include/te/topi/nn.h:48-80. acc = 0; acc += a[i,k] * b[j,k]. */
 int32_t kxc_oracle_dense_f32(const float* a, const float* b, float* out, int64_t M, int64_t Nn, int64_t K) {
     for (int64_t i = 0; i < M; ++i)

@@ -63,6 +63,8 @@ int32_t kxc_oracle_avg_pool2d_f32(const float* x, float* out, int64_t N, int64_t
                                   int64_t pb, int64_t pr, int32_t ceil_mode);
 
 int32_t kxc_oracle_global_avg_pool2d_f32(const float* x, float* out, int64_t N, int64_t C, int64_t H, int64_t W);
+int32_t kxc_oracle_softmax_f32(const float* x, float* out, int64_t outer, int64_t len, int64_t inner);
+int32_t kxc_oracle_reduce_mean_f32(const float* x, float* out, int32_t rank, const int64_t* shape, const int32_t* reduce);
 
 /* out[i,j] = sum_k a[i,k]*b[j,k]  (b is [Nn,K]) */
 int32_t kxc_oracle_dense_f32(const float* a, const float* b, float* out, int64_t M, int64_t Nn, int64_t K);

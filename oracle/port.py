@@ -41,6 +41,8 @@ def lib():
         _lib.kxc_oracle_avg_pool2d_f32.argtypes = [vp, vp] + [i64] * 12 + [i32]
         _lib.kxc_oracle_global_avg_pool2d_f32.argtypes = [vp, vp] + [i64] * 4
         _lib.kxc_oracle_dense_f32.argtypes = [vp, vp, vp] + [i64] * 3
+        _lib.kxc_oracle_softmax_f32.argtypes = [vp, vp] + [i64] * 3
+        _lib.kxc_oracle_reduce_mean_f32.argtypes = [vp, vp, i32, vp, vp]
         _lib.kxc_oracle_gemm_f32.argtypes = [vp] * 4 + [i64] * 3 + [ctypes.c_float] * 2 + [i32] * 2
         _lib.kxc_oracle_round_bf16.argtypes = [vp, vp, i64]
         _lib.kxc_oracle_round_tf32.argtypes = [vp, vp, i64]
@@ -158,6 +160,34 @@ def global_avg_pool2d(x):
     N, C, H, W = x.shape
     out = np.empty((N, C, 1, 1), dtype=np.float32)
     _check(lib().kxc_oracle_global_avg_pool2d_f32(_p(x), _p(out), N, C, H, W), "global_avg_pool2d")
+    return out
+
+
+def softmax(x, axis=-1):
+    """src/relay/op/nn/softmax.cc:44-70. Last axis only: for an inner axis the reference's keepdims reduction
+    (include/te/topi/reduction.h:47-58) indexes elements of other rows, which nothing should reproduce."""
+    x = _c(x, np.float32)
+    axis = axis % x.ndim
+    if axis != x.ndim - 1:
+        raise ValueError("softmax: only the last axis (see the docstring)")
+    outer = int(np.prod(x.shape[:axis], dtype=np.int64))
+    inner = int(np.prod(x.shape[axis + 1:], dtype=np.int64))
+    out = np.empty_like(x)
+    _check(lib().kxc_oracle_softmax_f32(_p(x), _p(out), outer, x.shape[axis], inner), "softmax")
+    return out
+
+
+def reduce_mean(x, axes, keepdims=True):
+    """src/relay/op/tensor/reduce.cc:81-99. keepdims only for trailing reduced axes (same reference defect as softmax)."""
+    x = _c(x, np.float32)
+    axes = sorted(a % x.ndim for a in axes)
+    if keepdims and axes != list(range(x.ndim - len(axes), x.ndim)):
+        raise ValueError("reduce_mean: keepdims needs the reduced axes to be the trailing ones (see the docstring)")
+    shape = np.asarray(x.shape, dtype=np.int64)
+    flags = np.asarray([1 if d in axes else 0 for d in range(x.ndim)], dtype=np.int32)
+    out_shape = [1 if d in axes else n for d, n in enumerate(x.shape) if keepdims or d not in axes]
+    out = np.empty(out_shape, dtype=np.float32)
+    _check(lib().kxc_oracle_reduce_mean_f32(_p(x), _p(out), x.ndim, _p(shape), _p(flags)), "reduce_mean")
     return out
 
 

@@ -175,6 +175,16 @@ def global_avg_pool2d(x):
     return run(f"in x float32 {_shape(x)};global_avg_pool2d p x", [x], (N, C, 1, 1))
 
 
+def softmax(x, axis=-1):
+    return run(f"in x float32 {_shape(x)};softmax p x {axis % x.ndim}", [x], x.shape)
+
+
+def reduce_mean(x, axes, keepdims=True):
+    axes = sorted(a % x.ndim for a in axes)
+    out_shape = [1 if d in axes else n for d, n in enumerate(x.shape) if keepdims or d not in axes]
+    return run(f"in x float32 {_shape(x)};reduce_mean p x {','.join(map(str, axes))} {1 if keepdims else 0}", [x], out_shape)
+
+
 def dense(a, b):
     return run(f"in a float32 {_shape(a)};in b float32 {_shape(b)};dense d a b", [a, b], (a.shape[0], b.shape[0]))
 

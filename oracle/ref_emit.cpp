@@ -17,6 +17,7 @@
 //   relu OUT X | add OUT A B | flatten OUT X | global_avg_pool2d OUT X
 //   max_pool2d OUT X kh,kw sh,sw pt,pl,pb,pr ceil   (avg_pool2d likewise)
 //   dense OUT X W | gemm OUT A B C alpha beta transA transB
+//   softmax OUT X axis | reduce_mean OUT X a0,a1,... keepdims
 // The function's parameters are the `in` tensors in declaration order; its result is the last OUT.
 // Each op may appear once per function: CodeGenC names buffers after the op (codegen_c.cc:38-46).
 //
@@ -227,6 +228,11 @@ int main(int argc, char** argv) {
                                                                 {k[0], k[1]}, "NCHW", ceil);
                 out = kxc::Call(kxc::relay::Op::Get(op == "max_pool2d" ? "nn_max_pool2d" : "nn_avg_pool2d"),
                                 {get(t[2])}, attrs);
+            } else if (op == "softmax") {
+                out = kxc::Call(kxc::relay::Op::Get("softmax"), {get(t[2])}, kxc::relay::SoftmaxAttrs::Create(std::atoi(t[3].c_str())));
+            } else if (op == "reduce_mean") {
+                out = kxc::Call(kxc::relay::Op::Get("reduce_mean"), {get(t[2])},
+                                kxc::relay::ReduceMeanAttrs::Create(Ints(t[3]), std::atoi(t[4].c_str())));
             } else if (op == "dense") {
                 out = kxc::Call(kxc::relay::Op::Get("nn_dense"), {get(t[2]), get(t[3])},
                                 kxc::relay::DenseAttrs::Create(0, ""));

@@ -277,3 +277,36 @@ def test_gemm_transA_rejected(ops):
     z = torch.zeros(2, 2, device="cuda")
     with pytest.raises(KxcError):
         ops.nn_gemm(z, z, torch.zeros(2, device="cuda"), transA=1, transB=1)
+
+
+@pytest.mark.parametrize("shape", [(4, 1000), (3, 5, 7), (2, 3, 4, 33), (1, 1), (0, 8)])
+def test_softmax_last_axis(ops, rng, shape):
+    x = rng.normal(0, 2, shape).astype(f32)
+    got = ops.softmax(dev(x), -1).cpu().numpy()
+    exp = port.softmax(x, -1) if x.size else x
+    # exp() comes from different math libraries (device / host): a few ulp, not the same bits
+    assert_close(got, exp, 2e-6, f"softmax {shape}")
+    if x.size:
+        assert np.abs(got.sum(-1) - 1).max() < 2e-6
+
+
+def test_softmax_inner_axis_rejected(ops, rng):
+    from hdkx_aicompiler_b200 import KxcError
+    with pytest.raises(KxcError):
+        ops.softmax(dev(rng.normal(0, 1, (3, 4)).astype(f32)), 0)
+
+
+@pytest.mark.parametrize("shape,axes,keep", [((4, 512, 7, 7), (2, 3), True), ((3, 5, 7), (2,), True), ((3, 5, 7), (1, 2), True),
+                                              ((3, 5, 7), (0, 2), False), ((3, 5, 7), (1,), False), ((64, 1000), (0,), False),
+                                              ((3, 5, 7), (0, 1, 2), True), ((2, 3, 4, 5, 6), (1, 3), False)])
+def test_reduce_mean_bit_exact(ops, rng, shape, axes, keep):
+    x = rng.normal(0, 1, shape).astype(f32)
+    got = ops.reduce_mean(dev(x), axes, keep).cpu().numpy()
+    assert_bit_exact(got, port.reduce_mean(x, axes, keep), f"reduce_mean {shape} {axes} keepdims={keep}")
+
+
+def test_reduce_mean_keepdims_inner_axis_rejected(ops, rng):
+    from hdkx_aicompiler_b200 import KxcError
+    with pytest.raises(KxcError):
+        ops.reduce_mean(dev(rng.normal(0, 1, (3, 4)).astype(f32)), (0,), True)
+

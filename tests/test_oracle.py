@@ -153,3 +153,23 @@ def test_rounding_helpers():
     t = port.round_tf32(x)
     assert np.all((t.view(np.uint32) & 0x1fff) == 0)
     assert np.all(np.abs(t - x) <= np.abs(x) * 2.0 ** -11)
+
+
+@needs_ref
+def test_port_softmax_reduce_mean_match_reference_bits(rng):
+    """softmax (last axis) and reduce_mean: the plain-C port against the kernels the reference's compiler generates.
+    Both use the C library's expf and the same sequential sums, so the bits agree."""
+    x = rng.normal(0, 2, (3, 5, 7)).astype(np.float32)
+    assert_bit_exact(port.softmax(x, -1), ref.softmax(x, -1), "softmax last axis")
+    assert_bit_exact(port.softmax(x.reshape(15, 7), 1), ref.softmax(x.reshape(15, 7), 1), "softmax rank 2")
+    assert np.abs(port.softmax(x, 2).sum(2) - 1).max() < 1e-6
+    for axes, keep in (((2,), True), ((1, 2), True), ((0, 2), False), ((1,), False), ((0,), False), ((0, 1, 2), True)):
+        assert_bit_exact(port.reduce_mean(x, axes, keep), ref.reduce_mean(x, axes, keep), f"reduce_mean {axes} keepdims={keep}")
+    # global average pooling is reduce_mean over (2, 3) with keepdims
+    y = rng.normal(0, 1, (2, 3, 4, 5)).astype(np.float32)
+    assert_bit_exact(port.reduce_mean(y, (2, 3), True), port.global_avg_pool2d(y), "reduce_mean == global_avg_pool2d")
+    with pytest.raises(ValueError):
+        port.softmax(x, 0)      # the reference's own result for an inner axis is not a softmax
+    with pytest.raises(ValueError):
+        port.reduce_mean(x, (0,), True)
+
