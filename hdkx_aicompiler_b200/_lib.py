@@ -12,7 +12,7 @@ vp = ctypes.c_void_p
 vpp = ctypes.POINTER(ctypes.c_void_p)
 
 OK = 0
-BIAS, RESIDUAL, RELU = 1, 2, 4
+BIAS, RESIDUAL, RELU, NHWC = 1, 2, 4, 8
 PREC_FP32, PREC_TF32, PREC_BF16, PREC_SIMT = 0, 1, 2, 3
 
 

@@ -108,7 +108,7 @@ extern "C" int32_t kxc_b200_nn_conv2d_s8(void** packed_args, const kxc_b200_conv
                               static_cast<const int32_t*>(packed_args[2]), static_cast<const int32_t*>(packed_args[3]),
                               static_cast<const int32_t*>(packed_args[4]), static_cast<int8_t*>(packed_args[5]), d,
                               (desc->flags & KXC_B200_RELU) ? 1 : 0, desc->precision == KXC_B200_PREC_SIMT ? 1 : 0,
-                              static_cast<cudaStream_t>(stream));
+                              (desc->flags & KXC_B200_NHWC) ? 1 : 0, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int32_t kxc_b200_nn_gemm(void** packed_args, const kxc_b200_gemm_desc* desc, void* stream) {

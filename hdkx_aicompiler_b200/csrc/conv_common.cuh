@@ -43,7 +43,7 @@ int32_t gemm_fp32_exact(const float* a, const float* b, const float* c, float* o
 int32_t conv2d_tensor_core(const float* data, const float* weight, const float* bias, const float* residual, float* out,
                            const ConvDims& d, int relu, int precision, cudaStream_t s);
 int32_t conv2d_s8_dispatch(const int8_t* data, const int8_t* weight, const int32_t* bias, const int32_t* multiplier,
-                           const int32_t* shift, int8_t* out, const ConvDims& d, int relu, int force_simt, cudaStream_t s);
+                           const int32_t* shift, int8_t* out, const ConvDims& d, int relu, int force_simt, int nhwc, cudaStream_t s);
 int32_t gemm_tensor_core(const float* a, const float* b, const float* c, float* out, const kxc_b200_gemm_desc& g,
                          cudaStream_t s);
 

@@ -64,10 +64,28 @@ int32_t conv2d_tensor_core(const float* data, const float* weight, const float* 
 }
 
 int32_t conv2d_s8_dispatch(const int8_t* data, const int8_t* weight, const int32_t* bias, const int32_t* multiplier,
-                           const int32_t* shift, int8_t* out, const ConvDims& d, int relu, int force_simt, cudaStream_t s) {
-    if (force_simt || !tc_shape_ok(d)) return conv2d_s8_exact(data, weight, bias, multiplier, shift, out, d, relu, s);
+                           const int32_t* shift, int8_t* out, const ConvDims& d, int relu, int force_simt, int nhwc,
+                           cudaStream_t s) {
     const TcDType dt = kTcS8;
     const int cpad = tc_channel_pad(dt, d.C);
+    if (nhwc) {
+        // operands already NHWC / OHWI with the kernel's channel granularity: straight to the tensor-core kernel
+        if (force_simt || !tc_shape_ok(d)) return fail(KXC_B200_ERR_UNSUPPORTED, "nn_conv2d_s8: the NHWC form exists for the tensor-core path only");
+        if (cpad != d.C || (d.O & 15) != 0 || !aligned16(data) || !aligned16(weight) || !aligned16(out))
+            return fail(KXC_B200_ERR_INVALID, "nn_conv2d_s8: NHWC operands need C = 32/64/128k channels, O a multiple of 16 and 16-byte aligned pointers");
+        TcParams p{};
+        TcConfig cfg{};
+        KXC_TRY(tc_setup_conv(&p, &cfg, dt, kOutNHWC_S8, data, weight, d.N, d.H, d.W, cpad, d.O, d.KH, d.KW, d.SH, d.PH, d.PW, d.DH,
+                              d.DW));
+        p.bias_i32 = bias;
+        p.multiplier = multiplier;
+        p.shift = shift;
+        p.out = out;
+        p.relu = relu;
+        tc_finish_params(&p);
+        return tc_launch(cfg, p, s);
+    }
+    if (force_simt || !tc_shape_ok(d)) return conv2d_s8_exact(data, weight, bias, multiplier, shift, out, d, relu, s);
     const size_t act_bytes = align_up((size_t)d.N * d.H * d.W * cpad, 1024);
     const size_t w_bytes = align_up((size_t)d.O * d.KH * d.KW * cpad, 1024);
     StreamScratch ws(s);

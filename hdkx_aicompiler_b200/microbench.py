@@ -106,6 +106,18 @@ def config5(iters, flush, hbm, tf, src):
         emit(config=5, kernel=f"nn_conv2d_s8 {name} N={N} (NCHW int8 in/out, includes operand conversion)", ms=ms,
              tops=ops_count / ms / 1e9, frac_of_2x_bf16_peak=ops_count / ms / 1e9 / (2 * tf), tcgen05_equals_cuda_core_kernel=same,
              peak_source=src)
+        # the same convolution with the tensors resident in the kernel's layout (NHWC int8, channels padded to the
+        # K-block granularity), as between the layers of a quantized network: the kernel alone
+        cp = 32 if cin <= 32 else (64 if cin <= 64 else (cin + 127) // 128 * 128)
+        xh = torch.zeros((N, h, h, cp), dtype=torch.int8, device="cuda")
+        xh[..., :cin] = x.permute(0, 2, 3, 1)
+        wh = torch.zeros((cout, k, k, cp), dtype=torch.int8, device="cuda")
+        wh[..., :cin] = w.permute(0, 2, 3, 1)
+        ms2 = timeit(lambda: ops.nn_conv2d_s8(xh, wh, b, m, sh, (s, s), (p, p), relu=True, nhwc=True), max(3, iters // 4), flush)
+        same2 = bool(torch.equal(ops.nn_conv2d_s8(xh, wh, b, m, sh, (s, s), (p, p), relu=True, nhwc=True).permute(0, 3, 1, 2),
+                                 ops.nn_conv2d_s8(x, w, b, m, sh, (s, s), (p, p), relu=True)))
+        emit(config=5, kernel=f"nn_conv2d_s8 {name} N={N} (NHWC int8 resident, kernel only)", ms=ms2, tops=ops_count / ms2 / 1e9,
+             frac_of_2x_bf16_peak=ops_count / ms2 / 1e9 / (2 * tf), equals_reference_layout_call=same2, peak_source=src)
     ops.device_status()
 
 

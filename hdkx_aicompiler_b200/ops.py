@@ -11,7 +11,7 @@ libkxc_b200.so through the C ABI of include/kxc_b200.h.
 import torch
 
 from . import _lib
-from ._lib import (BIAS, PREC_BF16, PREC_FP32, PREC_SIMT, PREC_TF32, RELU, RESIDUAL, AddDesc, Conv2dDesc, GemmDesc,
+from ._lib import (BIAS, NHWC, PREC_BF16, PREC_FP32, PREC_SIMT, PREC_TF32, RELU, RESIDUAL, AddDesc, Conv2dDesc, GemmDesc,
                    Pool2dDesc, check, load, packed)
 
 PRECISIONS = {"fp32": PREC_FP32, "tf32": PREC_TF32, "bf16": PREC_BF16, "simt": PREC_SIMT}
@@ -90,21 +90,28 @@ def nn_conv2d(data, weight, bias=None, strides=(1, 1), padding=(0, 0), dilation=
 
 
 def nn_conv2d_s8(data, weight, bias, multiplier, shift, strides=(1, 1), padding=(0, 0), dilation=(1, 1), relu=True,
-                 simt=False):
-    """int8 convolution, int32 accumulate + bias, fixed-point requantize to int8 (optionally fused relu)."""
+                 simt=False, nhwc=False):
+    """int8 convolution, int32 accumulate + bias, fixed-point requantize to int8 (optionally fused relu).
+
+    nhwc=True: data [N,H,W,C], weight [O,KH,KW,C] and the result [N,OH,OW,O] stay in the tensor-core kernel's layout
+    (a quantized pipeline's resident activations): no conversion kernels, no workspace."""
     data = _req(data, torch.int8, "nn_conv2d_s8 data")
     weight = _req(weight, torch.int8, "nn_conv2d_s8 weight")
     bias = _req(bias, torch.int32, "nn_conv2d_s8 bias")
     multiplier = _req(multiplier, torch.int32, "nn_conv2d_s8 multiplier")
     shift = _req(shift, torch.int32, "nn_conv2d_s8 shift")
-    N, C, H, W = data.shape
-    O, _, KH, KW = weight.shape
+    if nhwc:
+        N, H, W, C = data.shape
+        O, KH, KW, _ = weight.shape
+    else:
+        N, C, H, W = data.shape
+        O, _, KH, KW = weight.shape
     sh, sw = _pair(strides, 1)
     ph, pw = _pair(padding, 0)
     dh, dw = _pair(dilation, 1)
     OH, OW = conv_out_dim(H, KH, sh, ph, dh), conv_out_dim(W, KW, sw, pw, dw)
-    out = torch.empty((N, O, OH, OW), dtype=torch.int8, device=data.device)
-    desc = Conv2dDesc(N, C, H, W, O, KH, KW, sh, sw, ph, pw, dh, dw, BIAS | (RELU if relu else 0),
+    out = torch.empty((N, OH, OW, O) if nhwc else (N, O, OH, OW), dtype=torch.int8, device=data.device)
+    desc = Conv2dDesc(N, C, H, W, O, KH, KW, sh, sw, ph, pw, dh, dw, BIAS | (RELU if relu else 0) | (NHWC if nhwc else 0),
                       PREC_SIMT if simt else PREC_FP32)
     args = packed(data.data_ptr(), weight.data_ptr(), bias.data_ptr(), multiplier.data_ptr(), shift.data_ptr(),
                   out.data_ptr())

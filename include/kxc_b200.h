@@ -44,7 +44,8 @@ enum {
 enum {
     KXC_B200_BIAS = 1,     /* + bias[o]          (src/relay/op/nn/convolution.cc:72-74)       */
     KXC_B200_RESIDUAL = 2, /* + residual[n,o,h,w] (the `add` that follows in a BasicBlock)     */
-    KXC_B200_RELU = 4      /* x > 0 ? x : 0      (include/te/topi/nn.h:19-30)                 */
+    KXC_B200_RELU = 4,     /* x > 0 ? x : 0      (include/te/topi/nn.h:19-30)                 */
+    KXC_B200_NHWC = 8      /* kxc_b200_nn_conv2d_s8 only: operands already in the kernel's layout  */
 };
 
 /* arithmetic mode of the contraction */
@@ -103,7 +104,11 @@ int64_t kxc_b200_static_scratch_bytes(void);
  *                 shift int32[O], out int8[N,O,OH,OW] }.
  * y = sat8( relu?( (acc*M + 2^(30+shift)) >> (31+shift) ) ), 64-bit, arithmetic shift.
  * desc->precision: KXC_B200_PREC_SIMT forces the CUDA-core kernel, anything else takes the tcgen05
- * kind::i8 path (both are integer-exact). desc->flags: BIAS is required, RELU optional. */
+ * kind::i8 path (both are integer-exact). desc->flags: BIAS is required, RELU optional.
+ * With KXC_B200_NHWC (tensor-core path only) the tensors stay in the kernel's own layout from call to call, as in a
+ * quantized pipeline: data int8[N,H,W,C], weight int8[O,KH,KW,C], out int8[N,OH,OW,O], with C a multiple of 32 up to
+ * 128 or a multiple of 128, O a multiple of 16 and 16-byte aligned pointers; no conversion kernels run and no
+ * workspace is allocated. The values are those of the reference layout, permuted. */
 int32_t kxc_b200_nn_conv2d_s8(void** packed_args, const kxc_b200_conv2d_desc* desc, void* stream);
 
 /* nn_relu — topi::relu (include/te/topi/nn.h:19-30) via ReluCompute (src/relay/op/nn/activation.cc:14-19).

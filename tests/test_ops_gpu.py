@@ -310,3 +310,20 @@ def test_reduce_mean_keepdims_inner_axis_rejected(ops, rng):
     with pytest.raises(KxcError):
         ops.reduce_mean(dev(rng.normal(0, 1, (3, 4)).astype(f32)), (0,), True)
 
+
+@pytest.mark.parametrize("n,c,h,o,k,s,p", [(3, 64, 14, 64, 3, 1, 1), (2, 128, 9, 256, 3, 2, 1), (2, 32, 8, 48, 1, 1, 0), (1, 256, 7, 512, 1, 2, 0)])
+def test_conv2d_s8_resident_nhwc_layout(ops, rng, n, c, h, o, k, s, p):
+    """int8 convolution with the tensors already in the kernel's NHWC / OHWI layout: the same integers as the
+    reference-layout call (and therefore as the oracle), permuted."""
+    x = rng.integers(-128, 128, (n, c, h, h)).astype(np.int8)
+    w = rng.integers(-127, 128, (o, c, k, k)).astype(np.int8)
+    b = rng.integers(-1024, 1025, (o,)).astype(np.int32)
+    m = rng.integers(2 ** 30, 2 ** 31, (o,)).astype(np.int64).astype(np.int32)
+    sh = rng.integers(8, 16, (o,)).astype(np.int32)
+    exp = port.conv2d_s8_requant(x, w, b, m, sh, relu=True, stride=(s, s), pad=(p, p))
+    xh = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
+    wh = torch.from_numpy(np.ascontiguousarray(w.transpose(0, 2, 3, 1))).cuda()
+    got = ops.nn_conv2d_s8(xh, wh, dev(b), dev(m), dev(sh), (s, s), (p, p), relu=True, nhwc=True)
+    assert ops.device_status() == 0
+    assert np.array_equal(got.cpu().numpy().transpose(0, 3, 1, 2), exp)
+
