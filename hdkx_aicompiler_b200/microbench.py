@@ -64,6 +64,22 @@ def config1(iters, flush, hbm, tf, src):
              tflops=flops / ms / 1e9, frac_of_bf16_peak=flops / ms / 1e9 / tf, peak_source=src)
 
 
+    # the same layer inside a plan: operands resident in the kernels' layout, one CUDA-graph replay per call
+    # (input conversion, the row-stacked tensor-core kernel with fused bias + ReLU, conversion of the result back)
+    from . import plan, relay as R
+    xv = R.Var("input", (1, 64, 56, 56))
+    func = R.Function([xv], R.Call("nn_relu", [R.Call("nn_conv2d", [xv, R.Constant(w), R.Constant(b)],
+                                                        R.Conv2DAttrs((1, 1), (1, 1, 1, 1), (1, 1), 1))]))
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        g = plan.CompiledGraph(func, "bf16", cuda_graph=True)
+        ms = timeit(lambda: g.run(x, out=out), iters, flush)
+        _, per = g.run_timed(x, out=out)
+    names = [i[0].split()[0] for i in g.launch_info()]
+    emit(config=1, kernel="plan bf16, CUDA-graph replay: " + " + ".join(names), ms=ms, tflops=flops / ms / 1e9,
+         frac_of_bf16_peak=flops / ms / 1e9 / tf, launch_ms=dict(zip(names, [round(v, 4) for v in per])), peak_source=src)
+
+
 def config2(iters, flush, hbm, tf, src):
     g = torch.Generator(device="cuda").manual_seed(0)
     x = torch.empty(32, 64, 112, 112, device="cuda").uniform_(-1, 1, generator=g)
