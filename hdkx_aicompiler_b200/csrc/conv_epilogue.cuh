@@ -275,6 +275,40 @@ __device__ __forceinline__ void residual_fetch_rows(const EpiParams& p, const Ro
     for (int j = 0; j < 4; ++j)
         res[j] = ((m.valid >> j) & 1u) ? __ldg(reinterpret_cast<const uint4*>(base + m.pix[j] * p.Cout)) : make_uint4(0, 0, 0, 0);
 }
+// Residual-free chunk into the warp's store box: 32 rows x 128 bytes (64 channels), SWIZZLE_128B, 1024-byte aligned
+// (16-byte piece j of row r sits at piece j ^ (r & 7)). `piece0` = 0 for the first 32 channels of the box, 4 for the
+// second. The caller fences and issues the TMA store once both halves are in place.
+__device__ __forceinline__ void epilogue_box_bf16(const EpiParams& p, const uint32_t (&v)[32], int c0, uint32_t box, int piece0,
+                                                  int lane) {
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+    if (p.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + j));
+            f[j] = __fadd_rn(f[j], b.x);
+            f[j + 1] = __fadd_rn(f[j + 1], b.y);
+            f[j + 2] = __fadd_rn(f[j + 2], b.z);
+            f[j + 3] = __fadd_rn(f[j + 3], b.w);
+        }
+    }
+    if (p.relu) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = f[j] > 0.0f ? f[j] : 0.0f;
+    }
+    const uint32_t row = box + (uint32_t)lane * 128u;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        uint4 o;
+        o.x = pack_bf16(f[g * 8 + 0], f[g * 8 + 1]);
+        o.y = pack_bf16(f[g * 8 + 2], f[g * 8 + 3]);
+        o.z = pack_bf16(f[g * 8 + 4], f[g * 8 + 5]);
+        o.w = pack_bf16(f[g * 8 + 6], f[g * 8 + 7]);
+        st_shared_v4(row + ((uint32_t)((piece0 + g) ^ (lane & 7)) << 4), o);
+    }
+}
+
 // Whole warp, converged. `tile` = shared-memory address of this warp's staging tile of kPassRows x 64 bytes.
 // kPassRows = 32: the warp's 32 rows pass through the tile at once; 16: in two halves (for kernels that can
 // spare only 1 KiB of shared memory per epilogue warp).

@@ -31,6 +31,7 @@ namespace {
 using namespace sm100;
 
 constexpr int kTcThreads = 320;  // 2 control warps + 8 epilogue warps
+constexpr int kStoreBoxBytes = 32 * 128;
 constexpr int kSmemLimit = 227 * 1024;
 
 template <int KB_BYTES, int BN, int kCtas, int kMT = 1>
@@ -39,7 +40,9 @@ struct StageGeom {
     static constexpr int kABytes = kMT * kATileBytes;  // kMT pixel tiles share one B tile
     static constexpr int kBBytes = (BN / kCtas) * KB_BYTES;  // a CTA of a pair holds half of the B tile's rows
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kEpilogueBytes = 8 * kStageTileBytes;  // one staging tile per epilogue warp
+    // per epilogue warp a 4 KiB box (32 pixels x 64 channels, SWIZZLE_128B) that TMA stores read; its first half
+    // doubles as the staging tile of the per-thread store path
+    static constexpr int kEpilogueBytes = 8 * kStoreBoxBytes;
     static constexpr int kStagesRaw = (kSmemLimit - 2048 - kEpilogueBytes) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpilogueBytes + 1024;  // + slack to align the ring to 1024 B
@@ -280,7 +283,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
         const bool fast = (kOutMode == kOutNHWC_BF16) && p.vec_ok && ((p.Cout & 31) == 0);
         const bool has_res = p.residual != nullptr;
         const EpiParams ep = {p.bias, p.residual, p.out, p.Cout, p.relu};
-        const uint32_t stage_tile = ring + (uint32_t)(kStages * G::kStageBytes) + (uint32_t)((warp - 2) * kStageTileBytes);
+        const uint32_t stage_tile = ring + (uint32_t)(kStages * G::kStageBytes) + (uint32_t)((warp - 2) * kStoreBoxBytes);
+        // Residual-free launches with store maps: the warp's values go into its swizzled box and leave by TMA store
+        const bool boxed = fast && p.store_box && !has_res && (BN >= 128);
         pdl_wait();  // residual reads and output writes must not overtake earlier kernels
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -300,7 +305,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
             const int c_base = ct * BN + col0;
             uint4 res_cur[4] = {};
             RowMap rows;
-            if (fast) {
+            if (fast && !boxed) {
                 rows = make_row_map(pix, valid, lane);
                 if (has_res && c_base < p.Cout) residual_fetch_rows(ep, rows, c_base, lane, res_cur);
             }
@@ -323,7 +328,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                 if (fast && has_res && (i + 1 < kChunksPerWarp) && (c0 + 32 < p.Cout))
                     residual_fetch_rows(ep, rows, c0 + 32, lane, res_next);
                 tmem_ld_wait();
-                if (fast) {
+                if (boxed) {
+                    if ((i & 1) == 0) {  // a new 64-channel group: the previous store must have read the box
+                        if (lane == 0) bulk_wait_group_read<0>();
+                        __syncwarp();
+                    }
+                    if (c0 < p.Cout) epilogue_box_bf16(ep, v, c0, stage_tile, (i & 1) * 4, lane);
+                    if (i & 1) {
+                        fence_proxy_async_shared();
+                        __syncwarp();
+                        // lane 0's pixel is the first of the warp's 32: the box origin (a pair's missing second tile
+                        // lies beyond the last image and stores nothing)
+                        if (lane == 0 && c0 < p.Cout && n < p.N) {
+                            tma_store_4d(&p.tmOut, stage_tile, c0 - 32, ow, oh, n);
+                            bulk_commit_group();
+                        }
+                    }
+                } else if (fast) {
                     if (c0 < p.Cout) epilogue_coalesced_bf16<32>(ep, v, c0, stage_tile, lane, rows, res_cur, has_res);
                 } else {
                     epilogue_chunk<kOutMode>(p, v, c0, valid, n, oh, ow);
@@ -341,7 +362,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                     uint32_t v[32];
                     tmem_ld_32x32(t_addr + (uint32_t)(BN + i * 32), v);
                     tmem_ld_wait();
-                    if (c0 < p.Cout) epilogue_coalesced_bf16<32>(ep2, v, c0, stage_tile, lane, rows, none, false);
+                    if (boxed) {
+                        if ((i & 1) == 0) {
+                            if (lane == 0) bulk_wait_group_read<0>();
+                            __syncwarp();
+                        }
+                        if (c0 < p.Cout) epilogue_box_bf16(ep2, v, c0, stage_tile, (i & 1) * 4, lane);
+                        if (i & 1) {
+                            fence_proxy_async_shared();
+                            __syncwarp();
+                            if (lane == 0 && c0 < p.Cout && n < p.N) {
+                                tma_store_4d(&p.tmOut2, stage_tile, c0 - 32, ow, oh, n);
+                                bulk_commit_group();
+                            }
+                        }
+                    } else if (c0 < p.Cout) {
+                        epilogue_coalesced_bf16<32>(ep2, v, c0, stage_tile, lane, rows, none, false);
+                    }
                 }
             }
           }  // pixel tiles of the work item
@@ -357,6 +394,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
                 acc_phase ^= 1u;
             }
         }
+        if (boxed && lane == 0) bulk_wait_group_all();  // the stores have read shared memory and written the output
     }
 
     // ------------------------------ teardown ------------------------------
@@ -576,6 +614,34 @@ int32_t tc_status_word(int** out) {
         KXC_CUDA_TRY(cudaMemset(words[dev], 0, sizeof(int)));
     }
     *out = words[dev];
+    return KXC_B200_OK;
+}
+
+int32_t tc_bind_store(TcParams* p, const TcConfig& cfg) {
+    p->store_box = 0;
+    static const bool enabled = [] {
+        const char* e = getenv("KXC_B200_TMA_STORE");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
+    if (!enabled || cfg.dtype != kTcBF16 || cfg.out_mode != kOutNHWC_BF16 || cfg.bn < 128 || p->out == nullptr || (p->Cout & 63) != 0 ||
+        !pow2(p->BW) || !pow2(p->BH) || !pow2(p->BNI) || p->BW * p->BH * p->BNI != 128 || p->BW > 32)
+        return KXC_B200_OK;
+    // a warp's 32 consecutive tile rows as a box of the output tensor
+    const int hw = p->BW * p->BH;
+    const uint32_t sub_w = (uint32_t)p->BW;
+    const uint32_t sub_h = (uint32_t)(hw >= 32 ? 32 / p->BW : p->BH);
+    const uint32_t sub_n = (uint32_t)(hw >= 32 ? 1 : 32 / hw);
+    const uint64_t px = (uint64_t)p->Cout * 2;
+    const uint64_t dims[4] = {(uint64_t)p->Cout, (uint64_t)p->OW, (uint64_t)p->OH, (uint64_t)p->N};
+    const uint64_t strides[3] = {px, (uint64_t)p->OW * px, (uint64_t)p->OH * p->OW * px};
+    const uint32_t box[4] = {64u, sub_w, sub_h, sub_n};
+    KXC_TRY(tc_make_tmap(&p->tmOut, kTcBF16, 4, p->out, dims, strides, box, 128));
+    if (cfg.dual) {
+        if (p->out2 == nullptr) return KXC_B200_OK;
+        KXC_TRY(tc_make_tmap(&p->tmOut2, kTcBF16, 4, p->out2, dims, strides, box, 128));
+    }
+    p->store_box = 1;
     return KXC_B200_OK;
 }
 

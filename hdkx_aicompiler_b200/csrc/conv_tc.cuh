@@ -60,6 +60,9 @@ struct alignas(64) TcParams {
     const float* bias2;
     void* out2;
     int relu2;
+    // TMA stores of the output (tc_bind_store): each epilogue warp's 32 pixels x 64 channels leave as one box
+    CUtensorMap tmOut, tmOut2;
+    int store_box;               // 1 when tmOut (and tmOut2 for the two-output form) are valid
 };
 
 struct TcConfig {
@@ -104,6 +107,10 @@ int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_m
 // re-runs with the dual kernel's 128-wide tile).
 bool tc_dual_applicable(TcDType dtype, TcOutMode out_mode, int cpad, int Cout, int KH, int KW, int stride, int pad_h, int pad_w,
                         int dil_h, int dil_w);
+// After p->out (and p->out2) are final: builds the store maps when the configuration allows boxed stores (bf16 NHWC
+// output, full 128-pixel tiles whose 32-pixel quarters are boxes of the output tensor, channel count a multiple of 64)
+// and sets p->store_box; otherwise leaves the per-thread store path in place. KXC_B200_TMA_STORE=0 disables it.
+int32_t tc_bind_store(TcParams* p, const TcConfig& cfg);
 int32_t tc_setup_dual(TcParams* p, TcConfig* cfg, const void* act_nhwc, const void* w_packed, const void* w2_packed, int N,
                       int H, int W, int cpad, int Cout, int KH, int KW, int stride, int pad_h, int pad_w);
 

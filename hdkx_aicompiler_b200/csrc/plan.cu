@@ -837,6 +837,7 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
             st.params.residual = st.in1 >= 0 ? pl->storage(st.in1) : nullptr;
             st.params.out = st.out_is_graph_output ? nullptr : pl->storage(st.out);
             if (st.direct == 3) KXC_TRY(rowstack3x3_bind(&st.params));
+            if (st.direct == 0 && pw.mode == 0 && !st.out_is_graph_output) KXC_TRY(tc_bind_store(&st.params, st.cfg));
             (void)ov;
         } else if (st.kind == SKind::Gemm) {
             const PackedWeight& pw = pl->weights[st.weight];
