@@ -14,6 +14,8 @@ vpp = ctypes.POINTER(ctypes.c_void_p)
 OK = 0
 BIAS, RESIDUAL, RELU, NHWC = 1, 2, 4, 8
 PREC_FP32, PREC_TF32, PREC_BF16, PREC_SIMT = 0, 1, 2, 3
+# cast dtype codes: the reference's CastAttrs codes (src/relay/op/tensor/transform.cc:84-103)
+DT_F32, DT_I32, DT_I64, DT_F64, DT_BOOL, DT_I8, DT_U8 = 0, 1, 2, 3, 4, 5, 6
 
 
 class KxcError(RuntimeError):
@@ -40,6 +42,10 @@ class SoftmaxDesc(ctypes.Structure):
 
 class ReduceDesc(ctypes.Structure):
     _fields_ = [("rank", i32), ("shape", i64 * 6), ("num_axes", i32), ("axes", i32 * 6), ("keepdims", i32)]
+
+
+class TransposeDesc(ctypes.Structure):
+    _fields_ = [("rank", i32), ("shape", i64 * 6), ("num_axes", i32), ("perm", i32 * 6), ("elem_bytes", i32)]
 
 
 class Pool2dDesc(ctypes.Structure):
@@ -70,6 +76,10 @@ SYMBOLS = {
     "kxc_b200_nn_global_avg_pool2d": (i32, [vpp, i32, i32, i32, i32, vp]),
     "kxc_b200_softmax": (i32, [vpp, ctypes.POINTER(SoftmaxDesc), vp]),
     "kxc_b200_reduce_mean": (i32, [vpp, ctypes.POINTER(ReduceDesc), vp]),
+    "kxc_b200_matmul": (i32, [vpp, i32, i32, i32, i32, vp]),
+    "kxc_b200_transpose": (i32, [vpp, ctypes.POINTER(TransposeDesc), vp]),
+    "kxc_b200_reshape": (i32, [vpp, i64, i32, vp]),
+    "kxc_b200_cast": (i32, [vpp, i64, i32, i32, vp]),
     "kxc_b200_nn_flatten": (i32, [vpp, i64, vp]),
     "kxc_b200_nn_gemm": (i32, [vpp, ctypes.POINTER(GemmDesc), vp]),
 }

@@ -124,13 +124,38 @@ extern "C" int32_t kxc_b200_nn_gemm(void** packed_args, const kxc_b200_gemm_desc
     if (desc->m == 0) return KXC_B200_OK;
     if (!a || !b || !out || (desc->has_c && !c)) return fail(KXC_B200_ERR_INVALID, "nn_gemm: null tensor pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    switch (desc->precision) {
+    kxc_b200_gemm_desc g = *desc;
+    if (!g.has_c) g.transB = 1;  // nn_dense: the weight is always [N, K]
+    switch (g.precision) {
         case KXC_B200_PREC_FP32:
-            return gemm_fp32_exact(a, b, c, out, *desc, s);
+            return gemm_fp32_exact(a, b, c, out, g, s);
         case KXC_B200_PREC_TF32:
         case KXC_B200_PREC_BF16:
-            return gemm_tensor_core(a, b, c, out, *desc, s);
+            return gemm_tensor_core(a, b, c, out, g, s);
         default:
-            return fail(KXC_B200_ERR_INVALID, "nn_gemm: unknown precision %d", desc->precision);
+            return fail(KXC_B200_ERR_INVALID, "nn_gemm: unknown precision %d", g.precision);
+    }
+}
+
+extern "C" int32_t kxc_b200_matmul(void** packed_args, int32_t m, int32_t n, int32_t k, int32_t precision, void* stream) {
+    KXC_TRY(require_device());
+    if (!packed_args) return fail(KXC_B200_ERR_INVALID, "matmul: bad arguments");
+    if (m < 0 || n < 0 || k <= 0) return fail(KXC_B200_ERR_INVALID, "matmul: bad shape");
+    if (m == 0 || n == 0) return KXC_B200_OK;
+    const float* a = static_cast<const float*>(packed_args[0]);
+    const float* b = static_cast<const float*>(packed_args[1]);
+    float* out = static_cast<float*>(packed_args[2]);
+    if (!a || !b || !out) return fail(KXC_B200_ERR_INVALID, "matmul: null tensor pointer");
+    // b is [K, N] and nothing is added: the internal form of that is "no C, transB = 0"
+    const kxc_b200_gemm_desc g{m, n, k, 1.0f, 1.0f, 0, 0, 0, precision};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (precision) {
+        case KXC_B200_PREC_FP32:
+            return gemm_fp32_exact(a, b, nullptr, out, g, s);
+        case KXC_B200_PREC_TF32:
+        case KXC_B200_PREC_BF16:
+            return gemm_tensor_core(a, b, nullptr, out, g, s);
+        default:
+            return fail(KXC_B200_ERR_INVALID, "matmul: unknown precision %d", precision);
     }
 }

@@ -123,7 +123,7 @@ int32_t gemm_tensor_core(const float* a, const float* b, const float* c, float* 
     uint8_t* ap = static_cast<uint8_t*>(ws.ptr);
     uint8_t* bp = ap + a_bytes;
     KXC_TRY(convert_rows(a, ap, dt, g.m, g.k, kpad, s));
-    if (g.transB || !g.has_c) {
+    if (g.transB) {
         KXC_TRY(convert_rows(b, bp, dt, g.n, g.k, kpad, s));  // b is [N, K]
     } else {
         KXC_TRY(nchw_to_nhwc(b, bp, dt, 1, g.k, g.n, kpad, s));  // b is [K, N] -> [N, Kpad]

@@ -227,6 +227,114 @@ def reduce_mean(x, axes, keepdims=True):
     return out
 
 
+_CAST_CODES = {torch.float32: _lib.DT_F32, torch.int32: _lib.DT_I32, torch.int64: _lib.DT_I64, torch.float64: _lib.DT_F64,
+               torch.int8: _lib.DT_I8, torch.uint8: _lib.DT_U8}
+_CAST_NAMES = {"float32": torch.float32, "int32": torch.int32, "int64": torch.int64, "float64": torch.float64,
+               "int8": torch.int8, "uint8": torch.uint8}
+
+
+def _dev(t, name):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name}: expected a CUDA tensor (libkxc_b200 has no CPU path)")
+    return t.contiguous()
+
+
+def matmul(a, b, precision="tf32"):
+    """matmul(a[M,K], b[K,N]); rank-2 operands only, like the reference's type inference."""
+    a = _req(a, torch.float32, "matmul a")
+    b = _req(b, torch.float32, "matmul b")
+    if a.dim() != 2 or b.dim() != 2:
+        raise ValueError("matmul currently expects rank-2 inputs")
+    if a.shape[1] != b.shape[0]:
+        raise ValueError("matmul reduction dimension mismatch")
+    out = torch.empty((a.shape[0], b.shape[1]), dtype=torch.float32, device=a.device)
+    check("matmul", load().kxc_b200_matmul(packed(a.data_ptr(), b.data_ptr(), out.data_ptr()), a.shape[0], b.shape[1],
+                                           a.shape[1], PRECISIONS[precision], _stream(a)))
+    return out
+
+
+def transpose(x, axes=None):
+    """transpose(x, axes): output dimension i is input dimension axes[i]; no axes reverses the dimensions."""
+    x = _dev(x, "transpose")
+    if not 1 <= x.dim() <= 6:
+        raise ValueError("transpose expects rank 1..6")
+    axes = [int(a) for a in axes] if axes else []
+    if axes and len(axes) != x.dim():
+        raise ValueError("transpose perm rank mismatch")
+    norm = [a % x.dim() for a in axes] if axes else list(range(x.dim() - 1, -1, -1))
+    if len(set(norm)) != len(norm):
+        raise ValueError("transpose duplicate axis")
+    out = torch.empty([x.shape[a] for a in norm], dtype=x.dtype, device=x.device)
+    desc = _lib.TransposeDesc(x.dim(), (_lib.i64 * 6)(*x.shape), len(axes), (_lib.i32 * 6)(*axes), x.element_size())
+    check("transpose", load().kxc_b200_transpose(packed(x.data_ptr(), out.data_ptr()), desc, _stream(x)))
+    return out
+
+
+def reshape_out_shape(in_shape, newshape, allowzero=False):
+    """The output shape ReshapeInferType derives (src/relay/type_infer.cc:454-512): positive entries as given, 0 copies
+    the input's extent at that position unless allowzero, one -1 is inferred from the element count."""
+    in_shape = [int(d) for d in in_shape]
+    total = 1
+    for d in in_shape:
+        total *= d
+    out, infer, known = [], -1, 1
+    for i, dim in enumerate(int(d) for d in newshape):
+        if dim > 0:
+            out.append(dim)
+            known *= dim
+        elif dim == 0:
+            if allowzero:
+                out.append(0)
+                known = 0
+            else:
+                if i >= len(in_shape):
+                    raise ValueError("reshape 0-dim copy index exceeds input rank")
+                out.append(in_shape[i])
+                known *= in_shape[i]
+        elif dim == -1:
+            if infer >= 0:
+                raise ValueError("reshape allows at most one inferred -1 dimension")
+            infer = len(out)
+            out.append(-1)
+        else:
+            raise ValueError("reshape only supports positive, 0, and -1 dimensions")
+    if infer >= 0 and known > 0:
+        if total % known != 0:
+            raise ValueError("reshape cannot infer -1 dimension from element count")
+        out[infer] = total // known
+    elif infer < 0 and total != known:
+        raise ValueError("reshape element count mismatch")
+    return out
+
+
+def reshape(x, newshape, allowzero=False):
+    x = _dev(x, "reshape")
+    out = torch.empty(reshape_out_shape(x.shape, newshape, allowzero), dtype=x.dtype, device=x.device)
+    check("reshape", load().kxc_b200_reshape(packed(x.data_ptr(), out.data_ptr()), x.numel(), x.element_size(), _stream(x)))
+    return out
+
+
+def cast(x, dtype):
+    """cast(x, dtype): dtype is a torch dtype or the reference's dtype name ("float32", "int32", "int64", "float64",
+    "int8", "uint8"); bool is refused by the library."""
+    x = _dev(x, "cast")
+    if isinstance(dtype, str):
+        if dtype == "bool":
+            to, tdt = _lib.DT_BOOL, torch.bool
+        elif dtype not in _CAST_NAMES:
+            raise ValueError(f"cast has unsupported dtype: {dtype}")
+        else:
+            tdt = _CAST_NAMES[dtype]
+            to = _CAST_CODES[tdt]
+    else:
+        tdt = dtype
+        to = _lib.DT_BOOL if dtype == torch.bool else _CAST_CODES.get(dtype, -1)
+    frm = _lib.DT_BOOL if x.dtype == torch.bool else _CAST_CODES.get(x.dtype, -1)
+    out = torch.empty(x.shape, dtype=tdt, device=x.device)
+    check("cast", load().kxc_b200_cast(packed(x.data_ptr(), out.data_ptr()), x.numel(), frm, to, _stream(x)))
+    return out
+
+
 def nn_flatten(x):
     x = _req(x, torch.float32, "nn_flatten")
     out = torch.empty((x.shape[0], x.numel() // max(x.shape[0], 1)), dtype=torch.float32, device=x.device)

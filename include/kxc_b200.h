@@ -167,6 +167,44 @@ typedef struct kxc_b200_reduce_desc {
 } kxc_b200_reduce_desc;
 int32_t kxc_b200_reduce_mean(void** packed_args, const kxc_b200_reduce_desc* desc, void* stream);
 
+/* matmul — topi::matmul (include/te/topi/nn.h:82-101) via MatMulCompute (src/relay/op/tensor/math.cc:82-87):
+ * out[i,j] = sum over k, in ascending order, of a[i,k] * b[k,j]; rank-2 operands only (MatMulInferType,
+ * src/relay/type_infer.cc:280-298). packed_args = { a[M,K], b[K,N], out[M,N] }; precision = KXC_B200_PREC_*. */
+int32_t kxc_b200_matmul(void** packed_args, int32_t m, int32_t n, int32_t k, int32_t precision, void* stream);
+
+/* transpose — topi::transpose (include/te/topi/transform.h:20-52) via TransposeCompute
+ * (src/relay/op/tensor/transform.cc:206-212): out dimension i is input dimension perm[i]; num_axes = 0 reverses the
+ * dimensions; negative axes count from the end (TransposeInferType, src/relay/type_infer.cc:520-548). Elements are moved
+ * as bytes, so any dtype of 1, 4 or 8 bytes works. packed_args = { x, out } (not in place). */
+typedef struct kxc_b200_transpose_desc {
+    int32_t rank;
+    int64_t shape[6]; /* of the input */
+    int32_t num_axes; /* 0 or rank */
+    int32_t perm[6];
+    int32_t elem_bytes;
+} kxc_b200_transpose_desc;
+int32_t kxc_b200_transpose(void** packed_args, const kxc_b200_transpose_desc* desc, void* stream);
+
+/* reshape — ReshapeCompute (src/relay/op/tensor/transform.cc:185-204): the flat element order is unchanged, so this is
+ * a copy (a no-op when both pointers are equal). The caller resolves 0 / -1 entries of newshape as ReshapeInferType
+ * does (src/relay/type_infer.cc:454-512). packed_args = { x, out }. */
+int32_t kxc_b200_reshape(void** packed_args, int64_t numel, int32_t elem_bytes, void* stream);
+
+/* cast — topi::cast (include/te/topi/elemwise.h:113-122) via CastCompute (src/relay/op/tensor/transform.cc:214-224);
+ * dtype codes are the reference's CastAttrs codes (DTypeFromCastCode, transform.cc:84-103). Conversion semantics are
+ * those of CodeGenLLVM::CastValue (src/codegen/codegen_llvm.cc:219-248). A float outside the integer type's range is
+ * undefined in the reference and saturates here; bool (code 4) is refused. packed_args = { x, out }. */
+enum {
+    KXC_B200_DT_F32 = 0,
+    KXC_B200_DT_I32 = 1,
+    KXC_B200_DT_I64 = 2,
+    KXC_B200_DT_F64 = 3,
+    KXC_B200_DT_BOOL = 4,
+    KXC_B200_DT_I8 = 5,
+    KXC_B200_DT_U8 = 6
+};
+int32_t kxc_b200_cast(void** packed_args, int64_t numel, int32_t from, int32_t to, void* stream);
+
 /* nn_global_avg_pool2d — topi::global_avg_pool2d (include/te/topi/nn.h:260-287).
  * packed_args = { x[N,C,H,W], out[N,C,1,1] }. The sum runs sequentially over (h,w) per plane, like
  * the reference, so the result is bit-exact. */

@@ -285,6 +285,79 @@ int32_t kxc_oracle_gemm_f32(const float* a, const float* b, const float* c, floa
     return 0;
 }
 
+/* ---- matmul: include/te/topi/nn.h:82-101. acc = 0; acc = acc + a[i,k] * b[k,j], k ascending. ---- */
+int32_t kxc_oracle_matmul_f32(const float* a, const float* b, float* out, int64_t M, int64_t Nn, int64_t K) {
+    for (int64_t i = 0; i < M; ++i)
+        for (int64_t j = 0; j < Nn; ++j) {
+            float acc = 0.0f;
+            for (int64_t k = 0; k < K; ++k) acc = acc + a[i * K + k] * b[k * Nn + j];
+            out[i * Nn + j] = acc;
+        }
+    return 0;
+}
+
+/* ---- transpose: include/te/topi/transform.h:20-52. Output dimension i has the extent of input dimension perm[i]; the
+ * input index along perm[i] is the output index along i. Elements are `elem` bytes wide. ---- */
+int32_t kxc_oracle_transpose(const void* x, void* out, int32_t rank, const int64_t* shape, const int32_t* perm, int32_t elem) {
+    int64_t istride[8], oshape[8], idx[8], total = 1;
+    if (rank < 1 || rank > 8) return 1;
+    int64_t st = 1;
+    for (int i = rank - 1; i >= 0; --i) {
+        istride[i] = st;
+        st *= shape[i];
+    }
+    for (int i = 0; i < rank; ++i) {
+        oshape[i] = shape[perm[i]];
+        total *= oshape[i];
+        idx[i] = 0;
+    }
+    const char* src = (const char*)x;
+    char* dst = (char*)out;
+    for (int64_t o = 0; o < total; ++o) {
+        int64_t off = 0;
+        for (int i = 0; i < rank; ++i) off += idx[i] * istride[perm[i]];
+        memcpy(dst + o * elem, src + off * elem, (size_t)elem);
+        for (int i = rank - 1; i >= 0; --i) {
+            if (++idx[i] < oshape[i]) break;
+            idx[i] = 0;
+        }
+    }
+    return 0;
+}
+
+/* ---- cast: include/te/topi/elemwise.h:113-122, scalar rule CodeGenLLVM::CastValue (src/codegen/codegen_llvm.cc:219-248).
+ * dtype codes as in DTypeFromCastCode (src/relay/op/tensor/transform.cc:84-103): 0 f32, 1 i32, 2 i64, 3 f64, 5 i8, 6 u8.
+ * Every pair below is the C conversion, which is what sext/zext/trunc, sitofp/uitofp, fptosi/fptoui and fpext/fptrunc
+ * compute for values the target can hold (a float outside an integer target's range is undefined there and here). ---- */
+#define KXC_CAST_LOOP(S, D)                                             \
+    {                                                                   \
+        const S* s_ = (const S*)x;                                      \
+        D* d_ = (D*)out;                                                \
+        for (int64_t i = 0; i < n; ++i) d_[i] = (D)s_[i];               \
+        return 0;                                                       \
+    }
+#define KXC_CAST_TO(S)                                   \
+    switch (to) {                                        \
+        case 0: KXC_CAST_LOOP(S, float)                  \
+        case 1: KXC_CAST_LOOP(S, int32_t)                \
+        case 2: KXC_CAST_LOOP(S, int64_t)                \
+        case 3: KXC_CAST_LOOP(S, double)                 \
+        case 5: KXC_CAST_LOOP(S, int8_t)                 \
+        case 6: KXC_CAST_LOOP(S, uint8_t)                \
+        default: return 1;                               \
+    }
+int32_t kxc_oracle_cast(const void* x, void* out, int64_t n, int32_t from, int32_t to) {
+    switch (from) {
+        case 0: KXC_CAST_TO(float)
+        case 1: KXC_CAST_TO(int32_t)
+        case 2: KXC_CAST_TO(int64_t)
+        case 3: KXC_CAST_TO(double)
+        case 5: KXC_CAST_TO(int8_t)
+        case 6: KXC_CAST_TO(uint8_t)
+        default: return 1;
+    }
+}
+
 /* ---- operand roundings for the reduced-precision modes (no reference counterpart) ---- */
 void kxc_oracle_round_bf16(const float* x, float* out, int64_t n) {
     for (int64_t i = 0; i < n; ++i) {

@@ -69,6 +69,10 @@ int32_t kxc_oracle_reduce_mean_f32(const float* x, float* out, int32_t rank, con
 /* out[i,j] = sum_k a[i,k]*b[j,k]  (b is [Nn,K]) */
 int32_t kxc_oracle_dense_f32(const float* a, const float* b, float* out, int64_t M, int64_t Nn, int64_t K);
 
+int32_t kxc_oracle_matmul_f32(const float* a, const float* b, float* out, int64_t M, int64_t Nn, int64_t K);
+int32_t kxc_oracle_transpose(const void* x, void* out, int32_t rank, const int64_t* shape, const int32_t* perm, int32_t elem);
+int32_t kxc_oracle_cast(const void* x, void* out, int64_t n, int32_t from, int32_t to);
+
 /* nn_gemm: transA must be 0; transB=1 -> b is [Nn,K], transB=0 -> b is [K,Nn]; c broadcast [Nn]. */
 int32_t kxc_oracle_gemm_f32(const float* a, const float* b, const float* c, float* out, int64_t M, int64_t Nn,
                             int64_t K, float alpha, float beta, int32_t transA, int32_t transB);

@@ -43,6 +43,9 @@ def lib():
         _lib.kxc_oracle_dense_f32.argtypes = [vp, vp, vp] + [i64] * 3
         _lib.kxc_oracle_softmax_f32.argtypes = [vp, vp] + [i64] * 3
         _lib.kxc_oracle_reduce_mean_f32.argtypes = [vp, vp, i32, vp, vp]
+        _lib.kxc_oracle_matmul_f32.argtypes = [vp, vp, vp] + [i64] * 3
+        _lib.kxc_oracle_transpose.argtypes = [vp, vp, i32, vp, vp, i32]
+        _lib.kxc_oracle_cast.argtypes = [vp, vp, i64, i32, i32]
         _lib.kxc_oracle_gemm_f32.argtypes = [vp] * 4 + [i64] * 3 + [ctypes.c_float] * 2 + [i32] * 2
         _lib.kxc_oracle_round_bf16.argtypes = [vp, vp, i64]
         _lib.kxc_oracle_round_tf32.argtypes = [vp, vp, i64]
@@ -188,6 +191,45 @@ def reduce_mean(x, axes, keepdims=True):
     out_shape = [1 if d in axes else n for d, n in enumerate(x.shape) if keepdims or d not in axes]
     out = np.empty(out_shape, dtype=np.float32)
     _check(lib().kxc_oracle_reduce_mean_f32(_p(x), _p(out), x.ndim, _p(shape), _p(flags)), "reduce_mean")
+    return out
+
+
+CAST_CODES = {np.dtype(np.float32): 0, np.dtype(np.int32): 1, np.dtype(np.int64): 2, np.dtype(np.float64): 3,
+              np.dtype(np.int8): 5, np.dtype(np.uint8): 6}
+
+
+def matmul(a, b):
+    """include/te/topi/nn.h:82-101: a[M,K] x b[K,N], k ascending."""
+    a, b = _c(a, np.float32), _c(b, np.float32)
+    M, K = a.shape
+    Nn = b.shape[1]
+    out = np.empty((M, Nn), dtype=np.float32)
+    _check(lib().kxc_oracle_matmul_f32(_p(a), _p(b), _p(out), M, Nn, K), "matmul")
+    return out
+
+
+def transpose(x, axes=None):
+    """include/te/topi/transform.h:20-52; no axes reverses the dimensions."""
+    x = np.ascontiguousarray(x)
+    perm = [a % x.ndim for a in axes] if axes else list(range(x.ndim - 1, -1, -1))
+    out = np.empty([x.shape[a] for a in perm], dtype=x.dtype)
+    if x.size:
+        shape = np.asarray(x.shape, dtype=np.int64)
+        permv = np.asarray(perm, dtype=np.int32)
+        _check(lib().kxc_oracle_transpose(_p(x), _p(out), x.ndim, _p(shape), _p(permv), x.dtype.itemsize), "transpose")
+    return out
+
+
+def reshape(x, out_shape):
+    """src/relay/op/tensor/transform.cc:185-204: the flat order is kept."""
+    return np.ascontiguousarray(x).reshape(out_shape).copy()
+
+
+def cast(x, dtype):
+    """include/te/topi/elemwise.h:113-122 with CodeGenLLVM::CastValue's scalar rule (src/codegen/codegen_llvm.cc:219-248)."""
+    x = np.ascontiguousarray(x)
+    out = np.empty(x.shape, dtype=dtype)
+    _check(lib().kxc_oracle_cast(_p(x), _p(out), x.size, CAST_CODES[x.dtype], CAST_CODES[out.dtype]), "cast")
     return out
 
 

@@ -45,7 +45,7 @@ def _cpu_tag():
     return "generic"
 
 
-_VLA = re.compile(r"^  (float|int32_t|double|int64_t|int8_t) ([A-Za-z_0-9]+)\[(.*)\];$", re.M)
+_VLA = re.compile(r"^  (float|int32_t|double|int64_t|int8_t|uint8_t) ([A-Za-z_0-9]+)\[(.*)\];$", re.M)
 
 
 def _heapify(src):
@@ -85,7 +85,7 @@ def kernel(program):
             with open(csrc, "w") as f:
                 f.write(_heapify(res.stdout))
             tmp = so + f".tmp{os.getpid()}"
-            subprocess.check_call(["gcc", "-O3", "-march=native", "-ffp-contract=off", "-fno-fast-math", "-w",
+            subprocess.check_call(["gcc", "-O3", "-march=native", "-ffp-contract=off", "-fno-fast-math", "-w", "-Dcast(x)=(x)",
                                    "-shared", "-fPIC", csrc, "-o", tmp, "-lm"])
             os.replace(tmp, so)
         lib = ctypes.CDLL(so)
@@ -183,6 +183,34 @@ def reduce_mean(x, axes, keepdims=True):
     axes = sorted(a % x.ndim for a in axes)
     out_shape = [1 if d in axes else n for d, n in enumerate(x.shape) if keepdims or d not in axes]
     return run(f"in x float32 {_shape(x)};reduce_mean p x {','.join(map(str, axes))} {1 if keepdims else 0}", [x], out_shape)
+
+
+_NAMES = {np.dtype(np.float32): "float32", np.dtype(np.int32): "int32", np.dtype(np.int64): "int64",
+          np.dtype(np.float64): "float64", np.dtype(np.int8): "int8", np.dtype(np.uint8): "uint8"}
+_CAST_CODES = {"float32": 0, "int32": 1, "int64": 2, "float64": 3, "int8": 5, "uint8": 6}
+
+
+def matmul(a, b):
+    return run(f"in a float32 {_shape(a)};in b float32 {_shape(b)};matmul m a b", [a, b], (a.shape[0], b.shape[1]))
+
+
+def transpose(x, axes=None):
+    perm = [a % x.ndim for a in axes] if axes else list(range(x.ndim - 1, -1, -1))
+    spec = ",".join(str(int(a)) for a in axes) if axes else "-"
+    return run(f"in x {_NAMES[x.dtype]} {_shape(x)};transpose t x {spec}", [x], [x.shape[a] for a in perm], x.dtype)
+
+
+def reshape(x, newshape, out_shape):
+    """`newshape` as the attribute holds it (0 and -1 allowed); `out_shape` is the resolved shape of the result."""
+    spec = ",".join(str(int(d)) for d in newshape)
+    return run(f"in x {_NAMES[x.dtype]} {_shape(x)};reshape r x {spec}", [x], out_shape, x.dtype)
+
+
+def cast(x, dtype):
+    """The generated C calls `cast(v)`, which CodeGenC leaves undefined (src/codegen/codegen_c.cc:155-169); kernel()
+    compiles with -Dcast(x)=(x), so the conversion is the assignment's, i.e. what CodeGenLLVM::CastValue emits."""
+    dtype = np.dtype(dtype)
+    return run(f"in x {_NAMES[x.dtype]} {_shape(x)};cast c x {_CAST_CODES[_NAMES[dtype]]}", [x], x.shape, dtype)
 
 
 def dense(a, b):

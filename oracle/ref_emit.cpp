@@ -18,6 +18,7 @@
 //   max_pool2d OUT X kh,kw sh,sw pt,pl,pb,pr ceil   (avg_pool2d likewise)
 //   dense OUT X W | gemm OUT A B C alpha beta transA transB
 //   softmax OUT X axis | reduce_mean OUT X a0,a1,... keepdims
+//   matmul OUT A B | transpose OUT X a0,a1,...|- | reshape OUT X d0,d1,... | cast OUT X code
 // The function's parameters are the `in` tensors in declaration order; its result is the last OUT.
 // Each op may appear once per function: CodeGenC names buffers after the op (codegen_c.cc:38-46).
 //
@@ -233,6 +234,15 @@ int main(int argc, char** argv) {
             } else if (op == "reduce_mean") {
                 out = kxc::Call(kxc::relay::Op::Get("reduce_mean"), {get(t[2])},
                                 kxc::relay::ReduceMeanAttrs::Create(Ints(t[3]), std::atoi(t[4].c_str())));
+            } else if (op == "matmul") {
+                out = kxc::Call(kxc::relay::Op::Get("matmul"), {get(t[2]), get(t[3])});
+            } else if (op == "transpose") {
+                out = kxc::Call(kxc::relay::Op::Get("transpose"), {get(t[2])},
+                                kxc::relay::TransposeAttrs::Create(t[3] == "-" ? std::vector<int64_t>{} : Ints(t[3])));
+            } else if (op == "reshape") {
+                out = kxc::Call(kxc::relay::Op::Get("reshape"), {get(t[2])}, kxc::relay::ReshapeAttrs::Create(Ints(t[3]), 0));
+            } else if (op == "cast") {
+                out = kxc::Call(kxc::relay::Op::Get("cast"), {get(t[2])}, kxc::relay::CastAttrs::Create(std::atoi(t[3].c_str())));
             } else if (op == "dense") {
                 out = kxc::Call(kxc::relay::Op::Get("nn_dense"), {get(t[2]), get(t[3])},
                                 kxc::relay::DenseAttrs::Create(0, ""));

@@ -327,3 +327,109 @@ def test_conv2d_s8_resident_nhwc_layout(ops, rng, n, c, h, o, k, s, p):
     assert ops.device_status() == 0
     assert np.array_equal(got.cpu().numpy().transpose(0, 3, 1, 2), exp)
 
+
+
+# ---------------------------------------------------------------- matmul / transpose / reshape / cast
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (5, 11, 37), (33, 100, 64), (130, 72, 200)])
+def test_matmul_fp32_mode_bit_exact(ops, rng, M, N, K):
+    a = rng.normal(size=(M, K)).astype(f32)
+    b = rng.normal(size=(K, N)).astype(f32)
+    assert_bit_exact(host(ops.matmul(dev(a), dev(b), precision="fp32")), port.matmul(a, b), "matmul fp32")
+
+
+@pytest.mark.parametrize("precision,rounder", [("tf32", port.round_tf32), ("bf16", port.round_bf16)])
+@pytest.mark.parametrize("M,N,K", [(2, 4, 3), (33, 1000, 512), (300, 256, 64)])
+def test_matmul_tensor_core(ops, rng, M, N, K, precision, rounder):
+    a = (rng.normal(size=(M, K)) / np.sqrt(K)).astype(f32)
+    b = rng.normal(size=(K, N)).astype(f32)
+    got = host(ops.matmul(dev(a), dev(b), precision=precision))
+    assert ops.device_status() == 0
+    u = 2.0 ** -11 if precision == "tf32" else 2.0 ** -8
+    bound = (2 * u + u * u) * port.matmul(np.abs(a), np.abs(b)) + 1e-5
+    assert np.all(np.abs(got - port.matmul(a, b)) <= bound), f"matmul {precision}: exceeds the operand-rounding bound"
+    max_abs, max_rel = ref_metric(got, port.matmul(rounder(a), rounder(b)))
+    assert min(max_abs, max_rel) <= 2e-5 * max(1.0, np.sqrt(K) / 8)
+
+
+def test_matmul_shape_errors(ops):
+    z = torch.zeros(2, 3, device="cuda")
+    with pytest.raises(ValueError, match="reduction dimension mismatch"):
+        ops.matmul(z, z)
+    with pytest.raises(ValueError, match="rank-2"):
+        ops.matmul(z, torch.zeros(3, 2, 2, device="cuda"))
+
+
+@pytest.mark.parametrize("shape,axes", [
+    ((7,), None), ((5, 9), None), ((5, 9), (0, 1)), ((2, 3, 4, 5), (0, 2, 3, 1)), ((2, 3, 4, 5), (0, 3, 1, 2)),
+    ((2, 3, 4, 5), (3, 2, 1, 0)), ((2, 3, 4, 5), (1, 0, 2, 3)), ((2, 3, 4, 5), (0, 1, 3, 2)), ((2, 3, 4, 5), (-1, 0, 1, 2)),
+    ((2, 3, 4, 5, 6, 7), (5, 3, 1, 4, 2, 0)), ((2, 3, 4, 5, 6, 7), None), ((1, 64, 1, 33), (3, 2, 1, 0)),
+    ((4, 64, 56, 56), (0, 2, 3, 1)), ((4, 56, 56, 64), (0, 3, 1, 2)), ((1000, 513), (1, 0)), ((33, 1, 65), (2, 1, 0)),
+    ((0, 4), (1, 0)), ((3, 100, 37), (1, 0, 2)),
+])
+def test_transpose_bit_exact(ops, rng, shape, axes):
+    x = rng.normal(size=shape).astype(f32)
+    assert_bit_exact(host(ops.transpose(dev(x), axes)), port.transpose(x, axes), f"transpose {shape} {axes}")
+
+
+@pytest.mark.parametrize("dtype", [np.int8, np.uint8, np.int32, np.int64, np.float64])
+def test_transpose_other_dtypes(ops, rng, dtype):
+    x = rng.integers(0, 100, (6, 70, 35)).astype(dtype)
+    for axes in ((2, 1, 0), (0, 2, 1), (1, 0, 2)):
+        assert_bit_exact(host(ops.transpose(dev(x), axes)), port.transpose(x, axes), f"transpose {np.dtype(dtype).name} {axes}")
+
+
+def test_transpose_bad_axes(ops):
+    z = torch.zeros(2, 3, device="cuda")
+    with pytest.raises(ValueError, match="duplicate axis"):
+        ops.transpose(z, (0, 0))
+    with pytest.raises(ValueError, match="perm rank mismatch"):
+        ops.transpose(z, (0,))
+
+
+def test_reshape(ops, rng):
+    x = rng.normal(size=(2, 3, 4, 5)).astype(f32)
+    for newshape, expect in (((0, -1, 5), (2, 12, 5)), ((120,), (120,)), ((-1, 10), (12, 10)), ((2, 3, 20), (2, 3, 20))):
+        got = ops.reshape(dev(x), newshape)
+        assert tuple(got.shape) == expect
+        assert_bit_exact(host(got), port.reshape(x, expect), f"reshape {newshape}")
+    for bad, msg in (((7, -1), "cannot infer"), ((-1, -1), "at most one"), ((5, 5), "element count mismatch"), ((-2, 60), "only supports")):
+        with pytest.raises(ValueError, match=msg):
+            ops.reshape(dev(x), bad)
+
+
+_CAST_INPUTS = {
+    np.float32: lambda rng: np.concatenate([rng.normal(0, 40, 5000), [0.0, -0.0, 0.999, -0.999, 126.5, -127.5]]).astype(np.float32),
+    np.float64: lambda rng: np.concatenate([rng.normal(0, 40, 5000), [1.0 + 2.0 ** -30, 1e-50, -3.999999]]).astype(np.float64),
+    np.int32: lambda rng: np.concatenate([rng.integers(-2 ** 31, 2 ** 31, 5000), [16777217, -16777217, 2 ** 31 - 1, -2 ** 31]]).astype(np.int32),
+    np.int64: lambda rng: np.concatenate([rng.integers(-2 ** 62, 2 ** 62, 5000), [2 ** 53 + 1, 2 ** 40 + 5, -7]]).astype(np.int64),
+    np.int8: lambda rng: rng.integers(-128, 128, 5000).astype(np.int8),
+    np.uint8: lambda rng: rng.integers(0, 256, 5000).astype(np.uint8),
+}
+_TORCH = {np.float32: torch.float32, np.float64: torch.float64, np.int32: torch.int32, np.int64: torch.int64, np.int8: torch.int8,
+          np.uint8: torch.uint8}
+
+
+@pytest.mark.parametrize("src", list(_CAST_INPUTS))
+@pytest.mark.parametrize("dst", list(_CAST_INPUTS))
+def test_cast_bit_exact(ops, rng, src, dst):
+    x = _CAST_INPUTS[src](rng)
+    if np.dtype(src).kind == "f" and np.dtype(dst).kind in "iu":
+        # a float the target cannot hold is undefined in the reference: keep the inputs inside the target's range
+        info = np.iinfo(dst)
+        x = np.clip(x, max(info.min, -2.0 ** 31), min(info.max, 2.0 ** 31 - 128)).astype(src)
+    assert_bit_exact(host(ops.cast(dev(x), _TORCH[dst])), port.cast(x, dst), f"cast {np.dtype(src).name} -> {np.dtype(dst).name}")
+
+
+def test_cast_out_of_range_floats_saturate(ops):
+    x = np.array([1e10, -1e10, np.nan, np.inf, -np.inf, 300.0, -300.0], dtype=f32)
+    assert host(ops.cast(dev(x), "int32")).tolist() == [2 ** 31 - 1, -2 ** 31, 0, 2 ** 31 - 1, -2 ** 31, 300, -300]
+    assert host(ops.cast(dev(x), "int8")).tolist() == [127, -128, 0, 127, -128, 127, -128]
+    assert host(ops.cast(dev(x), "uint8")).tolist() == [255, 0, 0, 255, 0, 255, 0]
+
+
+def test_cast_bool_rejected(ops):
+    from hdkx_aicompiler_b200 import KxcError
+    with pytest.raises(KxcError):
+        ops.cast(torch.zeros(4, device="cuda"), "bool")
+    with pytest.raises(ValueError):
+        ops.cast(torch.zeros(4, device="cuda"), "float16")

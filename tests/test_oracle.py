@@ -173,3 +173,42 @@ def test_port_softmax_reduce_mean_match_reference_bits(rng):
     with pytest.raises(ValueError):
         port.reduce_mean(x, (0,), True)
 
+
+
+@needs_ref
+def test_port_matmul_transpose_reshape_cast_match_reference_bits(rng):
+    """matmul, transpose, reshape and cast: the plain-C port against the kernels the reference's compiler generates.
+    cast is compiled with the one-macro shim `cast(x) = (x)`: the reference's C backend prints the call but never
+    defines it (src/codegen/codegen_c.cc:155-169); the assignment then converts like CodeGenLLVM::CastValue."""
+    a = rng.normal(0, 1, (9, 13)).astype(np.float32)
+    b = rng.normal(0, 1, (13, 6)).astype(np.float32)
+    assert_bit_exact(port.matmul(a, b), ref.matmul(a, b), "matmul")
+    x = rng.normal(0, 1, (2, 3, 4, 5)).astype(np.float32)
+    for axes in (None, (0, 2, 3, 1), (0, 3, 1, 2), (3, 2, 1, 0), (1, 0, 2, 3), (0, 1, 3, 2), (-1, 0, 1, 2), (0, 1, 2, 3)):
+        got = port.transpose(x, axes)
+        assert_bit_exact(got, ref.transpose(x, axes), f"transpose {axes}")
+        assert_bit_exact(got, np.ascontiguousarray(np.transpose(x, axes)), f"transpose {axes} vs numpy")
+    xi = rng.integers(-1000, 1000, (7, 11)).astype(np.int32)
+    assert_bit_exact(port.transpose(xi, (1, 0)), ref.transpose(xi, (1, 0)), "transpose int32")
+    assert_bit_exact(ref.reshape(x, (0, -1, 5), (2, 12, 5)), port.reshape(x, (2, 12, 5)), "reshape 0/-1")
+    assert_bit_exact(ref.reshape(x, (120,), (120,)), port.reshape(x, (120,)), "reshape flat")
+    v = rng.normal(0, 40, (4, 9)).astype(np.float32)
+    v[0, :4] = (0.0, -0.0, 0.999, -0.999)
+    for dt in (np.int32, np.int64, np.float64, np.int8):
+        assert_bit_exact(port.cast(v, dt), ref.cast(v, dt), f"cast float32 -> {np.dtype(dt).name}")
+    assert_bit_exact(port.cast(np.abs(v), np.uint8), ref.cast(np.abs(v), np.uint8), "cast float32 -> uint8")
+    big = np.array([2**31 - 1, -2**31, 16777217, -16777217, 300, -300, 127, -128, 255, 0], dtype=np.int32)
+    for dt in (np.float32, np.int64, np.float64, np.int8, np.uint8):
+        assert_bit_exact(port.cast(big, dt), ref.cast(big, dt), f"cast int32 -> {np.dtype(dt).name}")
+    wide = np.array([2**40 + 5, -2**40 - 5, 2**53 + 1, -7, 2**31], dtype=np.int64)
+    for dt in (np.float32, np.int32, np.float64):
+        assert_bit_exact(port.cast(wide, dt), ref.cast(wide, dt), f"cast int64 -> {np.dtype(dt).name}")
+    d = np.array([1.0 + 2.0**-30, -3.999999, 1e-50, 123456.789, 0.1], dtype=np.float64)
+    for dt in (np.float32, np.int32, np.int64):
+        assert_bit_exact(port.cast(d, dt), ref.cast(d, dt), f"cast float64 -> {np.dtype(dt).name}")
+    s8 = np.array([-128, -1, 0, 1, 127], dtype=np.int8)
+    u8 = np.array([0, 1, 127, 128, 255], dtype=np.uint8)
+    for dt in (np.float32, np.int32, np.int64, np.uint8):
+        assert_bit_exact(port.cast(s8, dt), ref.cast(s8, dt), f"cast int8 -> {np.dtype(dt).name}")
+    for dt in (np.float32, np.int32, np.int64, np.int8):
+        assert_bit_exact(port.cast(u8, dt), ref.cast(u8, dt), f"cast uint8 -> {np.dtype(dt).name}")
