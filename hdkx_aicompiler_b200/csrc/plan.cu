@@ -27,6 +27,8 @@
 #include <string>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.cuh"
 #include "conv_direct.cuh"
 #include "conv_rowstack.cuh"
@@ -142,6 +144,9 @@ struct kxc_b200_plan {
     };
     GraphSlot graph_slots[kGraphSlots];
     int graph_next_slot = 0;
+    // optional NVTX ranges: one per launch, named like kxc_b200_plan_launch_info names it, inside one range per run
+    bool nvtx = false;
+    std::vector<std::string> nvtx_names;
 
     ~kxc_b200_plan() {
         for (auto& g : graph_slots)
@@ -855,6 +860,25 @@ extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
     return KXC_B200_OK;
 }
 
+namespace {
+// NVTX range around the host side of one launch (a no-op unless the plan asked for ranges; without a tool attached
+// the NVTX calls themselves return at once).
+struct LaunchRange {
+    bool on;
+    LaunchRange(const kxc_b200_plan* pl, size_t index) : on(pl->nvtx && index < pl->nvtx_names.size()) {
+        if (on) nvtxRangePushA(pl->nvtx_names[index].c_str());
+    }
+    explicit LaunchRange(const char* name, bool enable) : on(enable) {
+        if (on) nvtxRangePushA(name);
+    }
+    ~LaunchRange() {
+        if (on) nvtxRangePop();
+    }
+    LaunchRange(const LaunchRange&) = delete;
+    LaunchRange& operator=(const LaunchRange&) = delete;
+};
+}  // namespace
+
 static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream, cudaEvent_t* events) {
     if (!pl || !pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_run: plan is not finalized");
     if (pl->precision == KXC_B200_PREC_FP32) return run_exact(pl, packed_args, stream, events);
@@ -889,6 +913,7 @@ static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream
     if (events) KXC_CUDA_TRY(cudaEventRecord(events[0], s));
     for (auto& st : pl->steps) {
         if (step_index > 0 && events) KXC_CUDA_TRY(cudaEventRecord(events[step_index], s));
+        LaunchRange range(pl, step_index);
         ++step_index;
         switch (st.kind) {
             case SKind::InputNHWC:
@@ -944,7 +969,22 @@ extern "C" int32_t kxc_b200_plan_set_cuda_graph(kxc_b200_plan* pl, int32_t enabl
     return KXC_B200_OK;
 }
 
+extern "C" int32_t kxc_b200_plan_set_nvtx(kxc_b200_plan* pl, int32_t enable) {
+    if (!pl || !pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_set_nvtx: plan is not finalized");
+    if (enable && pl->nvtx_names.empty()) {
+        const int n = kxc_b200_plan_num_launches(pl);
+        char name[192];
+        for (int i = 0; i < n; ++i) {
+            KXC_TRY(kxc_b200_plan_launch_info(pl, i, name, (int32_t)sizeof(name), nullptr, nullptr));
+            pl->nvtx_names.emplace_back(name);
+        }
+    }
+    pl->nvtx = enable != 0;
+    return KXC_B200_OK;
+}
+
 extern "C" int32_t kxc_b200_plan_run(kxc_b200_plan* pl, void** packed_args, void* stream) {
+    LaunchRange run_range("kxc_b200_plan_run", pl && pl->nvtx);
     if (!pl || !pl->finalized || !packed_args || !pl->use_graph) return plan_run_impl(pl, packed_args, stream, nullptr);
     const size_t nargs = pl->inputs.size() + pl->constants.size() + 1;
     bool packed = true;  // weights must already be packed from these constants: packing stays outside the graph
@@ -983,6 +1023,7 @@ extern "C" int32_t kxc_b200_plan_run(kxc_b200_plan* pl, void** packed_args, void
         }
         slot->args.assign(packed_args, packed_args + nargs);
     }
+    LaunchRange replay("cuda graph replay", pl->nvtx);
     KXC_CUDA_TRY(cudaGraphLaunch(slot->exec, s));
     return KXC_B200_OK;
 }
@@ -1192,6 +1233,7 @@ static int32_t run_exact(kxc_b200_plan* pl, void** packed_args, void* stream, cu
     if (events) KXC_CUDA_TRY(cudaEventRecord(events[0], s));
     for (auto& xs : pl->xsteps) {
         if (idx > 0 && events) KXC_CUDA_TRY(cudaEventRecord(events[idx], s));
+        LaunchRange range(pl, idx);
         ++idx;
         const Node& n = pl->nodes[xs.node];
         const auto& ish = pl->find(xs.in0)->shape;

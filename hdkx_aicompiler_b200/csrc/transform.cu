@@ -28,21 +28,35 @@ struct TransposeDims {
 };
 
 // General form: consecutive threads take consecutive output elements. Coalesced on both sides when the last output
-// dimension is also contiguous in the input (istride == 1).
-template <typename T>
-__global__ void __launch_bounds__(256) transpose_rows_kernel(const T* __restrict__ in, T* __restrict__ out, TransposeDims d) {
-    for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < d.total; o += (int64_t)gridDim.x * blockDim.x) {
-        int64_t rem = o, off = 0;
+// dimension is also contiguous in the input (istride == 1). Index arithmetic is 32-bit when the tensor allows it
+// (64-bit divisions cost more than the copy); two elements are in flight per thread.
+template <typename I>
+__device__ __forceinline__ int64_t transpose_src_offset(I o, const TransposeDims& d) {
+    I rem = o;
+    int64_t off = 0;
 #pragma unroll
-        for (int j = 5; j >= 0; --j) {
-            if (j < d.rank) {
-                const int64_t q = rem / d.shape[j];
-                off += (rem - q * d.shape[j]) * d.istride[j];
-                rem = q;
-            }
+    for (int j = 5; j >= 0; --j) {
+        if (j < d.rank) {
+            const I ext = (I)d.shape[j];
+            const I q = rem / ext;
+            off += (int64_t)(rem - q * ext) * d.istride[j];
+            rem = q;
         }
-        out[o] = __ldg(in + off);
     }
+    return off;
+}
+
+template <typename T, typename I>
+__global__ void __launch_bounds__(256) transpose_rows_kernel(const T* __restrict__ in, T* __restrict__ out, TransposeDims d) {
+    const I total = (I)d.total, stride = (I)gridDim.x * 256;
+    I o = (I)blockIdx.x * 256 + threadIdx.x;
+    for (; o + stride < total; o += 2 * stride) {
+        const T a = __ldg(in + transpose_src_offset<I>(o, d));
+        const T b = __ldg(in + transpose_src_offset<I>(o + stride, d));
+        out[o] = a;
+        out[o + stride] = b;
+    }
+    if (o < total) out[o] = __ldg(in + transpose_src_offset<I>(o, d));
 }
 
 struct TileDims {
@@ -77,11 +91,14 @@ __global__ void __launch_bounds__(kTile* kTileRows) transpose_tiles_kernel(const
         }
         const int64_t x0 = bx * kTile, y0 = by * kTile;
         // read: threadIdx.x runs along Y (contiguous in the input)
+        T v[kTile / kTileRows];
 #pragma unroll
-        for (int r = ty; r < kTile; r += kTileRows) {
-            const int64_t x = x0 + r, y = y0 + tx;
-            if (x < d.X && y < d.Y) tile[r][tx] = __ldg(in + ibase + x * d.x_istride + y);
+        for (int k = 0; k < kTile / kTileRows; ++k) {  // all loads are issued before the first shared-memory store
+            const int64_t x = x0 + ty + k * kTileRows, y = y0 + tx;
+            v[k] = (x < d.X && y < d.Y) ? __ldg(in + ibase + x * d.x_istride + y) : T{};
         }
+#pragma unroll
+        for (int k = 0; k < kTile / kTileRows; ++k) tile[ty + k * kTileRows][tx] = v[k];
         __syncthreads();
         // write: threadIdx.x runs along X (contiguous in the output)
 #pragma unroll
@@ -99,19 +116,23 @@ int grid_for(int64_t blocks) {
 }
 
 template <typename T>
+int32_t rows_launch(const void* in, void* out, const TransposeDims& m, cudaStream_t s) {
+    const int grid = grid_for((m.total + 511) / 512);
+    if (m.total < (int64_t)1 << 31)
+        transpose_rows_kernel<T, uint32_t><<<grid, 256, 0, s>>>(static_cast<const T*>(in), static_cast<T*>(out), m);
+    else
+        transpose_rows_kernel<T, int64_t><<<grid, 256, 0, s>>>(static_cast<const T*>(in), static_cast<T*>(out), m);
+    return check_launch("transpose");
+}
+
+template <typename T>
 int32_t transpose_launch(const void* in, void* out, const TransposeDims& m, const int64_t* ostride, cudaStream_t s) {
     const int last = m.rank - 1;
-    if (m.istride[last] == 1) {
-        transpose_rows_kernel<T><<<grid_for((m.total + 255) / 256), 256, 0, s>>>(static_cast<const T*>(in), static_cast<T*>(out), m);
-        return check_launch("transpose");
-    }
+    if (m.istride[last] == 1) return rows_launch<T>(in, out, m, s);
     int q = -1;  // the output dimension that is contiguous in the input
     for (int j = 0; j < m.rank; ++j)
         if (m.istride[j] == 1) q = j;
-    if (q < 0 || m.rank - 2 > 4) {  // cannot happen for a permutation of at most 6 merged dimensions
-        transpose_rows_kernel<T><<<grid_for((m.total + 255) / 256), 256, 0, s>>>(static_cast<const T*>(in), static_cast<T*>(out), m);
-        return check_launch("transpose");
-    }
+    if (q < 0 || m.rank - 2 > 4) return rows_launch<T>(in, out, m, s);  // cannot happen for at most 6 merged dimensions
     TileDims d{};
     d.X = m.shape[last];
     d.Y = m.shape[q];
@@ -256,6 +277,16 @@ extern "C" int32_t kxc_b200_transpose(void** packed_args, const kxc_b200_transpo
     for (int i = m.rank - 1; i >= 0; --i) {
         ostr[i] = st;
         st *= m.shape[i];
+    }
+    const int last = m.rank - 1;
+    if (m.istride[last] == 1 && (m.shape[last] * desc->elem_bytes) % 16 == 0 && aligned16(packed_args[0]) && aligned16(packed_args[1])) {
+        // rows are contiguous on both sides and every row starts on a 16-byte boundary (all other strides are multiples
+        // of the row length): move 16-byte elements
+        const int64_t per = 16 / desc->elem_bytes;
+        m.shape[last] /= per;
+        m.total /= per;
+        for (int i = 0; i < last; ++i) m.istride[i] /= per;
+        return rows_launch<uint4>(packed_args[0], packed_args[1], m, s);
     }
     switch (desc->elem_bytes) {
         case 4: return transpose_launch<uint32_t>(packed_args[0], packed_args[1], m, ostr, s);

@@ -38,6 +38,7 @@ _PLAN_SYMBOLS = {
     "kxc_b200_plan_num_launches": (i32, [vp]),
     "kxc_b200_plan_run": (i32, [vp, vpp, vp]),
     "kxc_b200_plan_set_cuda_graph": (i32, [vp, i32]),
+    "kxc_b200_plan_set_nvtx": (i32, [vp, i32]),
     "kxc_b200_plan_launch_info": (i32, [vp, i32, ctypes.c_char_p, i32, ctypes.POINTER(ctypes.c_double),
                                         ctypes.POINTER(ctypes.c_double)]),
     "kxc_b200_plan_run_timed": (i32, [vp, vpp, vp, ctypes.POINTER(ctypes.c_float), i32]),
@@ -67,7 +68,7 @@ def _attrs_c(call):
 
 
 class CompiledGraph:
-    def __init__(self, func: relay.Function, precision="bf16", device=None, cuda_graph=False):
+    def __init__(self, func: relay.Function, precision="bf16", device=None, cuda_graph=False, nvtx=False):
         self.lib = load()
         self.func = func
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -102,6 +103,9 @@ class CompiledGraph:
         self.num_launches = self.lib.kxc_b200_plan_num_launches(self.handle)
         if cuda_graph:
             check("plan_set_cuda_graph", self.lib.kxc_b200_plan_set_cuda_graph(self.handle, 1))
+        if nvtx:
+            self.set_nvtx(True)
+        self.precision = precision
         self._const_ptrs = [c.data.data_ptr() for c in self.constants]
         for c in self.constants:
             assert c.data.is_cuda and c.data.dtype == torch.float32 and c.data.is_contiguous()
@@ -115,6 +119,10 @@ class CompiledGraph:
         stream = torch.cuda.current_stream(x.device).cuda_stream
         check("kxc_kernel_main", self.lib.kxc_b200_plan_run(self.handle, args, stream))
         return out
+
+    def set_nvtx(self, enable):
+        """One NVTX range per run holding one range per launch (ProfileOptions::enable_nvtx of the reference)."""
+        check("plan_set_nvtx", self.lib.kxc_b200_plan_set_nvtx(self.handle, 1 if enable else 0))
 
     def launch_info(self):
         """[(label, algorithmic flops, compulsory bytes)] per launch of one run."""

@@ -82,6 +82,11 @@ int32_t kxc_b200_plan_run(kxc_b200_plan* plan, void** packed_args, void* stream)
  * re-captures. The reference has no counterpart (its kernels are host loops). */
 int32_t kxc_b200_plan_set_cuda_graph(kxc_b200_plan* plan, int32_t enable);
 
+/* NVTX ranges (ProfileOptions::enable_nvtx, include/base/profiling.h:66): with it on, every run is one range
+ * "kxc_b200_plan_run" holding one range per launch, named as kxc_b200_plan_launch_info names that launch (a CUDA-graph
+ * replay is a single range "cuda graph replay"). Call after finalize. Costs nothing while no NVTX tool is attached. */
+int32_t kxc_b200_plan_set_nvtx(kxc_b200_plan* plan, int32_t enable);
+
 /* Measurement support (no reference counterpart: the reference only prints one wall-clock elapsed_ms,
  * test/onnx_importer_test.cpp:261-281). launch_info: a label, the algorithmic FLOPs and the compulsory
  * HBM bytes of launch `index`. run_timed: one run with a CUDA event between launches on `stream`;
