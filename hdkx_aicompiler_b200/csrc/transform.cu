@@ -110,6 +110,62 @@ __global__ void __launch_bounds__(kTile* kTileRows) transpose_tiles_kernel(const
     }
 }
 
+// 4-byte elements with 16-byte accesses on both sides: a 64x64 tile, 256 threads. Each thread reads float4s along Y
+// (16 threads cover one 256-byte row of the tile), the tile sits transposed in shared memory, and each thread writes
+// float4s along X. Needs X, Y, the two strides and the batch strides to be multiples of 4 elements and 16-byte aligned
+// pointers; tiles at the ragged edges are clipped per float4 (X and Y being multiples of 4 keeps every float4 whole).
+constexpr int kVTile = 64;
+
+__global__ void __launch_bounds__(256) transpose_tiles_vec4_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
+                                                                  TileDims d) {
+    __shared__ uint32_t tile[kVTile][kVTile + 1];  // tile[x][y]
+    const int lane16 = threadIdx.x & 15, row16 = threadIdx.x >> 4;  // 16 float4 per 64-element row, 16 rows per pass
+    for (int64_t t = blockIdx.x; t < d.tiles; t += gridDim.x) {
+        int64_t rem = t;
+        const int64_t bx = rem % d.tiles_x;
+        rem /= d.tiles_x;
+        const int64_t by = rem % d.tiles_y;
+        rem /= d.tiles_y;
+        int64_t ibase = 0, obase = 0;
+#pragma unroll
+        for (int j = 3; j >= 0; --j) {
+            if (j < d.nb) {
+                const int64_t q = rem / d.bshape[j];
+                const int64_t i = rem - q * d.bshape[j];
+                ibase += i * d.b_istride[j];
+                obase += i * d.b_ostride[j];
+                rem = q;
+            }
+        }
+        const int64_t x0 = bx * kVTile, y0 = by * kVTile;
+        uint4 v[kVTile / 16];
+#pragma unroll
+        for (int k = 0; k < kVTile / 16; ++k) {  // input rows x, float4 along y
+            const int64_t x = x0 + row16 + k * 16, y = y0 + lane16 * 4;
+            v[k] = (x < d.X && y < d.Y) ? __ldg(reinterpret_cast<const uint4*>(in + ibase + x * d.x_istride + y)) : uint4{0, 0, 0, 0};
+        }
+#pragma unroll
+        for (int k = 0; k < kVTile / 16; ++k) {
+            const int x = row16 + k * 16, y = lane16 * 4;
+            tile[x][y] = v[k].x;
+            tile[x][y + 1] = v[k].y;
+            tile[x][y + 2] = v[k].z;
+            tile[x][y + 3] = v[k].w;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kVTile / 16; ++k) {  // output rows y, float4 along x
+            const int yl = row16 + k * 16, xl = lane16 * 4;
+            const int64_t y = y0 + yl, x = x0 + xl;
+            if (x < d.X && y < d.Y) {
+                const uint4 w{tile[xl][yl], tile[xl + 1][yl], tile[xl + 2][yl], tile[xl + 3][yl]};
+                *reinterpret_cast<uint4*>(out + obase + y * d.y_ostride + x) = w;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 int grid_for(int64_t blocks) {
     const int64_t cap = (int64_t)kNumSMs * 16;
     return (int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
@@ -144,6 +200,18 @@ int32_t transpose_launch(const void* in, void* out, const TransposeDims& m, cons
         d.b_istride[d.nb] = m.istride[j];
         d.b_ostride[d.nb] = ostride[j];
         ++d.nb;
+    }
+    if (sizeof(T) == 4 && aligned16(in) && aligned16(out)) {
+        bool vec = d.X % 4 == 0 && d.Y % 4 == 0 && d.x_istride % 4 == 0 && d.y_ostride % 4 == 0;
+        for (int j = 0; j < d.nb; ++j) vec = vec && d.b_istride[j] % 4 == 0 && d.b_ostride[j] % 4 == 0;
+        if (vec) {
+            d.tiles_x = (d.X + kVTile - 1) / kVTile;
+            d.tiles_y = (d.Y + kVTile - 1) / kVTile;
+            d.tiles = d.tiles_x * d.tiles_y;
+            for (int j = 0; j < d.nb; ++j) d.tiles *= d.bshape[j];
+            transpose_tiles_vec4_kernel<<<grid_for(d.tiles), 256, 0, s>>>(static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out), d);
+            return check_launch("transpose");
+        }
     }
     d.tiles_x = (d.X + kTile - 1) / kTile;
     d.tiles_y = (d.Y + kTile - 1) / kTile;

@@ -365,6 +365,8 @@ def test_matmul_shape_errors(ops):
     ((2, 3, 4, 5, 6, 7), (5, 3, 1, 4, 2, 0)), ((2, 3, 4, 5, 6, 7), None), ((1, 64, 1, 33), (3, 2, 1, 0)),
     ((4, 64, 56, 56), (0, 2, 3, 1)), ((4, 56, 56, 64), (0, 3, 1, 2)), ((1000, 513), (1, 0)), ((33, 1, 65), (2, 1, 0)),
     ((0, 4), (1, 0)), ((3, 100, 37), (1, 0, 2)),
+    # 16-byte tile kernel with ragged tiles and with batch dimensions on both sides
+    ((3, 72, 132), (0, 2, 1)), ((8, 36, 20, 12), (3, 1, 0, 2)), ((260, 4), (1, 0)), ((4, 260), (1, 0)), ((2, 128, 192), (2, 0, 1)),
 ])
 def test_transpose_bit_exact(ops, rng, shape, axes):
     x = rng.normal(size=shape).astype(f32)
