@@ -125,23 +125,56 @@ __global__ void __launch_bounds__(kThreads) maxpool_3x3s2p1_kernel(const float* 
 }
 
 // ---- global average pool: coalesced staging, sequential per-plane sum --------------------------
+// kLinear: the CTA's planes are copied into shared memory exactly as they lie in global memory, 16 bytes per access
+// (odd plane sizes only: the per-thread sequential walk with an odd stride hits distinct banks). Otherwise planes are
+// padded to an odd pitch and the (plane, offset) pair of each element is advanced without divisions.
+template <bool kLinear>
 __global__ void __launch_bounds__(128) gap_staged_kernel(const float* __restrict__ x, float* __restrict__ out,
                                                          int64_t planes, int HW, int planes_per_cta, int pitch) {
-    extern __shared__ float tile[];
+    extern __shared__ __align__(16) float tile[];
     const float div = (float)HW;
     for (int64_t p0 = (int64_t)blockIdx.x * planes_per_cta; p0 < planes; p0 += (int64_t)gridDim.x * planes_per_cta) {
         const int np = (int)((planes - p0 < planes_per_cta) ? (planes - p0) : planes_per_cta);
         const float* src = x + p0 * HW;
         const int count = np * HW;
-        for (int i = threadIdx.x; i < count; i += blockDim.x) {
-            const int p = i / HW;
-            tile[p * pitch + (i - p * HW)] = __ldcs(src + i);
+        if (kLinear) {
+            const float4* src4 = reinterpret_cast<const float4*>(src);
+            float4* tile4 = reinterpret_cast<float4*>(tile);
+            const int n4 = count >> 2;
+            int i = threadIdx.x;
+            for (; i + 7 * 128 < n4; i += 8 * 128) {  // eight 16-byte loads in flight per thread
+                float4 v[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = __ldcs(src4 + i + k * 128);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) tile4[i + k * 128] = v[k];
+            }
+            for (; i + 128 < n4; i += 2 * 128) {
+                const float4 a = __ldcs(src4 + i), b = __ldcs(src4 + i + 128);
+                tile4[i] = a;
+                tile4[i + 128] = b;
+            }
+            for (; i < n4; i += 128) tile4[i] = __ldcs(src4 + i);
+            for (int j = (n4 << 2) + threadIdx.x; j < count; j += 128) tile[j] = __ldcs(src + j);
+        } else {
+            int p = threadIdx.x / HW, r = threadIdx.x - p * HW;
+            const int dp = 128 / HW, dr = 128 - dp * HW;
+            for (int i = threadIdx.x; i < count; i += 128) {
+                tile[p * pitch + r] = __ldcs(src + i);
+                p += dp;
+                r += dr;
+                if (r >= HW) {
+                    r -= HW;
+                    ++p;
+                }
+            }
         }
         __syncthreads();
         for (int p = threadIdx.x; p < np; p += blockDim.x) {
             const float* row = tile + p * pitch;
             float s = 0.0f;
-            for (int i = 0; i < HW; ++i) s = __fadd_rn(s, row[i]);
+#pragma unroll 7
+            for (int i = 0; i < HW; ++i) s = __fadd_rn(s, row[i]);  // the unrolled loads run ahead of the add chain
             out[p0 + p] = __fdiv_rn(s, div);
         }
         __syncthreads();
@@ -255,13 +288,18 @@ extern "C" int32_t kxc_b200_nn_global_avg_pool2d(void** packed_args, int32_t n, 
     float* out = static_cast<float*>(packed_args[1]);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     constexpr int kSmemBudget = 40 * 1024;
-    const int64_t pitch = HW | 1;  // odd pitch: the per-thread sequential walk hits distinct banks
+    const bool linear = (HW & 1) && aligned16(x);
+    const int64_t pitch = linear ? HW : (HW | 1);  // odd pitch: the per-thread sequential walk hits distinct banks
     if (pitch * 4 * 8 <= kSmemBudget) {
         int per_cta = (int)(kSmemBudget / (pitch * 4));
         if (per_cta > 128) per_cta = 128;
+        per_cta &= ~3;  // every CTA's first plane then starts on a 16-byte boundary
         const int64_t ctas = (planes + per_cta - 1) / per_cta;
         const int grid = (int)(ctas < (int64_t)kNumSMs * 8 ? ctas : (int64_t)kNumSMs * 8);
-        gap_staged_kernel<<<grid, 128, (size_t)per_cta * pitch * 4, s>>>(x, out, planes, (int)HW, per_cta, (int)pitch);
+        if (linear)
+            gap_staged_kernel<true><<<grid, 128, (size_t)per_cta * pitch * 4, s>>>(x, out, planes, (int)HW, per_cta, (int)pitch);
+        else
+            gap_staged_kernel<false><<<grid, 128, (size_t)per_cta * pitch * 4, s>>>(x, out, planes, (int)HW, per_cta, (int)pitch);
     } else {
         gap_direct_kernel<<<grid_for(planes, 128, 8), 128, 0, s>>>(x, out, planes, HW);
     }

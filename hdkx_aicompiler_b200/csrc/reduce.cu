@@ -43,6 +43,47 @@ __global__ void __launch_bounds__(kSoftmaxThreads) softmax_rows_kernel(const flo
     }
 }
 
+// Rows of at most kPer * 128 elements: every thread keeps its exponentials in registers, so the row is read once and
+// expf runs once per element. Same summation order as softmax_rows_kernel (thread-strided partial sums, warp shuffles,
+// warps in order), hence the same bits.
+template <int kPer>
+__global__ void __launch_bounds__(kSoftmaxThreads) softmax_rows_reg_kernel(const float* __restrict__ x, float* __restrict__ out,
+                                                                         int64_t rows, int len) {
+    __shared__ float warp_sum[2][kSoftmaxThreads / 32];
+    int phase = 0;
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x, phase ^= 1) {
+        const float* xp = x + r * len;
+        float* op = out + r * len;
+        float e[kPer];
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const int i = threadIdx.x + k * kSoftmaxThreads;
+            e[k] = i < len ? __ldcs(xp + i) : 0.0f;
+        }
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const int i = threadIdx.x + k * kSoftmaxThreads;
+            if (i < len) {
+                e[k] = expf(e[k]);
+                s = __fadd_rn(s, e[k]);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, o));
+        if ((threadIdx.x & 31) == 0) warp_sum[phase][threadIdx.x >> 5] = s;
+        __syncthreads();  // the buffer alternates between rows, so one barrier per row is enough
+        float denom = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kSoftmaxThreads / 32; ++w) denom = __fadd_rn(denom, warp_sum[phase][w]);
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const int i = threadIdx.x + k * kSoftmaxThreads;
+            if (i < len) __stcs(op + i, __fdiv_rn(e[k], denom));
+        }
+    }
+}
+
 struct ReduceDims {
     int nk, nr;               // kept / reduced dimensions
     int64_t kshape[6], kstride[6];
@@ -99,8 +140,17 @@ extern "C" int32_t kxc_b200_softmax(void** packed_args, const kxc_b200_softmax_d
     if (rows == 0 || len == 0) return KXC_B200_OK;
     if (!packed_args[0] || !packed_args[1]) return fail(KXC_B200_ERR_INVALID, "softmax: null tensor pointer");
     const int grid = (int)(rows < (int64_t)kNumSMs * 16 ? rows : (int64_t)kNumSMs * 16);
-    softmax_rows_kernel<<<grid, kSoftmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const float*>(packed_args[0]),
-                                                                                       static_cast<float*>(packed_args[1]), rows, (int)len);
+    const float* xin = static_cast<const float*>(packed_args[0]);
+    float* yout = static_cast<float*>(packed_args[1]);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (len <= 4 * kSoftmaxThreads)
+        softmax_rows_reg_kernel<4><<<grid, kSoftmaxThreads, 0, s>>>(xin, yout, rows, (int)len);
+    else if (len <= 8 * kSoftmaxThreads)
+        softmax_rows_reg_kernel<8><<<grid, kSoftmaxThreads, 0, s>>>(xin, yout, rows, (int)len);
+    else if (len <= 16 * kSoftmaxThreads)
+        softmax_rows_reg_kernel<16><<<grid, kSoftmaxThreads, 0, s>>>(xin, yout, rows, (int)len);
+    else
+        softmax_rows_kernel<<<grid, kSoftmaxThreads, 0, s>>>(xin, yout, rows, (int)len);
     return check_launch("softmax");
 }
 

@@ -258,9 +258,53 @@ __global__ void __launch_bounds__(256) cast_kernel(const S* __restrict__ in, D* 
     for (; i < n; i += stride) out[i] = convert_elem<S, D>(__ldg(in + i));
 }
 
+// V consecutive elements per thread, moved as aligned vectors (the wider of the two types takes 32 bytes per thread).
+template <typename T, int V>
+struct alignas(sizeof(T) * V) ElemVec {
+    T v[V];
+};
+
+template <typename S, typename D, int V>
+__global__ void __launch_bounds__(256) cast_vec_kernel(const S* __restrict__ in, D* __restrict__ out, int64_t n) {
+    const int64_t nv = n / V;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const ElemVec<S, V>* in_v = reinterpret_cast<const ElemVec<S, V>*>(in);
+    ElemVec<D, V>* out_v = reinterpret_cast<ElemVec<D, V>*>(out);
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + stride < nv; i += 2 * stride) {
+        const ElemVec<S, V> a = in_v[i], b = in_v[i + stride];
+        ElemVec<D, V> ra, rb;
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            ra.v[k] = convert_elem<S, D>(a.v[k]);
+            rb.v[k] = convert_elem<S, D>(b.v[k]);
+        }
+        out_v[i] = ra;
+        out_v[i + stride] = rb;
+    }
+    if (i < nv) {
+        const ElemVec<S, V> a = in_v[i];
+        ElemVec<D, V> ra;
+#pragma unroll
+        for (int k = 0; k < V; ++k) ra.v[k] = convert_elem<S, D>(a.v[k]);
+        out_v[i] = ra;
+    }
+    // the last n % V elements
+    const int64_t t = nv * V + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) out[t] = convert_elem<S, D>(in[t]);
+}
+
 template <typename S, typename D>
 int32_t cast_launch(const void* in, void* out, int64_t n, cudaStream_t s) {
-    cast_kernel<S, D><<<grid_for((n + 1023) / 1024), 256, 0, s>>>(static_cast<const S*>(in), static_cast<D*>(out), n);
+    constexpr int kWide = sizeof(S) > sizeof(D) ? sizeof(S) : sizeof(D);
+    constexpr int V = 32 / kWide;  // 4 (8-byte types), 8 (4-byte) or 32 (1-byte)
+    const bool aligned = (reinterpret_cast<uintptr_t>(in) % (sizeof(S) * V) == 0) && (reinterpret_cast<uintptr_t>(out) % (sizeof(D) * V) == 0);
+    if (aligned && n >= V) {
+        const int64_t nv = n / V;
+        cast_vec_kernel<S, D, V><<<grid_for((nv + 511) / 512), 256, 0, s>>>(static_cast<const S*>(in), static_cast<D*>(out), n);
+    } else {
+        cast_kernel<S, D><<<grid_for((n + 1023) / 1024), 256, 0, s>>>(static_cast<const S*>(in), static_cast<D*>(out), n);
+    }
     return check_launch("cast");
 }
 

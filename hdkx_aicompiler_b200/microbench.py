@@ -3,8 +3,9 @@
   config 1  fused conv2d + bias + ReLU, 1x64x56x56 (*) 64x64x3x3          (tensor / launch bound)
   config 2  max_pool2d 3x3 s2 p1 on 32x64x112x112 -> add -> relu            (HBM bound)
   config 5  int8 convolution sweep over the 11 distinct ResNet-18 shapes at N=256, requantize + ReLU
+  config t  transpose / cast / softmax / reduce_mean / matmul on the operator ABI (the formats either side of the path)
 
-    python -m hdkx_aicompiler_b200.microbench [--config 1|2|5|all] [--iters 20]
+    python -m hdkx_aicompiler_b200.microbench [--config 1|2|5|t|all] [--iters 20]
 
 Prints one JSON line per measured kernel: CUDA-event time (L2 flushed between iterations by writing a
 256 MB buffer), achieved GB/s or TOP/s and the fraction of the measured peak in MEASURED_PEAKS.json
@@ -137,6 +138,44 @@ def config5(iters, flush, hbm, tf, src):
     ops.device_status()
 
 
+def config_transform(iters, flush, hbm, tf, src):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.empty(32, 64, 112, 112, device="cuda").uniform_(-1, 1, generator=g)
+    nb = x.numel() * 4.0
+    xs8 = ops.cast(x * 100, "int8")
+    logits = torch.empty(65536, 1000, device="cuda").normal_(generator=g)
+    feat = torch.empty(1024, 512, 7, 7, device="cuda").normal_(generator=g)
+    cases = [
+        ("transpose NCHW -> NHWC (0,2,3,1)", 2 * nb, lambda: ops.transpose(x, (0, 2, 3, 1))),
+        ("transpose NHWC -> NCHW (0,3,1,2)", 2 * nb, lambda: ops.transpose(x.view(32, 112, 112, 64), (0, 3, 1, 2))),
+        ("transpose batch <-> channel (1,0,2,3)", 2 * nb, lambda: ops.transpose(x, (1, 0, 2, 3))),
+        ("transpose reverse (3,2,1,0)", 2 * nb, lambda: ops.transpose(x, (3, 2, 1, 0))),
+        ("cast float32 -> int32", 2 * nb, lambda: ops.cast(x, "int32")),
+        ("cast float32 -> int8", 1.25 * nb, lambda: ops.cast(x, "int8")),
+        ("cast int8 -> float32", 1.25 * nb, lambda: ops.cast(xs8, "float32")),
+        ("cast float32 -> float64", 3 * nb, lambda: ops.cast(x, "float64")),
+        ("softmax 65536 x 1000 (last axis)", 2.0 * logits.numel() * 4, lambda: ops.softmax(logits, -1)),
+        ("reduce_mean 1024x512x7x7 over (2,3)", feat.numel() * 4.0 + 1024 * 512 * 4, lambda: ops.reduce_mean(feat, (2, 3), True)),
+    ]
+    dst = torch.empty_like(x)
+    cases.append((f"reference: copy_ of {nb / 1e6:.1f} MB (same bytes as a transpose)", 2 * nb, lambda: dst.copy_(x)))
+    for name, nbytes, fn in cases:
+        ms = timeit(fn, iters, flush)
+        emit(config="t", kernel=name, ms=ms, algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, frac_of_hbm_peak=nbytes / ms / 1e6 / hbm,
+             peak_source=src)
+    a = torch.empty(4096, 4096, device="cuda").normal_(generator=g)
+    b = torch.empty(4096, 4096, device="cuda").normal_(generator=g)
+    def four(prec):  # four calls per sample: a single call after an idle GPU mostly measures the host's launch path
+        for _ in range(4):
+            ops.matmul(a, b, precision=prec)
+
+    for prec in ("bf16", "tf32"):
+        ms = timeit(lambda: four(prec), iters, flush) / 4
+        fl = 2.0 * 4096 ** 3
+        emit(config="t", kernel=f"matmul 4096x4096x4096 {prec} (fp32 operands converted inside the call)", ms=ms, flops=fl,
+             tflops=fl / ms / 1e9, frac_of_tensor_peak=fl / ms / 1e9 / (tf if prec == "bf16" else tf / 2), peak_source=src)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="all")
@@ -145,7 +184,7 @@ def main():
     assert torch.cuda.is_available(), "needs a GPU"
     hbm, tf, src = peaks()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
-    for c, fn in (("1", config1), ("2", config2), ("5", config5)):
+    for c, fn in (("1", config1), ("2", config2), ("5", config5), ("t", config_transform)):
         if args.config in ("all", c):
             fn(args.iters, flush, hbm, tf, src)
 
