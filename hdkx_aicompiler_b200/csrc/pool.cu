@@ -139,23 +139,15 @@ __global__ void __launch_bounds__(128) gap_staged_kernel(const float* __restrict
         const int count = np * HW;
         if (kLinear) {
             const float4* src4 = reinterpret_cast<const float4*>(src);
-            float4* tile4 = reinterpret_cast<float4*>(tile);
             const int n4 = count >> 2;
-            int i = threadIdx.x;
-            for (; i + 7 * 128 < n4; i += 8 * 128) {  // eight 16-byte loads in flight per thread
-                float4 v[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) v[k] = __ldcs(src4 + i + k * 128);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) tile4[i + k * 128] = v[k];
-            }
-            for (; i + 128 < n4; i += 2 * 128) {
-                const float4 a = __ldcs(src4 + i), b = __ldcs(src4 + i + 128);
-                tile4[i] = a;
-                tile4[i + 128] = b;
-            }
-            for (; i < n4; i += 128) tile4[i] = __ldcs(src4 + i);
+            // asynchronous 16-byte copies straight into shared memory: all of a thread's copies are in flight at once
+            // and none of them holds a register
+            const uint32_t tile_addr = (uint32_t)__cvta_generic_to_shared(tile);
+            for (int i = threadIdx.x; i < n4; i += 128)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(tile_addr + (uint32_t)i * 16u), "l"(src4 + i) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
             for (int j = (n4 << 2) + threadIdx.x; j < count; j += 128) tile[j] = __ldcs(src + j);
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         } else {
             int p = threadIdx.x / HW, r = threadIdx.x - p * HW;
             const int dp = 128 / HW, dr = 128 - dp * HW;
@@ -295,7 +287,9 @@ extern "C" int32_t kxc_b200_nn_global_avg_pool2d(void** packed_args, int32_t n, 
         if (per_cta > 128) per_cta = 128;
         per_cta &= ~3;  // every CTA's first plane then starts on a 16-byte boundary
         const int64_t ctas = (planes + per_cta - 1) / per_cta;
-        const int grid = (int)(ctas < (int64_t)kNumSMs * 8 ? ctas : (int64_t)kNumSMs * 8);
+        // one CTA per group of planes (no grid-stride loop unless the count exceeds the grid limit): the hardware
+        // hands out CTAs as SMs free up, which balances better than a fixed 3-or-4 iterations per resident CTA
+        const int grid = (int)(ctas < 0x7fffffff ? ctas : 0x7fffffff);
         if (linear)
             gap_staged_kernel<true><<<grid, 128, (size_t)per_cta * pitch * 4, s>>>(x, out, planes, (int)HW, per_cta, (int)pitch);
         else
