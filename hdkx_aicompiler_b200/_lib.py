@@ -13,7 +13,7 @@ vpp = ctypes.POINTER(ctypes.c_void_p)
 
 OK = 0
 BIAS, RESIDUAL, RELU, NHWC = 1, 2, 4, 8
-PREC_FP32, PREC_TF32, PREC_BF16, PREC_SIMT = 0, 1, 2, 3
+PREC_FP32, PREC_TF32, PREC_BF16, PREC_SIMT, PREC_TF32X3 = 0, 1, 2, 3, 4
 # cast dtype codes: the reference's CastAttrs codes (src/relay/op/tensor/transform.cc:84-103)
 DT_F32, DT_I32, DT_I64, DT_F64, DT_BOOL, DT_I8, DT_U8 = 0, 1, 2, 3, 4, 5, 6
 

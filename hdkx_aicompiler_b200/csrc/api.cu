@@ -88,6 +88,7 @@ extern "C" int32_t kxc_b200_nn_conv2d(void** packed_args, const kxc_b200_conv2d_
             return conv2d_fp32_exact(data, weight, bias, residual, out, d, relu, s);
         case KXC_B200_PREC_TF32:
         case KXC_B200_PREC_BF16:
+        case KXC_B200_PREC_TF32X3:
             return conv2d_tensor_core(data, weight, bias, residual, out, d, relu, desc->precision, s);
         default:
             return fail(KXC_B200_ERR_INVALID, "nn_conv2d: unknown precision %d", desc->precision);
@@ -131,6 +132,7 @@ extern "C" int32_t kxc_b200_nn_gemm(void** packed_args, const kxc_b200_gemm_desc
             return gemm_fp32_exact(a, b, c, out, g, s);
         case KXC_B200_PREC_TF32:
         case KXC_B200_PREC_BF16:
+        case KXC_B200_PREC_TF32X3:
             return gemm_tensor_core(a, b, c, out, g, s);
         default:
             return fail(KXC_B200_ERR_INVALID, "nn_gemm: unknown precision %d", g.precision);
@@ -154,6 +156,7 @@ extern "C" int32_t kxc_b200_matmul(void** packed_args, int32_t m, int32_t n, int
             return gemm_fp32_exact(a, b, nullptr, out, g, s);
         case KXC_B200_PREC_TF32:
         case KXC_B200_PREC_BF16:
+        case KXC_B200_PREC_TF32X3:
             return gemm_tensor_core(a, b, nullptr, out, g, s);
         default:
             return fail(KXC_B200_ERR_INVALID, "matmul: unknown precision %d", precision);

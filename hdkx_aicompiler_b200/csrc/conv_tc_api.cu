@@ -40,6 +40,39 @@ bool tc_shape_ok(const ConvDims& d) {
 int32_t conv2d_tensor_core(const float* data, const float* weight, const float* bias, const float* residual, float* out,
                            const ConvDims& d, int relu, int precision, cudaStream_t s) {
     if (!tc_shape_ok(d)) return conv2d_fp32_exact(data, weight, bias, residual, out, d, relu, s);
+    if (precision == KXC_B200_PREC_TF32X3) {
+        // Three tf32 passes into the same fp32 output, small terms first: x_lo*w_hi (+ the caller's residual), then
+        // x_hi*w_lo + that, then x_hi*w_hi + bias + that, ReLU last. Each pass reads the previous sum through the
+        // epilogue's residual input; reading and writing the same element from the same thread is safe in place.
+        const int cpad = tc_channel_pad(kTcTF32, d.C);
+        const size_t act_bytes = align_up((size_t)d.N * d.H * d.W * cpad * 4, 1024);
+        const size_t w_bytes = align_up((size_t)d.O * d.KH * d.KW * cpad * 4, 1024);
+        StreamScratch ws(s);
+        KXC_TRY(ws.alloc(2 * act_bytes + 2 * w_bytes));
+        uint8_t* act_hi = static_cast<uint8_t*>(ws.ptr);
+        uint8_t* act_lo = act_hi + act_bytes;
+        uint8_t* w_hi = act_lo + act_bytes;
+        uint8_t* w_lo = w_hi + w_bytes;
+        KXC_TRY(nchw_to_nhwc(data, act_hi, kTcTF32, d.N, d.C, d.H * d.W, cpad, s));
+        KXC_TRY(nchw_to_nhwc(data, act_lo, kTcTF32, d.N, d.C, d.H * d.W, cpad, s, true));
+        KXC_TRY(pack_weights_ohwi(weight, w_hi, kTcTF32, d.O, d.C, d.KH, d.KW, cpad, s));
+        KXC_TRY(pack_weights_ohwi(weight, w_lo, kTcTF32, d.O, d.C, d.KH, d.KW, cpad, s, true));
+        const uint8_t* as[3] = {act_lo, act_hi, act_hi};
+        const uint8_t* wsrc[3] = {w_hi, w_lo, w_hi};
+        for (int pass = 0; pass < 3; ++pass) {
+            TcParams p{};
+            TcConfig cfg{};
+            KXC_TRY(tc_setup_conv(&p, &cfg, kTcTF32, kOutNCHW_F32, as[pass], wsrc[pass], d.N, d.H, d.W, cpad, d.O, d.KH, d.KW, d.SH,
+                                  d.PH, d.PW, d.DH, d.DW));
+            p.bias = pass == 2 ? bias : nullptr;
+            p.residual = pass == 0 ? residual : out;
+            p.out = out;
+            p.relu = pass == 2 ? relu : 0;
+            tc_finish_params(&p);
+            KXC_TRY(tc_launch(cfg, p, s));
+        }
+        return KXC_B200_OK;
+    }
     const TcDType dt = precision == KXC_B200_PREC_BF16 ? kTcBF16 : kTcTF32;
     const int eb = tc_elem_bytes(dt);
     const int cpad = tc_channel_pad(dt, d.C);
@@ -113,6 +146,40 @@ int32_t gemm_tensor_core(const float* a, const float* b, const float* c, float* 
     // alpha = beta = 1 form is fused into the tensor-core epilogue.
     if ((g.has_c && ((double)g.alpha != 1.0 || (double)g.beta != 1.0)) || g.m > 65535 * 128)
         return gemm_fp32_exact(a, b, c, out, g, s);
+    if (g.precision == KXC_B200_PREC_TF32X3) {
+        // as in conv2d_tensor_core: a_lo*b_hi, + a_hi*b_lo, + a_hi*b_hi + c
+        const int kpad = tc_channel_pad(kTcTF32, g.k);
+        const size_t a_bytes = align_up((size_t)g.m * kpad * 4, 1024);
+        const size_t b_bytes = align_up((size_t)g.n * kpad * 4, 1024);
+        StreamScratch ws(s);
+        KXC_TRY(ws.alloc(2 * a_bytes + 2 * b_bytes));
+        uint8_t* part[4];  // a_hi, a_lo, b_hi, b_lo
+        part[0] = static_cast<uint8_t*>(ws.ptr);
+        part[1] = part[0] + a_bytes;
+        part[2] = part[1] + a_bytes;
+        part[3] = part[2] + b_bytes;
+        for (int lo = 0; lo < 2; ++lo) {
+            KXC_TRY(convert_rows(a, part[lo], kTcTF32, g.m, g.k, kpad, s, lo == 1));
+            if (g.transB)
+                KXC_TRY(convert_rows(b, part[2 + lo], kTcTF32, g.n, g.k, kpad, s, lo == 1));
+            else
+                KXC_TRY(nchw_to_nhwc(b, part[2 + lo], kTcTF32, 1, g.k, g.n, kpad, s, lo == 1));
+        }
+        const uint8_t* as[3] = {part[1], part[0], part[0]};
+        const uint8_t* bs[3] = {part[2], part[3], part[2]};
+        for (int pass = 0; pass < 3; ++pass) {
+            TcParams p{};
+            TcConfig cfg{};
+            KXC_TRY(tc_setup_conv(&p, &cfg, kTcTF32, kOutNHWC_F32, as[pass], bs[pass], g.m, 1, 1, kpad, g.n, 1, 1, 1, 0, 0, 1, 1));
+            p.bias = (pass == 2 && g.has_c) ? c : nullptr;
+            p.residual = pass == 0 ? nullptr : out;
+            p.out = out;
+            p.relu = 0;
+            tc_finish_params(&p);
+            KXC_TRY(tc_launch(cfg, p, s));
+        }
+        return KXC_B200_OK;
+    }
     const TcDType dt = g.precision == KXC_B200_PREC_BF16 ? kTcBF16 : kTcTF32;
     const int eb = tc_elem_bytes(dt);
     const int kpad = tc_channel_pad(dt, g.k);

@@ -22,6 +22,18 @@ __device__ __forceinline__ __nv_bfloat16 convert_to<__nv_bfloat16>(float v) { re
 template <>
 __device__ __forceinline__ float convert_to<float>(float v) { return round_tf32_rne(v); }
 
+// What single-pass tf32 drops: the tf32 rounding of (v - tf32(v)). a*b ~ a_hi*b_hi + a_hi*b_lo + a_lo*b_hi then carries
+// about 21 bits of each operand instead of 11.
+struct Tf32Lo {
+    float v;
+};
+template <>
+__device__ __forceinline__ Tf32Lo convert_to<Tf32Lo>(float v) {
+    const float hi = round_tf32_rne(v);
+    // inf - inf would be NaN: a non-finite value lives in the high part only
+    return Tf32Lo{(__float_as_uint(v) & 0x7f800000u) == 0x7f800000u ? 0.0f : round_tf32_rne(__fsub_rn(v, hi))};
+}
+
 template <typename TIn, typename TOut>
 __device__ __forceinline__ TOut convert_elem(TIn v) { return convert_to<TOut>((float)v); }
 template <>
@@ -81,7 +93,7 @@ int grid_1d(int64_t items, int threads) {
 
 }  // namespace
 
-int32_t nchw_to_nhwc(const void* in, void* out, TcDType dtype, int N, int C, int HW, int cpad, cudaStream_t s) {
+int32_t nchw_to_nhwc(const void* in, void* out, TcDType dtype, int N, int C, int HW, int cpad, cudaStream_t s, bool tf32_lo) {
     if (N == 0) return KXC_B200_OK;
     if (N > 65535) return fail(KXC_B200_ERR_UNSUPPORTED, "layout transform: batch %d exceeds the grid limit", N);
     const dim3 grid((HW + 31) / 32, (cpad + 31) / 32, N), block(32, 8);
@@ -90,7 +102,10 @@ int32_t nchw_to_nhwc(const void* in, void* out, TcDType dtype, int N, int C, int
             nchw_to_nhwc_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>(static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out), C, HW, cpad);
             break;
         case kTcTF32:
-            nchw_to_nhwc_kernel<float, float><<<grid, block, 0, s>>>(static_cast<const float*>(in), static_cast<float*>(out), C, HW, cpad);
+            if (tf32_lo)
+                nchw_to_nhwc_kernel<float, Tf32Lo><<<grid, block, 0, s>>>(static_cast<const float*>(in), static_cast<Tf32Lo*>(out), C, HW, cpad);
+            else
+                nchw_to_nhwc_kernel<float, float><<<grid, block, 0, s>>>(static_cast<const float*>(in), static_cast<float*>(out), C, HW, cpad);
             break;
         case kTcS8:
             nchw_to_nhwc_kernel<int8_t, int8_t><<<grid, block, 0, s>>>(static_cast<const int8_t*>(in), static_cast<int8_t*>(out), C, HW, cpad);
@@ -99,7 +114,7 @@ int32_t nchw_to_nhwc(const void* in, void* out, TcDType dtype, int N, int C, int
     return check_launch("nchw_to_nhwc");
 }
 
-int32_t pack_weights_ohwi(const void* w, void* out, TcDType dtype, int O, int C, int KH, int KW, int cpad, cudaStream_t s) {
+int32_t pack_weights_ohwi(const void* w, void* out, TcDType dtype, int O, int C, int KH, int KW, int cpad, cudaStream_t s, bool tf32_lo) {
     const int64_t total = (int64_t)O * KH * KW * cpad;
     const int grid = grid_1d(total, 256);
     switch (dtype) {
@@ -107,7 +122,10 @@ int32_t pack_weights_ohwi(const void* w, void* out, TcDType dtype, int O, int C,
             pack_weights_kernel<float, __nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const float*>(w), static_cast<__nv_bfloat16*>(out), O, C, KH, KW, cpad);
             break;
         case kTcTF32:
-            pack_weights_kernel<float, float><<<grid, 256, 0, s>>>(static_cast<const float*>(w), static_cast<float*>(out), O, C, KH, KW, cpad);
+            if (tf32_lo)
+                pack_weights_kernel<float, Tf32Lo><<<grid, 256, 0, s>>>(static_cast<const float*>(w), static_cast<Tf32Lo*>(out), O, C, KH, KW, cpad);
+            else
+                pack_weights_kernel<float, float><<<grid, 256, 0, s>>>(static_cast<const float*>(w), static_cast<float*>(out), O, C, KH, KW, cpad);
             break;
         case kTcS8:
             pack_weights_kernel<int8_t, int8_t><<<grid, 256, 0, s>>>(static_cast<const int8_t*>(w), static_cast<int8_t*>(out), O, C, KH, KW, cpad);
@@ -116,12 +134,14 @@ int32_t pack_weights_ohwi(const void* w, void* out, TcDType dtype, int O, int C,
     return check_launch("pack_weights");
 }
 
-int32_t convert_rows(const float* in, void* out, TcDType dtype, int64_t rows, int cols, int cpad, cudaStream_t s) {
+int32_t convert_rows(const float* in, void* out, TcDType dtype, int64_t rows, int cols, int cpad, cudaStream_t s, bool tf32_lo) {
     const int64_t total = rows * cpad;
     if (total == 0) return KXC_B200_OK;
     const int grid = grid_1d(total, 256);
     if (dtype == kTcBF16)
         convert_rows_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(in, static_cast<__nv_bfloat16*>(out), rows, cols, cpad);
+    else if (dtype == kTcTF32 && tf32_lo)
+        convert_rows_kernel<Tf32Lo><<<grid, 256, 0, s>>>(in, static_cast<Tf32Lo*>(out), rows, cols, cpad);
     else if (dtype == kTcTF32)
         convert_rows_kernel<float><<<grid, 256, 0, s>>>(in, static_cast<float*>(out), rows, cols, cpad);
     else

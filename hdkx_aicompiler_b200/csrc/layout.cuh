@@ -12,12 +12,12 @@ namespace kxc_b200 {
 // NCHW (fp32 or int8) -> NHWC with `cpad` channels (zero filled), converted to the tensor-core
 // operand type: bf16 (round to nearest even), tf32 kept in fp32 storage (low 13 mantissa bits
 // rounded away, nearest even), or int8 (copied).
-int32_t nchw_to_nhwc(const void* in, void* out, TcDType dtype, int N, int C, int HW, int cpad, cudaStream_t s);
+int32_t nchw_to_nhwc(const void* in, void* out, TcDType dtype, int N, int C, int HW, int cpad, cudaStream_t s, bool tf32_lo = false);
 
 // OIHW (fp32 or int8) -> [O][KH][KW][cpad] in the operand type.
-int32_t pack_weights_ohwi(const void* w, void* out, TcDType dtype, int O, int C, int KH, int KW, int cpad, cudaStream_t s);
+int32_t pack_weights_ohwi(const void* w, void* out, TcDType dtype, int O, int C, int KH, int KW, int cpad, cudaStream_t s, bool tf32_lo = false);
 
 // Row-major [rows, cols] fp32 -> [rows, cpad] operand type (dense operands).
-int32_t convert_rows(const float* in, void* out, TcDType dtype, int64_t rows, int cols, int cpad, cudaStream_t s);
+int32_t convert_rows(const float* in, void* out, TcDType dtype, int64_t rows, int cols, int cpad, cudaStream_t s, bool tf32_lo = false);
 
 }  // namespace kxc_b200

@@ -14,7 +14,7 @@ from . import _lib
 from ._lib import (BIAS, NHWC, PREC_BF16, PREC_FP32, PREC_SIMT, PREC_TF32, RELU, RESIDUAL, AddDesc, Conv2dDesc, GemmDesc,
                    Pool2dDesc, check, load, packed)
 
-PRECISIONS = {"fp32": PREC_FP32, "tf32": PREC_TF32, "bf16": PREC_BF16, "simt": PREC_SIMT}
+PRECISIONS = {"fp32": PREC_FP32, "tf32": PREC_TF32, "bf16": PREC_BF16, "simt": PREC_SIMT, "tf32x3": _lib.PREC_TF32X3}
 
 
 def _stream(t):

@@ -53,7 +53,9 @@ enum {
     KXC_B200_PREC_FP32 = 0, /* CUDA-core fp32, the reference's rc->rh->rw order, separately rounded mul/add: bit-exact */
     KXC_B200_PREC_TF32 = 1, /* tcgen05 kind::tf32, operands rounded to tf32 (RNE), fp32 accumulate in TMEM */
     KXC_B200_PREC_BF16 = 2, /* tcgen05 kind::f16 (bf16), operands rounded to bf16 (RNE), fp32 accumulate   */
-    KXC_B200_PREC_SIMT = 3  /* int8 entry point only: force the CUDA-core kernel instead of tcgen05 kind::i8 */
+    KXC_B200_PREC_SIMT = 3, /* int8 entry point only: force the CUDA-core kernel instead of tcgen05 kind::i8 */
+    KXC_B200_PREC_TF32X3 = 4 /* per-op conv / gemm / matmul: operands split into tf32 high and low parts, three tcgen05
+                                passes (lo*hi, hi*lo, hi*hi) summed in fp32: fp32-class accuracy on the tensor cores */
 };
 
 const char* kxc_b200_last_error(void);

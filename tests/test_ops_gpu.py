@@ -435,3 +435,51 @@ def test_cast_bool_rejected(ops):
         ops.cast(torch.zeros(4, device="cuda"), "bool")
     with pytest.raises(ValueError):
         ops.cast(torch.zeros(4, device="cuda"), "float16")
+
+
+# ---------------------------------------------------------------- three-pass tf32 (fp32-class accuracy on tensor cores)
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv2d_tf32x3_meets_the_reference_tolerance_strictly(ops, rng, case):
+    """precision="tf32x3": the reference's own acceptance rule (abs <= 1e-3 or |a-r|/max(1,|r|) <= 1e-3,
+    test/onnx_importer_test.cpp:161-177) against the fp32 oracle on the ORIGINAL operands, for every element, with an
+    order of magnitude to spare (single-pass tf32 sits at 1.0-1.3e-3 on these inputs). What is left (2e-5 at K = 4608)
+    is the accumulation itself: the tensor core's fp32 accumulator and the oracle's sequential fp32 sum round differently."""
+    N, C, H, W, O, KH, KW, s, p, d = case
+    x, w, b = conv_inputs(rng, N, C, H, W, O, KH, KW)
+    for with_bias, with_res, relu in [(True, False, True), (True, True, True), (False, False, False)]:
+        oh, ow = port.conv_out_dim(H, KH, s, p, d), port.conv_out_dim(W, KW, s, p, d)
+        res = rng.uniform(-1, 1, (N, O, oh, ow)).astype(f32) if with_res else None
+        got = host(ops.nn_conv2d(dev(x), dev(w), dev(b) if with_bias else None, (s, s), (p, p), (d, d),
+                                 residual=dev(res) if with_res else None, relu=relu, precision="tf32x3"))
+        assert ops.device_status() == 0
+        exp = conv_expect(x, w, b if with_bias else None, res, relu, s, p, d)
+        max_abs, max_rel = ref_metric(got, exp)
+        assert max_rel <= 1e-4, f"conv tf32x3 {case} bias={with_bias} res={with_res} relu={relu}: {max_abs:.3e} {max_rel:.3e}"
+
+
+def test_conv2d_config1_tf32x3_vs_single_pass(ops, rng):
+    """BASELINE config 1 (U(-1,1) data): the three-pass form is ~1000x closer to the fp32 reference than one pass."""
+    x = rng.uniform(-1, 1, (1, 64, 56, 56)).astype(f32)
+    w = rng.normal(0, np.sqrt(2 / 576), (64, 64, 3, 3)).astype(f32)
+    b = rng.normal(0, 0.01, (64,)).astype(f32)
+    expect = port.relu(port.conv2d(x, w, b, (1, 1), (1, 1)))
+    one = ref_metric(host(ops.nn_conv2d(dev(x), dev(w), dev(b), (1, 1), (1, 1), relu=True, precision="tf32")), expect)[1]
+    three = ref_metric(host(ops.nn_conv2d(dev(x), dev(w), dev(b), (1, 1), (1, 1), relu=True, precision="tf32x3")), expect)[1]
+    assert three <= 2e-5 and three * 50 < one, (one, three)
+
+
+@pytest.mark.parametrize("M,N,K", [(2, 4, 3), (33, 1000, 512), (130, 72, 200)])
+def test_gemm_and_matmul_tf32x3(ops, rng, M, N, K):
+    a = rng.normal(size=(M, K)).astype(f32)
+    b = rng.normal(size=(N, K)).astype(f32)
+    c = rng.normal(size=(N,)).astype(f32)
+    bt = np.ascontiguousarray(b.T)
+    for what, got, exp in (
+        ("gemm", ops.nn_gemm(dev(a), dev(b), dev(c), 1.0, 1.0, 0, 1, precision="tf32x3"), port.gemm(a, b, c)),
+        ("gemm transB=0", ops.nn_gemm(dev(a), dev(bt), dev(c), 1.0, 1.0, 0, 0, precision="tf32x3"), port.gemm(a, bt, c, 1.0, 1.0, 0, 0)),
+        ("dense", ops.nn_dense(dev(a), dev(b), precision="tf32x3"), port.dense(a, b)),
+        ("matmul", ops.matmul(dev(a), dev(bt), precision="tf32x3"), port.matmul(a, bt)),
+    ):
+        max_abs, max_rel = ref_metric(host(got), exp)
+        assert max_rel <= 1e-4, f"{what} tf32x3 {(M, N, K)}: {max_abs:.3e} {max_rel:.3e}"
+    assert ops.device_status() == 0
