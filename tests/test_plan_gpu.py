@@ -343,3 +343,34 @@ def test_imported_graph_fixture(kxc):
     got, _ = run_plan(kxc, func, io["input"], "tf32")  # 8- and 16-channel tensors: the tf32 plan's channel granularity
     assert_close(got, io["output"], 1e-2, "imported graph, tf32 plan")
 
+
+
+def test_resnet18_full_batch_properties(kxc):
+    """The benchmark's own size (batch 1024, bf16, CUDA-graph replay), checked through properties that do not need the
+    oracle to run 1024 images: every image is independent of the others, so
+      * a batch made of 16 distinct images repeated 64 times must give 64 bit-identical copies of 16 logit rows, whatever
+        tile, CTA pair or tile-pair an image's pixels land in;
+      * permuting the batch permutes the logits bit for bit;
+      * those 16 rows agree with the fp32 oracle run on the 16 images (tolerance 1e-2 of the logit scale for bf16)."""
+    rs = kxc.resnet18
+    weights = rs.make_weights(seed=0)
+    N, base = 1024, 16
+    x16 = np.random.default_rng(11).normal(0, 1, (base, 3, 224, 224)).astype(f32)
+    g = kxc.plan.CompiledGraph(rs.build(N, weights, to_constant=cuda_const), "bf16", cuda_graph=True)
+    xt = torch.from_numpy(x16).cuda().repeat(N // base, 1, 1, 1).contiguous()
+    out = g.run(xt).clone()
+    out_again = g.run(xt)  # the replayed graph
+    assert kxc.ops.device_status() == 0
+    assert torch.equal(out, out_again)
+    rows = out.view(N // base, base, 1000)
+    assert torch.equal(rows, rows[0:1].expand_as(rows)), "copies of the same image gave different logits"
+    perm = torch.from_numpy(np.random.default_rng(12).permutation(N)).cuda()
+    out_perm = g.run(xt[perm].contiguous())
+    assert torch.equal(out_perm, out[perm]), "permuting the batch did not permute the logits bit for bit"
+    exact = ograph.run(rs.build(base, weights), [x16], workers=8)
+    got = out[:base].cpu().numpy()
+    scale = float(np.abs(exact).max())
+    max_abs, _ = ref_metric(got, exact)
+    print(f"resnet18 bf16 batch 1024: 16 distinct images vs fp32 reference arithmetic normalised={max_abs / scale:.3e}")
+    assert max_abs / scale <= 1e-2
+    assert (got.argmax(1) == exact.argmax(1)).all()
