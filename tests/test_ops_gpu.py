@@ -483,3 +483,37 @@ def test_gemm_and_matmul_tf32x3(ops, rng, M, N, K):
         max_abs, max_rel = ref_metric(host(got), exp)
         assert max_rel <= 1e-4, f"{what} tf32x3 {(M, N, K)}: {max_abs:.3e} {max_rel:.3e}"
     assert ops.device_status() == 0
+
+
+# ---------------------------------------------------------------- the benchmark configurations at their full sizes
+def test_pool_add_relu_chain_full_size_bit_exact(ops, rng):
+    """BASELINE configuration 2 as it is timed: 32x64x112x112 -> max_pool2d 3x3 s2 p1 -> add -> relu, every element."""
+    x = rng.uniform(-1, 1, (32, 64, 112, 112)).astype(f32)
+    res = rng.uniform(-1, 1, (32, 64, 56, 56)).astype(f32)
+    expect = port.relu(port.add(port.max_pool2d(x, (3, 3), (2, 2), (1, 1, 1, 1)), res))
+    assert_bit_exact(host(ops.max_pool2d_add_relu(dev(x), dev(res), (3, 3), (2, 2), (1, 1, 1, 1))), expect, "fused chain, full size")
+    unfused = host(ops.nn_relu(ops.add(ops.nn_max_pool2d(dev(x), (3, 3), (2, 2), (1, 1, 1, 1)), dev(res))))
+    assert_bit_exact(unfused, expect, "three kernels, full size")
+
+
+# (Cin, Cout, k, stride, pad, Hin): the 11 distinct ResNet-18 convolutions (test/resnet18_ir_dump.cpp:281-448)
+RESNET_CONVS = [(3, 64, 7, 2, 3, 224), (64, 64, 3, 1, 1, 56), (64, 128, 3, 2, 1, 56), (128, 128, 3, 1, 1, 28), (64, 128, 1, 2, 0, 56),
+                (128, 256, 3, 2, 1, 28), (256, 256, 3, 1, 1, 14), (128, 256, 1, 2, 0, 28), (256, 512, 3, 2, 1, 14),
+                (512, 512, 3, 1, 1, 7), (256, 512, 1, 2, 0, 14)]
+
+
+@pytest.mark.parametrize("shape", RESNET_CONVS)
+def test_conv2d_s8_full_batch_256(ops, rng, shape):
+    """BASELINE configuration 5 at its batch (N = 256): 4 distinct images repeated 64 times. Images are independent,
+    so all copies must be bit-identical wherever their pixels fall in the tiling, and the 4 distinct results must be the
+    oracle's integers."""
+    C, O, k, s, p, H = shape
+    base, N = 4, 256
+    x, w, b, m, sh = s8_inputs(rng, base, C, H, H, O, k, k)
+    xt = dev(x).repeat(N // base, 1, 1, 1).contiguous()
+    got = ops.nn_conv2d_s8(xt, dev(w), dev(b), dev(m), dev(sh), (s, s), (p, p), (1, 1), relu=True)
+    assert ops.device_status() == 0
+    rows = got.view(N // base, base, *got.shape[1:])
+    assert torch.equal(rows, rows[0:1].expand_as(rows)), f"s8 conv {shape}: copies of the same image differ"
+    expect = port.conv2d_s8_requant(x, w, b, m, sh, True, (s, s), (p, p), (1, 1))
+    assert np.array_equal(got[:base].cpu().numpy(), expect), f"s8 conv {shape} at N=256 differs from the oracle"
