@@ -144,6 +144,11 @@ struct kxc_b200_plan {
     };
     GraphSlot graph_slots[kGraphSlots];
     int graph_next_slot = 0;
+    // optional last node softmax(last axis) on the graph's fp32 result: the plan proper writes into tail_buf and one
+    // more launch writes the caller's output
+    int tail_in = -1, tail_out = -1, tail_axis = -1;
+    void* tail_buf = nullptr;
+    int64_t tail_rows = 0, tail_len = 0;
     // optional NVTX ranges: one per launch, named like kxc_b200_plan_launch_info names it, inside one range per run
     bool nvtx = false;
     std::vector<std::string> nvtx_names;
@@ -151,6 +156,7 @@ struct kxc_b200_plan {
     ~kxc_b200_plan() {
         for (auto& g : graph_slots)
             if (g.exec) cudaGraphExecDestroy(g.exec);
+        if (tail_buf) cudaFree(tail_buf);
         if (arena) cudaFree(arena);
         if (weight_arena) cudaFree(weight_arena);
     }
@@ -333,6 +339,24 @@ extern "C" int32_t kxc_b200_plan_add_kernel(kxc_b200_plan* plan, const char* op_
     if (!plan || plan->finalized || !op_name || num_inputs < 0 || (num_inputs > 0 && !input_ids) || output_id < 0)
         return fail(KXC_B200_ERR_INVALID, "plan_add_kernel: bad arguments");
     if (plan->find(output_id)) return fail(KXC_B200_ERR_INVALID, "plan: value %d already defined", output_id);
+    if (std::string(op_name) == "softmax") {
+        // SoftmaxCompute (src/relay/op/nn/softmax.cc:44-70), accepted as the graph's last node
+        if (num_inputs != 1) return fail(KXC_B200_ERR_INVALID, "softmax expects exactly 1 input");
+        if (plan->tail_out >= 0) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: only one softmax (the last node) is supported");
+        if (!plan->find(input_ids[0])) return fail(KXC_B200_ERR_INVALID, "plan: node 'softmax' reads undefined value %d", input_ids[0]);
+        plan->tail_in = input_ids[0];
+        plan->tail_out = output_id;
+        plan->tail_axis = attrs ? static_cast<const kxc_b200_softmax_attrs*>(attrs)->axis : -1;
+        Value v;
+        v.id = output_id;
+        v.kind = VKind::Intermediate;
+        v.producer = -1;
+        plan->values[output_id] = v;
+        return KXC_B200_OK;
+    }
+    if (plan->tail_out >= 0)
+        for (int32_t i = 0; i < num_inputs; ++i)
+            if (input_ids[i] == plan->tail_out) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: softmax is supported as the last node only");
     Node n;
     n.op = op_name;
     n.in.assign(input_ids, input_ids + num_inputs);
@@ -382,11 +406,40 @@ extern "C" int32_t kxc_b200_plan_value_shape(kxc_b200_plan* plan, int32_t value_
 
 extern "C" int32_t kxc_b200_plan_num_launches(kxc_b200_plan* plan) {
     if (!plan || !plan->finalized) return -KXC_B200_ERR_INVALID;
-    if (plan->precision == KXC_B200_PREC_FP32) return (int32_t)plan->xsteps.size();
-    return (int32_t)plan->steps.size();
+    const int tail = plan->tail_out >= 0 ? 1 : 0;
+    if (plan->precision == KXC_B200_PREC_FP32) return (int32_t)plan->xsteps.size() + tail;
+    return (int32_t)plan->steps.size() + tail;
 }
 
+static int32_t finalize_core(kxc_b200_plan* pl);
+
 extern "C" int32_t kxc_b200_plan_finalize(kxc_b200_plan* pl) {
+    if (!pl || pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_finalize: null or already finalized");
+    if (pl->tail_out < 0) return finalize_core(pl);
+    if (pl->output_id != pl->tail_out) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: softmax is supported as the last node only");
+    Value* src = pl->find(pl->tail_in);
+    if (!src || src->kind != VKind::Intermediate)
+        return fail(KXC_B200_ERR_UNSUPPORTED, "plan: softmax must follow a kernel of the plan (use kxc_b200_softmax on its own)");
+    pl->output_id = pl->tail_in;  // the plan proper ends at the softmax's operand
+    KXC_TRY(finalize_core(pl));
+    const std::vector<int64_t> shape = pl->find(pl->tail_in)->shape;
+    const int rank = (int)shape.size();
+    const int axis = pl->tail_axis < 0 ? pl->tail_axis + rank : pl->tail_axis;
+    pl->finalized = false;  // until the checks below pass
+    if (rank < 1 || axis != rank - 1)
+        return fail(KXC_B200_ERR_UNSUPPORTED, "softmax: only the last axis is supported (the reference's reduction over an inner axis "
+                                             "reads the wrong elements)");
+    pl->find(pl->tail_out)->shape = shape;
+    pl->tail_len = shape[rank - 1];
+    pl->tail_rows = 1;
+    for (int i = 0; i < rank - 1; ++i) pl->tail_rows *= shape[i];
+    const size_t bytes = (size_t)(pl->tail_rows * pl->tail_len) * sizeof(float);
+    if (bytes > 0) KXC_CUDA_TRY(cudaMalloc(&pl->tail_buf, bytes));
+    pl->finalized = true;
+    return KXC_B200_OK;
+}
+
+static int32_t finalize_core(kxc_b200_plan* pl) {
     if (!pl || pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_finalize: null or already finalized");
     KXC_TRY(require_device());
     if (pl->output_id < 0) return fail(KXC_B200_ERR_INVALID, "plan_finalize: no output set");
@@ -879,7 +932,32 @@ struct LaunchRange {
 };
 }  // namespace
 
+static int32_t plan_run_core(kxc_b200_plan* pl, void** packed_args, void* stream, cudaEvent_t* events);
+
 static int32_t plan_run_impl(kxc_b200_plan* pl, void** packed_args, void* stream, cudaEvent_t* events) {
+    if (!pl || !pl->finalized || pl->tail_out < 0 || !packed_args) return plan_run_core(pl, packed_args, stream, events);
+    const size_t nargs = pl->inputs.size() + pl->constants.size();
+    if (!packed_args[nargs]) return fail(KXC_B200_ERR_INVALID, "plan_run: packed_args[%zu] is null", nargs);
+    if (pl->tail_rows * pl->tail_len == 0) return KXC_B200_OK;
+    std::vector<void*> args(packed_args, packed_args + nargs + 1);
+    args[nargs] = pl->tail_buf;
+    KXC_TRY(plan_run_core(pl, args.data(), stream, events));  // records events[0 .. core launches]
+    const size_t ncore = pl->precision == KXC_B200_PREC_FP32 ? pl->xsteps.size() : pl->steps.size();
+    {
+        LaunchRange range(pl, ncore);
+        kxc_b200_softmax_desc d{};
+        d.rank = 2;
+        d.shape[0] = pl->tail_rows;
+        d.shape[1] = pl->tail_len;
+        d.axis = 1;
+        void* io[2] = {pl->tail_buf, packed_args[nargs]};
+        KXC_TRY(kxc_b200_softmax(io, &d, stream));
+    }
+    if (events) KXC_CUDA_TRY(cudaEventRecord(events[ncore + 1], static_cast<cudaStream_t>(stream)));
+    return KXC_B200_OK;
+}
+
+static int32_t plan_run_core(kxc_b200_plan* pl, void** packed_args, void* stream, cudaEvent_t* events) {
     if (!pl || !pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_run: plan is not finalized");
     if (pl->precision == KXC_B200_PREC_FP32) return run_exact(pl, packed_args, stream, events);
     if (!packed_args) return fail(KXC_B200_ERR_INVALID, "plan_run: null packed_args");
@@ -1031,7 +1109,7 @@ extern "C" int32_t kxc_b200_plan_run(kxc_b200_plan* pl, void** packed_args, void
 extern "C" int32_t kxc_b200_plan_run_timed(kxc_b200_plan* pl, void** packed_args, void* stream, float* launch_ms,
                                            int32_t capacity) {
     if (!pl || !pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_run_timed: plan is not finalized");
-    const int n = pl->precision == KXC_B200_PREC_FP32 ? (int)pl->xsteps.size() : (int)pl->steps.size();
+    const int n = kxc_b200_plan_num_launches(pl);
     if (!launch_ms || capacity < n) return fail(KXC_B200_ERR_INVALID, "plan_run_timed: need room for %d durations", n);
     std::vector<cudaEvent_t> ev(n + 1);
     for (auto& e : ev) KXC_CUDA_TRY(cudaEventCreate(&e));
@@ -1065,6 +1143,13 @@ const char* step_kind_name(SKind k) {
 
 extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, char* name, int32_t name_size,
                                              double* flops, double* bytes) {
+    if (pl && pl->finalized && pl->tail_out >= 0 &&
+        index == (int)(pl->precision == KXC_B200_PREC_FP32 ? pl->xsteps.size() : pl->steps.size())) {
+        if (name && name_size > 0) snprintf(name, (size_t)name_size, "softmax rows%lld len%lld", (long long)pl->tail_rows, (long long)pl->tail_len);
+        if (flops) *flops = 0.0;
+        if (bytes) *bytes = 2.0 * (double)pl->tail_rows * (double)pl->tail_len * 4.0;
+        return KXC_B200_OK;
+    }
     if (pl && pl->finalized && pl->precision == KXC_B200_PREC_FP32) {
         if (index < 0 || index >= (int)pl->xsteps.size()) return fail(KXC_B200_ERR_INVALID, "plan_launch_info: bad index");
         const auto& xs = pl->xsteps[index];

@@ -26,6 +26,10 @@ class GemmAttrsC(ctypes.Structure):
     _fields_ = [("alpha", ctypes.c_float), ("beta", ctypes.c_float), ("transA", i32), ("transB", i32)]
 
 
+class SoftmaxAttrsC(ctypes.Structure):
+    _fields_ = [("axis", i32)]
+
+
 _PLAN_SYMBOLS = {
     "kxc_b200_plan_create": (i32, [i32, ctypes.POINTER(vp)]),
     "kxc_b200_plan_destroy": (i32, [vp]),
@@ -64,6 +68,8 @@ def _attrs_c(call):
     if call.op == "nn_gemm":
         a = a or relay.GemmAttrs()
         return GemmAttrsC(a.alpha, a.beta, a.transA, a.transB)
+    if call.op == "softmax":
+        return SoftmaxAttrsC(int(a.axis) if a is not None else -1)
     return None
 
 

@@ -59,6 +59,11 @@ class GemmAttrs:
     transB: int = 0
 
 
+@dataclass
+class SoftmaxAttrs:
+    axis: int = -1
+
+
 @dataclass(eq=False)
 class Call(Expr):
     op: str  # Relay op name: "nn_conv2d", "nn_relu", "add", ...

@@ -49,6 +49,12 @@ typedef struct kxc_b200_gemm_attrs {
     int32_t transA, transB;
 } kxc_b200_gemm_attrs;
 
+/* SoftmaxAttrsNode (include/relay/op.h): accepted for "softmax" as the LAST node of the graph, last axis only (see
+ * kxc_b200_softmax); it runs as one more launch on the plan's fp32 result. */
+typedef struct kxc_b200_softmax_attrs {
+    int32_t axis; /* negative values count from the end */
+} kxc_b200_softmax_attrs;
+
 /* precision: KXC_B200_PREC_BF16 (bf16 activations/weights, fp32 accumulate), KXC_B200_PREC_TF32 (fp32
  * activations, tf32-rounded operands, fp32 accumulate) — both on the tensor cores — or KXC_B200_PREC_FP32:
  * CUDA-core kernels in the reference's operation order on NCHW fp32 values, bit-identical to the reference's

@@ -130,6 +130,8 @@ def run(func, inputs, operand_round=None, workers=1, backend=None):
             y = be.dense(val(c.args[0], True), val(c.args[1], True))
         elif c.op == "nn_gemm":
             y = be.gemm(val(c.args[0], True), val(c.args[1], True), val(c.args[2]), a.alpha, a.beta, a.transA, a.transB)
+        elif c.op == "softmax":
+            y = be.softmax(val(c.args[0]), a.axis if a is not None else -1)
         else:
             raise NotImplementedError(c.op)
         if operand_round is not None and id(c) in stored and c is not func.body:

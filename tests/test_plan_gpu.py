@@ -374,3 +374,34 @@ def test_resnet18_full_batch_properties(kxc):
     print(f"resnet18 bf16 batch 1024: 16 distinct images vs fp32 reference arithmetic normalised={max_abs / scale:.3e}")
     assert max_abs / scale <= 1e-2
     assert (got.argmax(1) == exact.argmax(1)).all()
+
+
+@pytest.mark.parametrize("precision", ["bf16", "tf32", "fp32"])
+def test_softmax_as_last_node(kxc, rng, precision):
+    """A classifier that ends in softmax: the plan runs it as one more launch on its fp32 logits."""
+    R = kxc.relay
+    func = small_cnn(kxc, rng)
+    sm = R.Function(func.params, R.Call("softmax", [func.body], R.SoftmaxAttrs(-1)))
+    x = rng.normal(0, 1, (3, 8, 20, 20)).astype(f32)
+    logits, g0 = run_plan(kxc, func, x, precision)
+    probs, g1 = run_plan(kxc, sm, x, precision)
+    assert g1.num_launches == g0.num_launches + 1
+    assert g1.launch_info()[-1][0].startswith("softmax rows3 len10")
+    assert probs.shape == (3, 10) and np.abs(probs.sum(1) - 1).max() < 1e-5
+    # the last launch is the per-op softmax kernel on the same logits (expf of the device: a few ulp from the host's)
+    assert_close(probs, port.softmax(logits, -1), 2e-6, f"softmax tail {precision}")
+    exact = ograph.run(host_func(sm), [x])
+    assert_close(probs, exact, TOL.get(precision, 1e-5), f"softmax tail {precision} vs oracle graph")
+    # CUDA-graph replay and per-launch timing include the extra launch
+    gg = kxc.plan.CompiledGraph(sm, precision, cuda_graph=True)
+    xt = torch.from_numpy(x).cuda()
+    a = gg.run(xt).cpu().numpy()
+    b = gg.run(xt).cpu().numpy()
+    assert np.array_equal(a, probs) and np.array_equal(b, probs)
+    _, ms = gg.run_timed(xt)
+    assert len(ms) == gg.num_launches
+    # softmax over another axis, or anywhere but at the end, is refused
+    with pytest.raises(kxc.KxcError):
+        kxc.plan.CompiledGraph(R.Function(func.params, R.Call("softmax", [func.body], R.SoftmaxAttrs(0))), precision)
+    with pytest.raises(kxc.KxcError):
+        kxc.plan.CompiledGraph(R.Function(func.params, R.Call("nn_relu", [R.Call("softmax", [func.body], R.SoftmaxAttrs(-1))])), precision)
