@@ -1125,22 +1125,6 @@ extern "C" int32_t kxc_b200_plan_run_timed(kxc_b200_plan* pl, void** packed_args
 }
 
 // ---- measurement support ------------------------------------------------------------------------
-namespace {
-const char* step_kind_name(SKind k) {
-    switch (k) {
-        case SKind::InputNHWC: return "input_nhwc";
-        case SKind::InputStem: return "stem_pack";
-        case SKind::Conv: return "conv_igemm";
-        case SKind::Gemm: return "dense_igemm";
-        case SKind::MaxPool: return "maxpool_nhwc";
-        case SKind::Gap: return "gap_nhwc";
-        case SKind::Eltwise: return "eltwise_nhwc";
-        case SKind::ToNCHW: return "nhwc_to_nchw";
-    }
-    return "?";
-}
-}  // namespace
-
 extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, char* name, int32_t name_size,
                                              double* flops, double* bytes) {
     if (pl && pl->finalized && pl->tail_out >= 0 &&
@@ -1217,7 +1201,6 @@ extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, c
             snprintf(buf, sizeof(buf), "nhwc_to_nchw c%d h%d w%d", st.C, st.H, st.W);
             break;
     }
-    (void)step_kind_name;
     if (name && name_size > 0) snprintf(name, (size_t)name_size, "%s", buf);
     if (flops) *flops = fl;
     if (bytes) *bytes = by;
