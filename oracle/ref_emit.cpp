@@ -23,7 +23,10 @@
 // Each op may appear once per function: CodeGenC names buffers after the op (codegen_c.cc:38-46).
 //
 // Usage: ref_emit --import <spec.json> <params.bin>   (JSON on stdout)
-//   Loads a "kxc.onnx_import.v1" graph with the reference's own importer (LoadONNXImportSpec,
+// Usage: ref_emit --plan <spec.json> <params.bin> | ref_emit --plan-check <plan.json>   (ExecutionPlan JSON on stdout)
+//   The reference's ExecutionPlan of an imported graph in its own JSON form, and its reader applied to such a file.
+//
+//   --import loads a "kxc.onnx_import.v1" graph with the reference's own importer (LoadONNXImportSpec,
 //   src/frontend/onnx_importer.cc:410-520), runs its InferTypePass and prints the resulting Relay function as the
 //   reference sees it: inputs, calls in post order (operator name, arguments, attributes as its Attrs objects hold
 //   them, inferred output shape) and the result. The Python side feeds that one description to both the CPU checker
@@ -44,7 +47,9 @@
 #include "relay/op.h"
 #include "relay/relay.h"
 #include "relay/transforms/infer_type.h"
+#include "base/execution_plan.h"
 #include "relay/transforms/lower.h"
+#include "relay/transforms/multi_device.h"
 #include "relay/transforms/pipeline.h"
 #include "tir/transforms/pipeline.h"
 
@@ -165,7 +170,33 @@ int DumpImported(const std::string& json_path, const std::string& params_path) {
 
 }  // namespace
 
+// --plan: the reference's own ExecutionPlan for an imported graph (LowerRelayToExecPlanPass,
+// src/relay/transforms/multi_device.cc:244-), serialized by its own SerializeExecutionPlanToJson.
+int DumpPlan(const std::string& json_path, const std::string& params_path) {
+    kxc::frontend::ImportedONNXModel m = kxc::frontend::LoadONNXImportSpec(json_path, params_path);
+    kxc::Function func = kxc::relay::InferTypePass(m.function);
+    kxc::ExecutionPlan plan = kxc::relay::LowerRelayToExecPlanPass(func);
+    std::cout << kxc::SerializeExecutionPlanToJson(plan) << "\n";
+    return 0;
+}
+
+// --plan-check: feed a plan JSON (for instance one whose kernel_symbol fields were filled in) to the reference's
+// DeserializeExecutionPlanFromJson and print what it serializes back.
+int CheckPlan(const std::string& path) {
+    kxc::ExecutionPlan plan = kxc::LoadExecutionPlanFromJsonFile(path);
+    std::cout << kxc::SerializeExecutionPlanToJson(plan) << "\n";
+    return 0;
+}
+
 int main(int argc, char** argv) {
+    if ((argc == 4 && std::string(argv[1]) == "--plan") || (argc == 3 && std::string(argv[1]) == "--plan-check")) {
+        try {
+            return argc == 4 ? DumpPlan(argv[2], argv[3]) : CheckPlan(argv[2]);
+        } catch (const std::exception& e) {
+            std::cerr << "ref_emit: " << e.what() << "\n";
+            return 1;
+        }
+    }
     if (argc == 4 && std::string(argv[1]) == "--import") {
         try {
             return DumpImported(argv[2], argv[3]);
