@@ -24,16 +24,8 @@ __device__ __forceinline__ float4 add4(float4 a, float4 b) {
 }
 
 // Streaming loads/stores: every element is touched once, keep it out of L1.
-#if defined(KXC_ELTWISE_PLAIN_ALL)
-__device__ __forceinline__ float4 ldg_stream(const float4* p) { return __ldg(p); }
-__device__ __forceinline__ void stg_stream(float4* p, float4 v) { *p = v; }
-#elif defined(KXC_ELTWISE_PLAIN_STORE)
-__device__ __forceinline__ float4 ldg_stream(const float4* p) { return __ldcs(p); }
-__device__ __forceinline__ void stg_stream(float4* p, float4 v) { *p = v; }
-#else
 __device__ __forceinline__ float4 ldg_stream(const float4* p) { return __ldcs(p); }
 __device__ __forceinline__ void stg_stream(float4* p, float4 v) { __stcs(p, v); }
-#endif
 
 // Each sweep keeps kUnroll independent 16-byte loads per thread in flight; out-of-range slots are predicated off
 // instead of being handled by a second, one-load-at-a-time loop (these kernels run for ~10 us: a tail sweep
@@ -41,14 +33,10 @@ __device__ __forceinline__ void stg_stream(float4* p, float4 v) { __stcs(p, v); 
 template <bool kRelu>
 __global__ void __launch_bounds__(kThreads) relu_vec_kernel(const float4* __restrict__ x, float4* __restrict__ out,
                                                             int64_t nvec) {
-#if defined(KXC_ELTWISE_CONTIG)
-    // block-contiguous: a block's kUnroll loads cover one contiguous run of kUnroll * kThreads vectors
+    // a block's kUnroll loads cover one contiguous run of kUnroll * kThreads vectors (measured 6 % faster than loads a
+    // whole grid apart: the memory system sees one linear sweep)
     const int64_t stride = kThreads;
     for (int64_t i = (int64_t)blockIdx.x * (kUnroll * kThreads) + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * kUnroll * kThreads) {
-#else
-    const int64_t stride = (int64_t)gridDim.x * kThreads;
-    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nvec; i += kUnroll * stride) {
-#endif
         float4 v[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u)
@@ -67,13 +55,8 @@ __global__ void relu_scalar_kernel(const float* __restrict__ x, float* __restric
 template <bool kRelu>
 __global__ void __launch_bounds__(kThreads) add_vec_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
                                                            float4* __restrict__ out, int64_t nvec) {
-#if defined(KXC_ELTWISE_CONTIG)
     const int64_t stride = kThreads;
     for (int64_t i = (int64_t)blockIdx.x * (kUnrollAdd * kThreads) + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * kUnrollAdd * kThreads) {
-#else
-    const int64_t stride = (int64_t)gridDim.x * kThreads;
-    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nvec; i += kUnrollAdd * stride) {
-#endif
         float4 va[kUnrollAdd], vb[kUnrollAdd];
 #pragma unroll
         for (int u = 0; u < kUnrollAdd; ++u) {
@@ -146,7 +129,7 @@ extern "C" int32_t kxc_b200_nn_relu(void** packed_args, int64_t numel, void* str
         const int64_t nvec = numel / 4;
         vec_elems = nvec * 4;
         if (nvec > 0)
-            relu_vec_kernel<true><<<grid_for(nvec), kThreads, 0, s>>>(reinterpret_cast<const float4*>(x),
+            relu_vec_kernel<true><<<grid_for((nvec + kUnroll - 1) / kUnroll), kThreads, 0, s>>>(reinterpret_cast<const float4*>(x),
                                                                         reinterpret_cast<float4*>(out), nvec);
     }
     if (vec_elems < numel)
@@ -209,9 +192,9 @@ extern "C" int32_t kxc_b200_add(void** packed_args, const kxc_b200_add_desc* des
             auto* b4 = reinterpret_cast<const float4*>(b);
             auto* o4 = reinterpret_cast<float4*>(out);
             if (relu)
-                add_vec_kernel<true><<<grid_for(nvec), kThreads, 0, s>>>(a4, b4, o4, nvec);
+                add_vec_kernel<true><<<grid_for((nvec + kUnrollAdd - 1) / kUnrollAdd), kThreads, 0, s>>>(a4, b4, o4, nvec);
             else
-                add_vec_kernel<false><<<grid_for(nvec), kThreads, 0, s>>>(a4, b4, o4, nvec);
+                add_vec_kernel<false><<<grid_for((nvec + kUnrollAdd - 1) / kUnrollAdd), kThreads, 0, s>>>(a4, b4, o4, nvec);
         }
     }
     if (done < total) {

@@ -127,12 +127,27 @@ def config2(iters, flush, hbm, tf, src):
     xs = [torch.empty_like(x).uniform_(-1, 1, generator=g) for _ in range(sets)]
     rs = [torch.empty_like(res).uniform_(-1, 1, generator=g) for _ in range(sets)]
     os_ = [torch.empty_like(res) for _ in range(sets)]
+    # straight through the C ABI with descriptors and argument lists built once: the Python wrappers in ops.py cost
+    # 10-25 us per call, more than these kernels run
+    from . import _lib
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    pool_desc = _lib.Pool2dDesc(32, 64, 112, 112, 3, 3, 2, 2, 1, 1, 1, 1, 0)
+    add_desc = _lib.AddDesc()
+    add_desc.rank_a = add_desc.rank_b = 4
+    for i, d in enumerate(res.shape):
+        add_desc.shape_a[i] = add_desc.shape_b[i] = d
+    ptr = lambda t: t.data_ptr()  # noqa: E731
+    chain_args = [_lib.packed(ptr(xs[i]), ptr(rs[i]), ptr(os_[i])) for i in range(sets)]
+    pool_args = [_lib.packed(ptr(xs[i]), ptr(os_[i])) for i in range(sets)]
+    add_args = [_lib.packed(ptr(rs[i]), ptr(rs[(i + 1) % sets]), ptr(os_[i])) for i in range(sets)]
+    relu_args = [_lib.packed(ptr(rs[i]), ptr(os_[i])) for i in range(sets)]
+    nres = res.numel()
     rotating = [
-        ("max_pool2d_add_relu (fused chain)", 154.14e6,
-         [lambda i=i: ops.max_pool2d_add_relu(xs[i], rs[i], (3, 3), (2, 2), (1, 1, 1, 1), out=os_[i]) for i in range(sets)]),
-        ("nn_max_pool2d", 128.45e6, [lambda i=i: ops.nn_max_pool2d(xs[i], (3, 3), (2, 2), (1, 1, 1, 1)) for i in range(sets)]),
-        ("add", 77.07e6, [lambda i=i: ops.add(rs[i], os_[i]) for i in range(sets)]),
-        ("nn_relu", 51.38e6, [lambda i=i: ops.nn_relu(rs[i]) for i in range(sets)]),
+        ("max_pool2d_add_relu (fused chain)", 154.14e6, [lambda a=a: lib.kxc_b200_max_pool2d_add_relu(a, pool_desc, stream) for a in chain_args]),
+        ("nn_max_pool2d", 128.45e6, [lambda a=a: lib.kxc_b200_nn_max_pool2d(a, pool_desc, stream) for a in pool_args]),
+        ("add", 77.07e6, [lambda a=a: lib.kxc_b200_add(a, add_desc, stream) for a in add_args]),
+        ("nn_relu", 51.38e6, [lambda a=a: lib.kxc_b200_nn_relu(a, nres, stream) for a in relu_args]),
         ("reference: copy_ of 64.2 MB", 128.45e6, [lambda i=i: xs[i].view(-1)[:16056320].copy_(xs[(i + 1) % sets].view(-1)[:16056320]) for i in range(sets)]),
     ]
     for name, nbytes, fns in rotating:
