@@ -64,6 +64,8 @@ SYMBOLS = {
     "kxc_b200_abi_version": (i32, []),
     "kxc_b200_device_check": (i32, []),
     "kxc_b200_device_status": (i32, [vp, ctypes.POINTER(i32)]),
+    "kxc_b200_selftest_bounded_wait": (i32, [i64, vp, ctypes.POINTER(i32)]),
+    "kxc_b200_selftest_per_device_once": (i32, []),
     "kxc_b200_nn_conv2d": (i32, [vpp, ctypes.POINTER(Conv2dDesc), vp]),
     "kxc_b200_nn_conv2d_s8": (i32, [vpp, ctypes.POINTER(Conv2dDesc), vp]),
     "kxc_b200_nn_conv2d_static_scratch": (i32, [vpp, ctypes.POINTER(Conv2dDesc), vp]),

@@ -67,6 +67,23 @@ extern "C" const char* kxc_b200_last_error(void) { return last_error_buffer(); }
 extern "C" int32_t kxc_b200_abi_version(void) { return KXC_B200_ABI_VERSION; }
 extern "C" int32_t kxc_b200_device_check(void) { return require_device(); }
 
+// Host-only check of the once-per-device bookkeeping behind the shared-memory opt-in: the action must run exactly
+// once for every device ordinal it is asked for, be retried after a failure, and refuse ordinals out of range.
+extern "C" int32_t kxc_b200_selftest_per_device_once(void) {
+    PerDeviceOnce once;
+    int calls[PerDeviceOnce::kMaxDevices] = {0};
+    auto run = [&](int dev, cudaError_t result) { return once.run(dev, [&] { ++calls[dev]; return result; }); };
+    if (run(0, cudaSuccess) != cudaSuccess || run(1, cudaSuccess) != cudaSuccess || run(0, cudaSuccess) != cudaSuccess ||
+        run(1, cudaSuccess) != cudaSuccess || run(63, cudaSuccess) != cudaSuccess)
+        return fail(KXC_B200_ERR_INVALID, "per-device once: a valid device was refused");
+    if (calls[0] != 1 || calls[1] != 1 || calls[63] != 1) return fail(KXC_B200_ERR_INVALID, "per-device once: action ran %d/%d/%d times", calls[0], calls[1], calls[63]);
+    if (run(2, cudaErrorInvalidValue) != cudaErrorInvalidValue || run(2, cudaSuccess) != cudaSuccess || run(2, cudaSuccess) != cudaSuccess || calls[2] != 2)
+        return fail(KXC_B200_ERR_INVALID, "per-device once: a failed action must be retried once, then remembered");
+    if (run(-1, cudaSuccess) == cudaSuccess || run(PerDeviceOnce::kMaxDevices, cudaSuccess) == cudaSuccess)
+        return fail(KXC_B200_ERR_INVALID, "per-device once: an ordinal out of range was accepted");
+    return KXC_B200_OK;
+}
+
 extern "C" int32_t kxc_b200_nn_conv2d(void** packed_args, const kxc_b200_conv2d_desc* desc, void* stream) {
     KXC_TRY(require_device());
     ConvDims d;

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <mutex>
 
 #include "kxc_b200.h"
 
@@ -85,6 +86,44 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     lc.attrs = attr;
     lc.numAttrs = n;
     return cudaLaunchKernelEx(&lc, kernel, static_cast<KArgs>(args)...);
+}
+
+// Runs a set-up action once per CUDA device. Function attributes such as the dynamic shared-memory opt-in belong
+// to the device that is current when they are set, so a process that drives several GPUs must repeat them on each.
+class PerDeviceOnce {
+  public:
+    static constexpr int kMaxDevices = 64;
+    // Calls `fn` (returning cudaError_t) the first time `device` is seen; later calls return that first result.
+    // A failed action is retried on the next call.
+    template <typename F>
+    cudaError_t run(int device, F&& fn) {
+        if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lock(mu_);
+        if (!done_[device]) {
+            const cudaError_t e = fn();
+            if (e != cudaSuccess) return e;
+            done_[device] = true;
+        }
+        return cudaSuccess;
+    }
+
+  private:
+    std::mutex mu_;
+    bool done_[kMaxDevices] = {};
+};
+
+// Opt-in to `bytes` of dynamic shared memory for `kernel` on the current device (once per device).
+template <typename K>
+inline int32_t smem_opt_in(PerDeviceOnce& once, K kernel, int bytes, int* device_out = nullptr) {
+    int dev = 0;
+    KXC_CUDA_TRY(cudaGetDevice(&dev));
+    if (device_out) *device_out = dev;
+    const cudaError_t e = once.run(dev, [&] {
+        return cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    });
+    if (e != cudaSuccess)
+        return fail(KXC_B200_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) on device %d: %s", bytes, dev, cudaGetErrorString(e));
+    return KXC_B200_OK;
 }
 
 constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this

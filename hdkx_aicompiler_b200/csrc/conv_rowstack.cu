@@ -335,12 +335,8 @@ int32_t rowstack3x3_bind(TcParams* p) {
 }
 
 int32_t rowstack3x3_launch(const TcParams& p, cudaStream_t stream) {
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(conv3x3_rowstack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    });
-    if (attr_err != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
+    static PerDeviceOnce smem_once;
+    KXC_TRY(smem_opt_in(smem_once, conv3x3_rowstack_kernel, kSmemBytes));
     if (!p.vec_ok || p.out == nullptr) return fail(KXC_B200_ERR_INVALID, "row-stacked 3x3 conv: pointers must be 16-byte aligned");
     const long long tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n;
     if (tiles <= 0) return KXC_B200_OK;

@@ -12,8 +12,9 @@
 //  * the operands of one call must fit (converted activations + packed weights <= the array size);
 //    larger problems are rejected with KXC_B200_ERR_NOMEM and a message naming both sizes;
 //  * the array keeps the previous call's contents; every byte a call reads is first rewritten by
-//    that call's own conversion kernels (padding channels included), and the wait-status word is
-//    only ever set on failure, so nothing needs clearing between calls;
+//    that call's own conversion kernels (padding channels included), so nothing needs clearing between
+//    calls. The wait-status word of these kernels is a second static device word; it is only ever set on
+//    failure, and kxc_b200_device_status reads and clears it together with the regular one;
 //  * two calls whose GPU work overlaps (different streams, or different host threads on different
 //    streams) race on the array. Issue them on one stream, or serialise them yourself;
 //  * the first call on each device looks up the array's device address (cudaGetSymbolAddress, with
@@ -71,6 +72,20 @@ int32_t scratch_for_current_device(DeviceScratch* out) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace
+
+namespace kxc_b200 {
+// The wait-status word of the static-scratch kernels on the current device, or nullptr while no call has resolved
+// the symbols on that device (then no such kernel has run there and the word is still zero). Never allocates.
+int32_t static_scratch_status_word(int** out) {
+    int dev = 0;
+    KXC_CUDA_TRY(cudaGetDevice(&dev));
+    *out = nullptr;
+    if (dev < 0 || dev >= kMaxDevices) return KXC_B200_OK;
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    if (g_per_device[dev].ready) *out = g_per_device[dev].status;
+    return KXC_B200_OK;
+}
+}  // namespace kxc_b200
 
 using namespace kxc_b200;
 

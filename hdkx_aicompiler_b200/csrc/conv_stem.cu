@@ -542,12 +542,8 @@ bool stem_pool_applicable(int OH, int OW, int pool_k, int pool_s, int pool_pad) 
 }
 
 int32_t stem_pool_launch(const TcParams& p, cudaStream_t stream) {
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(conv_stem_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPoolSmemBytes);
-    });
-    if (attr_err != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
+    static PerDeviceOnce smem_once;
+    KXC_TRY(smem_opt_in(smem_once, conv_stem_pool_kernel, kPoolSmemBytes));
     if (!p.vec_ok || p.out == nullptr) return fail(KXC_B200_ERR_INVALID, "fused stem conv + pool: pointers must be 16-byte aligned");
     if (!p.relu) return fail(KXC_B200_ERR_INVALID, "fused stem conv + pool: the pooling shortcut relies on the ReLU in between");
     const long long strips = (long long)(p.OH / kStripRows) * p.N;
@@ -558,12 +554,8 @@ int32_t stem_pool_launch(const TcParams& p, cudaStream_t stream) {
 }
 
 int32_t stem_direct_launch(const TcParams& p, cudaStream_t stream) {
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(conv_stem_direct_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    });
-    if (attr_err != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
+    static PerDeviceOnce smem_once;
+    KXC_TRY(smem_opt_in(smem_once, conv_stem_direct_kernel, kSmemBytes));
     if (!p.vec_ok || p.out == nullptr) return fail(KXC_B200_ERR_INVALID, "direct stem conv: pointers must be 16-byte aligned");
     const long long strips = (long long)((p.OH + kStripRows - 1) / kStripRows) * p.N;
     if (strips <= 0) return KXC_B200_OK;

@@ -421,22 +421,17 @@ template <MmaKind kKind, int KB_BYTES, int BN, int kOutMode, int kCtas, bool kDu
 int32_t launch_one(const TcParams& p, cudaStream_t stream) {
     using G = StageGeom<KB_BYTES, BN, kCtas, kMT>;
     auto kernel = conv_igemm_kernel<kKind, KB_BYTES, BN, kOutMode, kCtas, kDual, kMT>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    static int max_units[64] = {0};  // per device: CTAs (kCtas = 1) or clusters of two (kCtas = 2) resident at once
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes);
-    });
-    if (attr_err != cudaSuccess)
-        return fail(KXC_B200_ERR_CUDA, "cudaFuncSetAttribute(smem=%d): %s", G::kSmemBytes, cudaGetErrorString(attr_err));
+    static PerDeviceOnce smem_once;
+    static std::mutex units_mu;
+    static int max_units[PerDeviceOnce::kMaxDevices] = {0};  // per device: clusters of two (kCtas = 2) resident at once
+    int dev = 0;
+    KXC_TRY(smem_opt_in(smem_once, kernel, G::kSmemBytes, &dev));
     const long long m_tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n;
     const long long tiles = (long long)p.tiles_c * ((m_tiles + kCtas * kMT - 1) / (kCtas * kMT));
     if (tiles <= 0) return KXC_B200_OK;
     int units = kNumSMs;
     if constexpr (kCtas == 2) {
-        int dev = 0;
-        KXC_CUDA_TRY(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64) return fail(KXC_B200_ERR_INVALID, "device ordinal %d out of range", dev);
+        std::lock_guard<std::mutex> lock(units_mu);
         if (max_units[dev] == 0) {
             cudaLaunchConfig_t lc = {};
             cudaLaunchAttribute attr[1];

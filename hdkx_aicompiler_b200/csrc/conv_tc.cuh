@@ -94,6 +94,10 @@ int32_t tc_make_tmap(CUtensorMap* out, TcDType dtype, int rank, void* base, cons
 // Device status word shared by all tensor-core launches of this process (lazily allocated, zeroed).
 int32_t tc_status_word(int** out);
 
+// conv_static_scratch.cu: the status word of the entry point that allocates nothing (nullptr until it has been
+// used on the current device).
+int32_t static_scratch_status_word(int** out);
+
 // Fills tmA/tmB and the geometry of `p` for a regular convolution over an NHWC activation tensor
 // with `cpad` channels and weights packed as [Cout][KH][KW][cpad].
 // `status_word`: device int the kernel reports a run-out wait into; nullptr = the process-wide word

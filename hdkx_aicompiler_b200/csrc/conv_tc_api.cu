@@ -6,6 +6,7 @@
 #include "conv_common.cuh"
 #include "conv_tc.cuh"
 #include "layout.cuh"
+#include "sm100.cuh"
 
 namespace kxc_b200 {
 
@@ -210,18 +211,69 @@ int32_t gemm_tensor_core(const float* a, const float* b, const float* c, float* 
 
 using namespace kxc_b200;
 
-// Reads (and clears) the device status word written by a tensor-core kernel whose bounded wait ran
-// out. Synchronises the stream. 0 = every kernel so far completed its protocol.
+// Reads (and clears) the device status words written by a tensor-core kernel whose bounded wait ran
+// out: the regular one and the one of the static-scratch entry point. Synchronises the stream.
+// 0 = every kernel so far completed its protocol. Allocates nothing once the regular word exists.
 extern "C" int32_t kxc_b200_device_status(void* stream, int32_t* status_out) {
     KXC_TRY(require_device());
+    int* words[2] = {nullptr, nullptr};
+    KXC_TRY(tc_status_word(&words[0]));
+    KXC_TRY(static_scratch_status_word(&words[1]));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int host[2] = {0, 0};
+    for (int i = 0; i < 2; ++i)
+        if (words[i]) KXC_CUDA_TRY(cudaMemcpyAsync(&host[i], words[i], sizeof(int), cudaMemcpyDeviceToHost, s));
+    KXC_CUDA_TRY(cudaStreamSynchronize(s));
+    for (int i = 0; i < 2; ++i)
+        if (host[i] != 0) KXC_CUDA_TRY(cudaMemsetAsync(words[i], 0, sizeof(int), s));
+    const int combined = host[0] | host[1];
+    if (status_out) *status_out = combined;
+    if (combined != 0)
+        return fail(KXC_B200_ERR_DEVICE_WAIT, "a tensor-core kernel gave up a bounded wait (status %d%s)", combined,
+                    host[1] != 0 ? ", static-scratch entry point" : "");
+    return KXC_B200_OK;
+}
+
+// ---- self tests -----------------------------------------------------------------------------------------
+namespace kxc_b200 {
+namespace {
+// One CTA waits, through the same bounded wait every tensor-core kernel uses, on an mbarrier that nothing ever
+// arrives on. After `limit_ns` the wait gives up, the kernel reports into the status word and returns normally.
+__global__ void bounded_wait_selftest_kernel(uint64_t limit_ns, int* status, int* gave_up) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        sm100::mbar_init(sm100::smem_u32(&bar), 1);
+        sm100::mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool arrived = sm100::mbar_wait_bounded(sm100::smem_u32(&bar), 0, &abort_flag, limit_ns);
+        *gave_up = arrived ? 0 : 1;
+        if (!arrived) atomicExch(status, KXC_B200_ERR_DEVICE_WAIT);
+    }
+}
+}  // namespace
+}  // namespace kxc_b200
+
+extern "C" int32_t kxc_b200_selftest_bounded_wait(int64_t limit_ns, void* stream, int32_t* gave_up_out) {
+    KXC_TRY(require_device());
+    if (limit_ns <= 0 || limit_ns > 100000000ll) return fail(KXC_B200_ERR_INVALID, "selftest_bounded_wait: limit must be in (0, 100 ms]");
     int* word = nullptr;
     KXC_TRY(tc_status_word(&word));
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int* flag = nullptr;
+    KXC_CUDA_TRY(cudaMallocAsync(&flag, sizeof(int), s));
+    KXC_CUDA_TRY(cudaMemsetAsync(flag, 0, sizeof(int), s));
+    bounded_wait_selftest_kernel<<<1, 32, 0, s>>>((uint64_t)limit_ns, word, flag);
+    const int32_t rc = check_launch("bounded_wait_selftest_kernel");
     int host = 0;
-    KXC_CUDA_TRY(cudaMemcpyAsync(&host, word, sizeof(int), cudaMemcpyDeviceToHost, s));
-    KXC_CUDA_TRY(cudaStreamSynchronize(s));
-    if (host != 0) KXC_CUDA_TRY(cudaMemsetAsync(word, 0, sizeof(int), s));
-    if (status_out) *status_out = host;
-    if (host != 0) return fail(KXC_B200_ERR_DEVICE_WAIT, "a tensor-core kernel gave up a bounded wait (status %d)", host);
+    cudaError_t e = cudaMemcpyAsync(&host, flag, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFreeAsync(flag, s);
+    if (rc != KXC_B200_OK) return rc;
+    if (e != cudaSuccess) return fail(KXC_B200_ERR_CUDA, "selftest_bounded_wait: %s", cudaGetErrorString(e));
+    if (gave_up_out) *gave_up_out = host;
     return KXC_B200_OK;
 }

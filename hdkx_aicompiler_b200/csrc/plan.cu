@@ -24,6 +24,7 @@
 #include <cstring>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -71,6 +72,7 @@ struct Node {
 struct PackedWeight {
     int const_id = -1;
     void* ptr = nullptr;       // plan-owned, tensor-core layout
+    void* ptr_lo = nullptr;    // TF32X3 plans: the tf32 rounding of what `ptr`'s rounding dropped
     size_t bytes = 0;
     const void* source = nullptr;  // user pointer it was packed from
     int mode = 0;              // 0 conv OHWI, 1 stem (igemm), 2 dense [N,K], 3 dense from [K,N], 4 stem (direct kernel)
@@ -93,6 +95,10 @@ struct Step {
     // conv / gemm
     TcParams params{};
     TcConfig cfg{};
+    // TF32X3 plans: the two correction passes (x_lo * w_hi, x_hi * w_lo) that run before `params` (x_hi * w_hi);
+    // src_input = the graph input this step reads through its NHWC copy (-1: an intermediate)
+    TcParams params_lohi{}, params_hilo{};
+    int src_input = -1;
     // pooling / misc geometry
     int N = 0, C = 0, H = 0, W = 0, OH = 0, OW = 0;
     kxc_b200_pool2d_attrs pool{};
@@ -113,6 +119,11 @@ int64_t numel_of(const std::vector<int64_t>& s) {
 struct kxc_b200_plan {
     int precision = KXC_B200_PREC_BF16;
     TcDType dtype = kTcBF16;
+    // KXC_B200_PREC_TF32X3: activations stay full fp32 in the arena; every convolution / dense step splits its
+    // input into tf32 high and low parts (x3_scratch) and runs three tensor-core passes into the same fp32 output
+    bool x3 = false;
+    void* x3_scratch = nullptr;
+    size_t x3_half_bytes = 0;  // the low part starts this many bytes into x3_scratch
     std::map<int, Value> values;
     std::vector<int> inputs, constants;
     std::vector<Node> nodes;
@@ -152,11 +163,15 @@ struct kxc_b200_plan {
     // optional NVTX ranges: one per launch, named like kxc_b200_plan_launch_info names it, inside one range per run
     bool nvtx = false;
     std::vector<std::string> nvtx_names;
+    // one run in flight per plan: run / run_timed calls from several host threads are serialised here (the arena,
+    // the packed weights and the captured graphs are per plan)
+    std::mutex run_mu;
 
     ~kxc_b200_plan() {
         for (auto& g : graph_slots)
             if (g.exec) cudaGraphExecDestroy(g.exec);
         if (tail_buf) cudaFree(tail_buf);
+        if (x3_scratch) cudaFree(x3_scratch);
         if (arena) cudaFree(arena);
         if (weight_arena) cudaFree(weight_arena);
     }
@@ -295,12 +310,14 @@ static int32_t run_exact(kxc_b200_plan* pl, void** packed_args, void* stream, cu
 
 extern "C" int32_t kxc_b200_plan_create(int32_t precision, kxc_b200_plan** out) {
     if (!out) return fail(KXC_B200_ERR_INVALID, "plan_create: null out pointer");
-    if (precision != KXC_B200_PREC_BF16 && precision != KXC_B200_PREC_TF32 && precision != KXC_B200_PREC_FP32)
-        return fail(KXC_B200_ERR_UNSUPPORTED, "plan_create: precision must be KXC_B200_PREC_BF16, _TF32 or _FP32");
+    if (precision != KXC_B200_PREC_BF16 && precision != KXC_B200_PREC_TF32 && precision != KXC_B200_PREC_FP32 &&
+        precision != KXC_B200_PREC_TF32X3)
+        return fail(KXC_B200_ERR_UNSUPPORTED, "plan_create: precision must be KXC_B200_PREC_BF16, _TF32, _TF32X3 or _FP32");
     auto* pl = new (std::nothrow) kxc_b200_plan();
     if (!pl) return fail(KXC_B200_ERR_NOMEM, "plan_create: out of host memory");
     pl->precision = precision;
     pl->dtype = precision == KXC_B200_PREC_BF16 ? kTcBF16 : kTcTF32;
+    pl->x3 = precision == KXC_B200_PREC_TF32X3;
     *out = pl;
     return KXC_B200_OK;
 }
@@ -524,7 +541,7 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
             PackedWeight pw;
             pw.const_id = n.in[1];
             pw.O = (int)w->shape[0]; pw.C = (int)w->shape[1]; pw.KH = (int)w->shape[2]; pw.KW = (int)w->shape[3];
-            const bool stem = is_input(n.in[0]) && st.C <= 4 && n.conv.strides[0] == 2 && n.conv.strides[1] == 2 &&
+            const bool stem = !pl->x3 && is_input(n.in[0]) && st.C <= 4 && n.conv.strides[0] == 2 && n.conv.strides[1] == 2 &&
                               n.conv.dilation[0] == 1 && n.conv.dilation[1] == 1 && pw.KW <= 8 && st.W >= 8;
             if (stem) {
                 pw.mode = 1;
@@ -717,6 +734,7 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
         if (st.kind == SKind::Conv && is_input(st.in0)) {
             const bool stem = st.Hp == 1;
             const int copy_id = input_copy[st.in0 * 2 + (stem ? 1 : 0)];
+            st.src_input = st.in0;
             st.in0 = copy_id;
             if (stem) {
                 for (auto& s2 : pl->steps)
@@ -830,12 +848,26 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
     pl->arena_bytes = std::max<size_t>(top, 1024);
     KXC_CUDA_TRY(cudaMalloc(&pl->arena, pl->arena_bytes));
     size_t wtop = 0;
-    for (auto& w : pl->weights) wtop += align_up(w.bytes, 1024);
+    for (auto& w : pl->weights) wtop += align_up(w.bytes, 1024) * (pl->x3 ? 2 : 1);
     KXC_CUDA_TRY(cudaMalloc(&pl->weight_arena, std::max<size_t>(wtop, 1024)));
     wtop = 0;
     for (auto& w : pl->weights) {
         w.ptr = static_cast<uint8_t*>(pl->weight_arena) + wtop;
         wtop += align_up(w.bytes, 1024);
+        if (pl->x3) {
+            w.ptr_lo = static_cast<uint8_t*>(pl->weight_arena) + wtop;
+            wtop += align_up(w.bytes, 1024);
+        }
+    }
+    if (pl->x3) {
+        // high / low halves of the largest convolution or dense input
+        size_t half = 0;
+        for (auto& st : pl->steps) {
+            if (st.kind == SKind::Conv) half = std::max(half, align_up((size_t)st.N * st.H * st.W * st.cpad * 4, 1024));
+            if (st.kind == SKind::Gemm) half = std::max(half, align_up((size_t)st.N * pl->weights[st.weight].cpad * 4, 1024));
+        }
+        pl->x3_half_bytes = half;
+        KXC_CUDA_TRY(cudaMalloc(&pl->x3_scratch, std::max<size_t>(2 * half, 1024)));
     }
 
     // ---- tensor maps and launch parameters ----
@@ -891,9 +923,29 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
                                       pw.KH, pw.KW, st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0], st.pool.pool_size[1]));
             }
             st.params.relu = st.relu ? 1 : 0;
-            st.params.round_out_tf32 = (!st.out_is_graph_output && dt == kTcTF32) ? 1 : 0;
+            st.params.round_out_tf32 = (!st.out_is_graph_output && dt == kTcTF32 && !pl->x3) ? 1 : 0;
             st.params.residual = st.in1 >= 0 ? pl->storage(st.in1) : nullptr;
             st.params.out = st.out_is_graph_output ? nullptr : pl->storage(st.out);
+            if (pl->x3) {
+                // three passes, small terms first; each later pass adds the previous sum through its residual input
+                uint8_t* hi = static_cast<uint8_t*>(pl->x3_scratch);
+                uint8_t* lo = hi + pl->x3_half_bytes;
+                const void* act_hi = st.src_input >= 0 ? pl->storage(st.in0) : hi;  // a graph input's NHWC copy already holds the high part
+                TcConfig c2{};
+                KXC_TRY(tc_setup_conv(&st.params, &st.cfg, dt, om, act_hi, pw.ptr, st.N, st.H, st.W, st.cpad, pw.O, pw.KH, pw.KW,
+                                      st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0], st.pool.pool_size[1]));
+                KXC_TRY(tc_setup_conv(&st.params_lohi, &c2, dt, om, lo, pw.ptr, st.N, st.H, st.W, st.cpad, pw.O, pw.KH, pw.KW,
+                                      st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0], st.pool.pool_size[1]));
+                KXC_TRY(tc_setup_conv(&st.params_hilo, &c2, dt, om, act_hi, pw.ptr_lo, st.N, st.H, st.W, st.cpad, pw.O, pw.KH, pw.KW,
+                                      st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0], st.pool.pool_size[1]));
+                st.params.relu = st.relu ? 1 : 0;
+                st.params.out = st.out_is_graph_output ? nullptr : pl->storage(st.out);
+                st.params.residual = st.params.out;  // pass 3 adds the sum of passes 1 and 2
+                st.params_lohi.out = st.params.out;
+                st.params_lohi.residual = st.in1 >= 0 ? pl->storage(st.in1) : nullptr;
+                st.params_hilo.out = st.params.out;
+                st.params_hilo.residual = st.params.out;
+            }
             if (st.direct == 3) KXC_TRY(rowstack3x3_bind(&st.params));
             if (st.direct == 0 && pw.mode == 0 && !st.out_is_graph_output) KXC_TRY(tc_bind_store(&st.params, st.cfg));
             (void)ov;
@@ -902,11 +954,24 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
             TcOutMode om = st.out_is_graph_output ? kOutNHWC_F32 : (dt == kTcBF16 ? kOutNHWC_BF16 : kOutNHWC_F32);
             if (!st.out_is_graph_output && (pw.O % lanes))
                 return fail(KXC_B200_ERR_UNSUPPORTED, "plan: %d dense outputs must be a multiple of %d", pw.O, lanes);
-            KXC_TRY(tc_setup_conv(&st.params, &st.cfg, dt, om, pl->storage(st.in0), pw.ptr, st.N, 1, 1, pw.cpad, pw.O, 1, 1, 1, 0, 0, 1, 1));
+            KXC_TRY(tc_setup_conv(&st.params, &st.cfg, dt, om, pl->x3 ? pl->x3_scratch : pl->storage(st.in0), pw.ptr, st.N, 1, 1, pw.cpad,
+                                  pw.O, 1, 1, 1, 0, 0, 1, 1));
             st.params.relu = 0;
-            st.params.round_out_tf32 = (!st.out_is_graph_output && dt == kTcTF32) ? 1 : 0;
+            st.params.round_out_tf32 = (!st.out_is_graph_output && dt == kTcTF32 && !pl->x3) ? 1 : 0;
             st.params.residual = nullptr;
             st.params.out = st.out_is_graph_output ? nullptr : pl->storage(st.out);
+            if (pl->x3) {
+                uint8_t* hi = static_cast<uint8_t*>(pl->x3_scratch);
+                uint8_t* lo = hi + pl->x3_half_bytes;
+                TcConfig c2{};
+                KXC_TRY(tc_setup_conv(&st.params_lohi, &c2, dt, om, lo, pw.ptr, st.N, 1, 1, pw.cpad, pw.O, 1, 1, 1, 0, 0, 1, 1));
+                KXC_TRY(tc_setup_conv(&st.params_hilo, &c2, dt, om, hi, pw.ptr_lo, st.N, 1, 1, pw.cpad, pw.O, 1, 1, 1, 0, 0, 1, 1));
+                st.params.residual = st.params.out;
+                st.params_lohi.out = st.params.out;
+                st.params_lohi.residual = nullptr;
+                st.params_hilo.out = st.params.out;
+                st.params_hilo.residual = st.params.out;
+            }
         }
     }
     pl->finalized = true;
@@ -984,6 +1049,14 @@ static int32_t plan_run_core(kxc_b200_plan* pl, void** packed_args, void* stream
             case 2: KXC_TRY(convert_rows(static_cast<const float*>(src), w.ptr, dt, w.O, w.C, w.cpad, s)); break;
             case 3: KXC_TRY(nchw_to_nhwc(src, w.ptr, dt, 1, w.C, w.O, w.cpad, s)); break;
         }
+        if (pl->x3) {
+            switch (w.mode) {
+                case 0: KXC_TRY(pack_weights_ohwi(src, w.ptr_lo, dt, w.O, w.C, w.KH, w.KW, w.cpad, s, true)); break;
+                case 2: KXC_TRY(convert_rows(static_cast<const float*>(src), w.ptr_lo, dt, w.O, w.C, w.cpad, s, true)); break;
+                case 3: KXC_TRY(nchw_to_nhwc(src, w.ptr_lo, dt, 1, w.C, w.O, w.cpad, s, true)); break;
+                default: return fail(KXC_B200_ERR_UNSUPPORTED, "plan: weight layout %d has no TF32X3 form", w.mode);
+            }
+        }
         w.source = src;
     }
 
@@ -1009,7 +1082,31 @@ static int32_t plan_run_core(kxc_b200_plan* pl, void** packed_args, void* stream
                 if (st.out_is_graph_output) p.out = out_ptr;
                 tc_finish_params(&p);
                 if (st.weight2 >= 0 && ((reinterpret_cast<uintptr_t>(p.bias2) | reinterpret_cast<uintptr_t>(p.out2)) & 15u)) p.vec_ok = 0;
-                if (st.direct == 2) {
+                if (pl->x3) {
+                    uint8_t* hi = static_cast<uint8_t*>(pl->x3_scratch);
+                    uint8_t* lo = hi + pl->x3_half_bytes;
+                    const bool gemm = st.kind == SKind::Gemm;
+                    const int cpad = gemm ? pl->weights[st.weight].cpad : st.cpad;
+                    if (st.src_input >= 0) {
+                        KXC_TRY(nchw_to_nhwc(arg_of(st.src_input), lo, dt, st.N, st.C, st.H * st.W, cpad, s, true));
+                    } else {
+                        const int64_t rows = gemm ? (int64_t)st.N : (int64_t)st.N * st.H * st.W;
+                        const float* src = static_cast<const float*>(pl->storage(st.in0));
+                        KXC_TRY(convert_rows(src, hi, dt, rows, cpad, cpad, s, false));
+                        KXC_TRY(convert_rows(src, lo, dt, rows, cpad, cpad, s, true));
+                    }
+                    TcParams q = st.params_lohi;
+                    if (st.out_is_graph_output) q.out = out_ptr;
+                    tc_finish_params(&q);
+                    KXC_TRY(tc_launch(st.cfg, q, s));
+                    q = st.params_hilo;
+                    if (st.out_is_graph_output) { q.out = out_ptr; q.residual = out_ptr; }
+                    tc_finish_params(&q);
+                    KXC_TRY(tc_launch(st.cfg, q, s));
+                    if (st.out_is_graph_output) p.residual = out_ptr;
+                    tc_finish_params(&p);
+                    KXC_TRY(tc_launch(st.cfg, p, s));
+                } else if (st.direct == 2) {
                     KXC_TRY(st.fused_pool ? stem_pool_launch(p, s) : stem_direct_launch(p, s));
                 } else if (st.direct == 3) {
                     KXC_TRY(rowstack3x3_launch(p, s));
@@ -1063,7 +1160,9 @@ extern "C" int32_t kxc_b200_plan_set_nvtx(kxc_b200_plan* pl, int32_t enable) {
 
 extern "C" int32_t kxc_b200_plan_run(kxc_b200_plan* pl, void** packed_args, void* stream) {
     LaunchRange run_range("kxc_b200_plan_run", pl && pl->nvtx);
-    if (!pl || !pl->finalized || !packed_args || !pl->use_graph) return plan_run_impl(pl, packed_args, stream, nullptr);
+    if (!pl) return plan_run_impl(pl, packed_args, stream, nullptr);
+    std::lock_guard<std::mutex> run_lock(pl->run_mu);
+    if (!pl->finalized || !packed_args || !pl->use_graph) return plan_run_impl(pl, packed_args, stream, nullptr);
     const size_t nargs = pl->inputs.size() + pl->constants.size() + 1;
     bool packed = true;  // weights must already be packed from these constants: packing stays outside the graph
     for (auto& w : pl->weights) packed = packed && (w.source == packed_args[pl->find(w.const_id)->arg_index]);
@@ -1111,6 +1210,7 @@ extern "C" int32_t kxc_b200_plan_run_timed(kxc_b200_plan* pl, void** packed_args
     if (!pl || !pl->finalized) return fail(KXC_B200_ERR_INVALID, "plan_run_timed: plan is not finalized");
     const int n = kxc_b200_plan_num_launches(pl);
     if (!launch_ms || capacity < n) return fail(KXC_B200_ERR_INVALID, "plan_run_timed: need room for %d durations", n);
+    std::lock_guard<std::mutex> run_lock(pl->run_mu);
     std::vector<cudaEvent_t> ev(n + 1);
     for (auto& e : ev) KXC_CUDA_TRY(cudaEventCreate(&e));
     int32_t rc = plan_run_impl(pl, packed_args, stream, ev.data());

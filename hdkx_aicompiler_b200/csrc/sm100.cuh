@@ -58,7 +58,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // (or as soon as another role of the CTA has given up), so a protocol error ends in an error
 // status instead of a hung GPU.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     uint32_t spins = 0;
@@ -66,7 +67,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 0xff) == 0) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (global_timer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }

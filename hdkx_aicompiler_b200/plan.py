@@ -11,7 +11,7 @@ import torch
 from . import _lib, relay
 from ._lib import PREC_BF16, PREC_FP32, PREC_TF32, check, i32, i64, load, packed, vp, vpp
 
-PRECISIONS = {"bf16": PREC_BF16, "tf32": PREC_TF32, "fp32": PREC_FP32}
+PRECISIONS = {"bf16": PREC_BF16, "tf32": PREC_TF32, "fp32": PREC_FP32, "tf32x3": _lib.PREC_TF32X3}
 
 
 class Conv2dAttrsC(ctypes.Structure):

@@ -64,9 +64,29 @@ int32_t kxc_b200_abi_version(void);
 int32_t kxc_b200_device_check(void);
 /* The tensor-core kernels bound every device-side wait; one that runs out sets a device status word
  * instead of hanging. This call synchronises `stream`, returns that word in *status_out (0 = clean)
- * and clears it; its return value is non-zero when the word was set. No reference counterpart: the
- * reference's kernels are synchronous CPU loops (src/codegen/compiled_kernel.cc:41-55). */
+ * and clears it; its return value is non-zero when the word was set. The kernels launched by
+ * kxc_b200_nn_conv2d_static_scratch report into a word of their own, which this call reads, ORs into the
+ * result and clears as well. No reference counterpart: the reference's kernels are synchronous CPU
+ * loops (src/codegen/compiled_kernel.cc:41-55). */
 int32_t kxc_b200_device_status(void* stream, int32_t* status_out);
+
+/* Self tests of the library's safety plumbing (no reference counterpart).
+ * selftest_bounded_wait: launches ONE small kernel whose only thread waits, through the bounded wait every
+ *   tensor-core kernel uses, on a barrier nothing ever arrives on. After `limit_ns` (at most 100 ms) the wait
+ *   gives up, the kernel sets the device status word to KXC_B200_ERR_DEVICE_WAIT and returns normally;
+ *   *gave_up_out = 1. A following kxc_b200_device_status call must report and clear the word. Nothing hangs,
+ *   traps or faults: this is the path a protocol error in a real kernel would take.
+ * selftest_per_device_once: host only (runs without a GPU): checks the once-per-device bookkeeping that repeats
+ *   the shared-memory opt-in of every kernel on each device of a multi-GPU process. Returns 0 when it holds. */
+int32_t kxc_b200_selftest_bounded_wait(int64_t limit_ns, void* stream, int32_t* gave_up_out);
+int32_t kxc_b200_selftest_per_device_once(void);
+
+/* Threading. Every per-operator entry point of this header is re-entrant: it keeps no mutable state besides
+ * thread-safe caches (device check, per-device kernel attributes, the status words) and a per-thread error
+ * message, so several host threads may call the same or different entry points at the same time, each on its
+ * own stream, as the reference's KernelRunner does (src/runtime/kernel_runner.cc:17-30). The exceptions are
+ * spelled out where they apply: kxc_b200_nn_conv2d_static_scratch (one shared workspace) here, and a
+ * kxc_b200_plan object in kxc_b200_plan.h (one run in flight per plan). */
 
 /* ---------------------------------------------------------------------------------------------
  * nn_conv2d — replaces the kernel generated from topi::conv2d_nchw (include/te/topi/nn.h:107-158)

@@ -26,6 +26,13 @@
 extern "C" {
 #endif
 
+/* Threading: a plan owns ONE activation arena and ONE set of captured CUDA graphs, so it supports one run in
+ * flight at a time. kxc_b200_plan_run / _run_timed calls on the same plan are serialised by a mutex inside the
+ * plan on the host side, and the caller must not enqueue two runs of one plan on DIFFERENT streams without
+ * ordering them (they would share the arena on the GPU). Different plans are independent: a host that runs the
+ * same graph from several threads (src/runtime/kernel_runner.cc:17-30, src/runtime/runtime_session.cc:115-161)
+ * creates one plan per thread; the weights are packed per plan. Building calls (add_*, finalize) are not
+ * thread-safe per plan. */
 typedef struct kxc_b200_plan kxc_b200_plan;
 
 /* Attribute structs: the fields of Conv2DAttrsNode (include/relay/op.h:104-120), MaxPool2DAttrsNode
@@ -56,9 +63,12 @@ typedef struct kxc_b200_softmax_attrs {
 } kxc_b200_softmax_attrs;
 
 /* precision: KXC_B200_PREC_BF16 (bf16 activations/weights, fp32 accumulate), KXC_B200_PREC_TF32 (fp32
- * activations, tf32-rounded operands, fp32 accumulate) — both on the tensor cores — or KXC_B200_PREC_FP32:
- * CUDA-core kernels in the reference's operation order on NCHW fp32 values, bit-identical to the reference's
- * CPU lowering of the same graph. */
+ * activations, tf32-rounded operands, fp32 accumulate), KXC_B200_PREC_TF32X3 (full fp32 activations; every
+ * convolution / dense node splits both operands into tf32 high and low parts and runs three tensor-core passes,
+ * lo*hi + hi*lo + hi*hi, into one fp32 result: fp32-class accuracy, the mode that meets the reference's 1e-3
+ * acceptance metric of test/onnx_importer_test.cpp:161-177 on a whole network) — all three on the tensor cores —
+ * or KXC_B200_PREC_FP32: CUDA-core kernels in the reference's operation order on NCHW fp32 values, bit-identical
+ * to the reference's CPU lowering of the same graph. */
 int32_t kxc_b200_plan_create(int32_t precision, kxc_b200_plan** out);
 int32_t kxc_b200_plan_destroy(kxc_b200_plan* plan);
 

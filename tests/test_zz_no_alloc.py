@@ -5,7 +5,9 @@ every other test. The test is self-contained, so it also passes alone in a fresh
 
 It calls the entry point through the C ABI twice in a row with different operands (the second call
 reuses the library's fixed workspace with the first call's bytes still in it) and checks each result
-against the regular, allocating entry point, which runs the same kernels on the same values.
+against the regular, allocating entry point, which runs the same kernels on the same values, and against
+the CPU oracle on identically rounded operands. A further pair of calls checks the claim itself: the
+device's free memory is the same before and after a warmed-up call, and the status word stays clean.
 """
 import ctypes
 
@@ -55,6 +57,39 @@ def test_static_scratch_conv_matches_allocating_entry_point(precision):
         err = np.abs(a - r) / np.maximum(1.0, np.abs(r))
         assert err.max() <= 2e-5, err.max()
         assert np.array_equal(a, r)
+        # and against the CPU oracle on the same rounded operands (only the fp32 summation order differs)
+        from oracle import port
+        rnd = port.round_bf16 if precision == "bf16" else port.round_tf32
+        exp = port.relu(port.add(port.conv2d(rnd(x.cpu().numpy()), rnd(w.cpu().numpy()), b.cpu().numpy(), (s, s), (p, p)),
+                                 res.cpu().numpy()))
+        err = np.abs(a - exp) / np.maximum(1.0, np.abs(exp))
+        assert err.max() <= 2e-5, err.max()
+    # a wait that ran out in these kernels would show here: their status word is read together with the regular one
+    from hdkx_aicompiler_b200 import ops
+    assert ops.device_status() == 0
+
+
+def test_static_scratch_call_allocates_nothing():
+    """Free device memory is the same before and after a warmed-up call (and its kernels have finished)."""
+    from hdkx_aicompiler_b200 import _lib, ops
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    N, C, H, W, O, K = 2, 32, 20, 20, 64, 3
+    x = torch.rand(N, C, H, W, device="cuda")
+    w = torch.rand(O, C, K, K, device="cuda")
+    b = torch.rand(O, device="cuda")
+    res = torch.rand(N, O, H, W, device="cuda")
+    out = torch.empty(N, O, H, W, device="cuda")
+    d = (N, C, H, W, O, K, K, 1, 1, 1, 1, 1, 1, _lib.BIAS | _lib.RESIDUAL | _lib.RELU, _lib.PREC_BF16)
+    assert _call(lib, lib.kxc_b200_nn_conv2d_static_scratch, x, w, b, res, out, d, stream) == 0, _lib.last_error()  # warm-up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert _call(lib, lib.kxc_b200_nn_conv2d_static_scratch, x, w, b, res, out, d, stream) == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+    assert ops.device_status() == 0
 
 
 def test_static_scratch_rejects_oversize():
