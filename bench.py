@@ -11,8 +11,13 @@ gathered to rank 0 with one NCCL gather inside the step). Prints ONE JSON line o
 value     device-timed (CUDA events, max over ranks) with the inputs resident in HBM
 e2e       the same step through the public API with HOST buffers: pinned-host -> device copy of the
           images and device -> host read of the logits inside the timed region
-roofline  the tensor-core implicit-GEMM kernel (20 conv + 1 dense launches per step): algorithmic FLOPs
-          / its summed launch durations, from one run with CUDA events between launches
+roofline  the tensor-core launches of a step (20 convolutions in 17 launches + 1 dense): algorithmic FLOPs / their summed
+          launch durations, from runs with CUDA events between launches; `frac` is taken against the measured cuBLAS
+          bf16 BURST figure (the launches are timed one by one, the whole timed region lasts a tenth of a second),
+          `frac_sustained` against the seconds-long figure
+hbm_kernels / config1 / config3  (one GPU only) the benchmark's other single-GPU configurations, measured in the same
+          run after the headline timing: the memory-bound pool -> add -> relu kernels at 32x64x112x112 against the measured
+          copy bandwidth, the single fused convolution, ResNet-18 fp32/tf32 at batch 32 (microbench.py)
 cpu_baseline  the reference compiler's own CPU lowering (oracle/_ref) on a bounded sample, rank 0 only
 
 --impl reference times that CPU path alone, on all host cores (independent batch shards per core).
@@ -30,9 +35,16 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 GLOBAL_BATCH = 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of the tensor-core launches of one bf16 plan run, per image, from the ncu
-# capture summarised in profiles/conv_direct_stem_pool_igemm_b128_ncu_full.md (taken at 128 images; it grows with the batch)
-NCU_DRAM_BYTES_PER_IMAGE = 6.03e6
+# dram__bytes_read.sum + dram__bytes_write.sum per image of the tensor-core launches of one bf16 plan run, by kernel
+# family, from ncu captures of this script at 512 images per GPU (about 2.5 GB on the device; a capture at the full 1024
+# would break the size rule for captures). Outputs of 205-411 MB no longer fit the 126 MB L2 at that size, as at 1024.
+NCU_TRAFFIC_BATCH = 512
+NCU_DRAM_BYTES_PER_IMAGE = {
+    "conv_stem_pool_nchw": None,
+    "conv_rowstack": None,
+    "conv_igemm": None,
+    "dense_igemm": None,
+}
 
 METRIC = "resnet18_inference_throughput"
 UNIT = "img/s"
@@ -148,6 +160,7 @@ def main():
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch (default: the benchmark's 1024)")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "tf32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-side-configs", action="store_true", help="skip the pool/eltwise, single-conv and batch-32 measurements")
     ap.add_argument("--gather", default="nccl", choices=["nccl", "peer"],
                     help="exchange step: NCCL gather of the logits (default) or the dense layer's epilogue storing them "
                          "straight into rank 0's buffer through peer-mapped memory")
@@ -229,6 +242,8 @@ def main():
                 peers[j].complete()  # every rank's last kernel has stored its shard into rank 0's buffer
                 if from_host and rank == 0:
                     host_out.copy_(peers[j].gathered(), non_blocking=True)
+                # a second barrier after rank 0 has read: no rank's stores of a LATER step may land in this buffer before
+                peers[j].complete()
             else:
                 parts = gathers[j](logits_buf[j])  # GatherToWorker0: shards in rank order on rank 0
                 if from_host and rank == 0:
@@ -261,6 +276,23 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    # With more than one GPU: one untimed step through BOTH forms of the exchange, compared bit for bit on rank 0
+    # (the dense layer's epilogue storing its logits straight into rank 0's buffer over NVLink vs the NCCL gather).
+    peer_check = None
+    if world > 1:
+        try:
+            chk = peers[0] if peers else PeerStoreToWorker0(graph.out_shape, torch.float32, device)
+            graph.run(xs[0], out=chk.output())
+            chk.complete()
+            graph.run(xs[0], out=logits_buf[0])
+            parts = gathers[0](logits_buf[0])
+            torch.cuda.synchronize()
+            if rank == 0:
+                peer_check = "ok" if torch.equal(chk.gathered(), torch.cat(parts, 0)) else "failed"
+            chk.complete()
+        except Exception as e:  # noqa: BLE001  (symmetric memory unavailable on this box: report, do not fail the bench)
+            peer_check = f"unavailable: {type(e).__name__}"
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -292,6 +324,10 @@ def main():
     achieved = tc_flops / (tc_ms / 1e3) / 1e12
     layers = [{"launch": n, "ms": round(t, 4), "tflops": round(f / (t / 1e3) / 1e12, 1) if f else None,
                "gbs": round(b / (t / 1e3) / 1e9, 0)} for (n, f, b), t in zip(info, launch_ms)]
+    families = collections.Counter(n.split()[0] for n, _, _, _ in tc)
+    traffic = None
+    if args.precision == "bf16" and all(NCU_DRAM_BYTES_PER_IMAGE.get(k) is not None for k in families):
+        traffic = sum(NCU_DRAM_BYTES_PER_IMAGE[k] for k in families) * per_gpu
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -306,23 +342,49 @@ def main():
         "e2e": {"value": args.batch / (e2e_ms / args.steps / 1e3), "unit": UNIT,
                 "h2d_bytes_per_step": int(host_in.numel() * 4 * world), "d2h_bytes_per_step": int(args.batch * graph.out_shape[1] * 4)},
         "gpu_launches": int(graph.num_launches * args.steps),
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
-                     "frac": achieved / peaks["tflops_sustained"],
-                     "traffic": NCU_DRAM_BYTES_PER_IMAGE * per_gpu if args.precision == "bf16" else None,
-                     "traffic_note": "dram read+write bytes of the same launches from an ncu capture at 128 images, "
-                                     "scaled by the per-GPU batch (profiles/conv_direct_stem_pool_igemm_b128_ncu_full.md); "
-                                     "algorithmic bytes: %.2f GB" % (sum(b for n, f, b in info if n.startswith(("conv_", "dense_"))) / 1e9),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["tflops_burst"],
+                     "peak_sustained": peaks["tflops_sustained"], "frac_sustained": achieved / peaks["tflops_sustained"],
+                     "peak_note": "frac: cuBLAS bf16 burst figure (each launch is timed alone between CUDA events, best of three; "
+                                  "the timed region lasts ~0.1 s); frac_sustained: the seconds-long figure under the power cap",
+                     "step_level": {"achieved": tc_flops / (ms_per_step / 1e3) / 1e12,
+                                    "frac": tc_flops / (ms_per_step / 1e3) / 1e12 / peaks["tflops_burst"],
+                                    "note": "same FLOPs over the whole device-timed step (all launches, gaps and the gather included)"},
+                     "traffic": traffic,
+                     "traffic_note": f"dram read+write bytes per image by kernel family from ncu captures at {NCU_TRAFFIC_BATCH} images per GPU, "
+                                     "summed and scaled by the per-GPU batch; algorithmic bytes: %.2f GB" % (
+                                         sum(b for n, f, b in info if n.startswith(("conv_", "dense_"))) / 1e9),
                      "peak_source": peaks["source"],
-                     "kernel": "all tensor-core launches of a step: " + ", ".join(
-                         f"{c} x {k}" for k, c in sorted(collections.Counter(n.split()[0] for n, _, _, _ in tc).items())),
+                     "kernel": "all tensor-core launches of a step: " + ", ".join(f"{c} x {k}" for k, c in sorted(families.items())),
                      "flops_per_step_per_gpu": tc_flops, "ms_per_step_in_kernel": tc_ms},
         "launches": layers,
     }
+    if peer_check is not None:
+        line["peer_store_check"] = peer_check
+    if world == 1 and not args.no_side_configs:
+        # the benchmark's other single-GPU configurations, in the same process on the same GPU (after the headline timing)
+        import microbench
+        microbench.QUIET = True
+        del graph, xs, logits_buf
+        torch.cuda.empty_cache()
+        torch.cuda.set_stream(torch.cuda.default_stream(device))
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+        hbm, tf = peaks["hbm_gbs"], peaks["tflops_burst"]
+        line["hbm_kernels"] = [{"kernel": r["kernel"], "form": r["form"], "bytes": r["algorithmic_bytes"], "ms": round(r["ms"], 5),
+                                "gbs": round(r["gbs"], 1), "frac": round(r["frac_of_hbm_peak"], 4)}
+                               for r in microbench.config2(10, flush, hbm, tf, peaks["source"])]
+        line["hbm_kernels_note"] = ("max_pool2d 3x3 s2 p1 on 32x64x112x112 fp32 -> add -> relu through the C ABI, L2 flushed between "
+                                    f"iterations; frac = algorithmic bytes / time / measured copy bandwidth {hbm} GB/s")
+        c1 = microbench.config1_plan(10, flush, hbm, tf, peaks["source"])
+        line["config1"] = {"workload": "conv2d 1x64x56x56 (*) 64x64x3x3 + bias + relu, bf16 plan, CUDA-graph replay",
+                           "ms": round(c1["ms"], 5), "tflops": round(c1["tflops"], 2), "launch_ms": c1["launch_ms"]}
+        line["config3"] = [{"workload": r["kernel"], "ms": round(r["ms"], 4), "img_per_s": round(r["img_per_s"], 1),
+                            "tflops": round(r["tflops"], 1)} for r in microbench.config3(5, flush, hbm, tf, peaks["source"])]
     if not args.no_cpu_baseline:
-        t0 = time.perf_counter()
         cpu_value, kind = cpu_reference_throughput(4, 1, steps=1, warmup=0)
         line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": kind,
-                                "sample": f"4 images of the same network, one core, {time.perf_counter() - t0:.0f} s incl. kernel build"}
+                                "sample": f"4 images of the same network on one core, {4 / cpu_value:.1f} s timed (the per-operator kernels "
+                                          "are compiled and loaded before the timed pass)"}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -16,4 +16,15 @@ int32_t stem_direct_launch(const TcParams& p, cudaStream_t stream);
 bool stem_pool_applicable(int OH, int OW, int pool_k, int pool_s, int pool_pad);
 int32_t stem_pool_launch(const TcParams& p, cudaStream_t stream);
 
+// conv_stem_fused.cu: the same convolution + bias + ReLU + max_pool2d(3x3, s2, p1), reading the NCHW fp32 graph
+// input directly (the packed layout exists only in shared memory) and issuing row-stacked MMAs. `p.aux_in` is the
+// fp32 input (bound at run time), `p.out` the pooled bf16 NHWC tensor. Bit-identical to stem_pool_launch.
+bool stem_pool_nchw_applicable(TcDType dtype, int C, int O, int KH, int KW, int W, int OH, int OW, int Wp);
+size_t stem_stacked_weight_bytes();
+// OIHW fp32 -> filter rows stacked by parity in core-matrix order
+int32_t stem_stacked_pack_weights(const float* w, void* out, int O, int C, int KW, cudaStream_t s);
+int32_t stem_pool_nchw_setup(TcParams* p, const void* packed_w, int N, int C, int H, int W, int OH, int OW, int pad_h, int pad_w,
+                             int Hp, int Wp);
+int32_t stem_pool_nchw_launch(const TcParams& p, cudaStream_t stream);
+
 }  // namespace kxc_b200

@@ -75,7 +75,8 @@ struct PackedWeight {
     void* ptr_lo = nullptr;    // TF32X3 plans: the tf32 rounding of what `ptr`'s rounding dropped
     size_t bytes = 0;
     const void* source = nullptr;  // user pointer it was packed from
-    int mode = 0;              // 0 conv OHWI, 1 stem (igemm), 2 dense [N,K], 3 dense from [K,N], 4 stem (direct kernel)
+    int mode = 0;              // 0 conv OHWI, 1 stem (igemm), 2 dense [N,K], 3 dense from [K,N], 4 stem (direct kernel),
+                               // 5 stem, filter rows stacked by parity (fused-input kernel)
     int O = 0, C = 0, KH = 0, KW = 0, cpad = 0;
 };
 
@@ -89,6 +90,7 @@ struct Step {
     bool out_is_graph_output = false;
     int direct = 0;  // 0 = implicit-GEMM kernel; 1 = direct 3x3 kernel; 2 = direct stem kernel
     int fused_pool = 0;  // direct stem kernel only: the following max_pool2d(3x3, s2, p1) is computed in its epilogue
+    int direct_input = 0;  // fused stem kernel reads the NCHW fp32 graph input itself: no packed copy, no conversion step
     // second output (two-output implicit-GEMM kernel): a 1x1 convolution of the same stride over the same input
     int weight2 = -1, bias2_const = -1, out2 = -1;
     bool relu2 = false;
@@ -532,6 +534,10 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
                         pl->nodes[pc].fused_into_other = true;
                         cur = pl->nodes[pc].out;
                         emit_at = pc;
+                        const char* e3 = getenv("KXC_B200_STEM_FUSED_INPUT");  // "0" keeps the pack kernel + packed-input kernel
+                        if ((!e3 || atoi(e3) != 0) && n.conv.padding[0] == KHc / 2 && n.conv.padding[1] == KWc / 2 &&
+                            stem_pool_nchw_applicable(dt, st.C, (int)w->shape[0], KHc, KWc, st.W, OHc, OWc, Wpc))
+                            st.direct_input = 1;
                     }
                 }
             }
@@ -700,7 +706,7 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
     // input conversion steps go first
     for (auto& pr : pending) {
         Step& st = pr.second;
-        if (st.kind != SKind::Conv || !is_input(st.in0)) continue;
+        if (st.kind != SKind::Conv || !is_input(st.in0) || st.direct_input) continue;
         const bool stem = st.Hp == 1;
         const int key = st.in0 * 2 + (stem ? 1 : 0);
         if (input_copy.count(key)) continue;
@@ -731,7 +737,16 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
     }
     for (auto& pr : pending) {
         Step st = pr.second;
-        if (st.kind == SKind::Conv && is_input(st.in0)) {
+        if (st.kind == SKind::Conv && is_input(st.in0) && st.direct_input) {
+            // geometry of the packed layout the kernel builds in shared memory (same as the InputStem step's)
+            const PackedWeight& pw = pl->weights[st.weight];
+            const int OW = (int)conv_out_dim(st.W, pw.KW, 2, st.pad_w, 1);
+            st.Hp = st.H + 2 * st.pad_h;
+            st.Hp += st.Hp & 1;
+            st.Wp = (std::max(st.W + 2 * st.pad_w, 2 * (OW - 1) + 8) + 3) / 4 * 4;
+            st.src_input = st.in0;
+            st.in0 = -1;
+        } else if (st.kind == SKind::Conv && is_input(st.in0)) {
             const bool stem = st.Hp == 1;
             const int copy_id = input_copy[st.in0 * 2 + (stem ? 1 : 0)];
             st.src_input = st.in0;
@@ -876,6 +891,10 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
             PackedWeight& pw = pl->weights[st.weight];
             Value* ov = pl->find(st.out);
             const int stem_oh = (int)conv_out_dim(st.H, pw.KH, 2, st.pad_h, 1), stem_ow = (int)conv_out_dim(st.W, pw.KW, 2, st.pad_w, 1);
+            if (st.direct_input) {
+                pw.mode = 5;
+                if (stem_stacked_weight_bytes() > pw.bytes) return fail(KXC_B200_ERR_INVALID, "plan: stacked stem weights do not fit their slot");
+            }
             if (pw.mode == 1 && !st.out_is_graph_output) {
                 // the direct stem kernel writes bf16 NHWC only; its packed weights take the same number of bytes
                 const char* e = getenv("KXC_B200_STEM_DIRECT");  // "0" keeps the implicit-GEMM stem for A/B runs
@@ -888,8 +907,12 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
                 return fail(KXC_B200_ERR_UNSUPPORTED, "plan: a residual convolution cannot be the graph output");
             if (!st.out_is_graph_output && (pw.O % lanes))
                 return fail(KXC_B200_ERR_UNSUPPORTED, "plan: %d output channels must be a multiple of %d", pw.O, lanes);
-            if (st.fused_pool && pw.mode != 4) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: fused stem pooling needs the direct stem kernel");
-            if (pw.mode == 4) {
+            if (st.fused_pool && pw.mode != 4 && pw.mode != 5) return fail(KXC_B200_ERR_UNSUPPORTED, "plan: fused stem pooling needs the direct stem kernel");
+            if (pw.mode == 5) {
+                st.direct = 4;
+                KXC_TRY(stem_pool_nchw_setup(&st.params, pw.ptr, st.N, st.C, st.H, st.W, stem_oh, stem_ow, st.pad_h, st.pad_w, st.Hp, st.Wp));
+                st.cfg = TcConfig{dt, 64, 64, om};
+            } else if (pw.mode == 4) {
                 st.direct = 2;
                 KXC_TRY(stem_direct_setup(&st.params, pl->storage(st.in0), pw.ptr, st.N, stem_oh, stem_ow, pw.KH, st.Hp, st.Wp));
                 st.cfg = TcConfig{dt, 64, 64, om};
@@ -1046,6 +1069,7 @@ static int32_t plan_run_core(kxc_b200_plan* pl, void** packed_args, void* stream
             case 0: KXC_TRY(pack_weights_ohwi(src, w.ptr, dt, w.O, w.C, w.KH, w.KW, w.cpad, s)); break;
             case 1: KXC_TRY(stem_pack_weights(static_cast<const float*>(src), w.ptr, dt, w.O, w.C, w.KH, w.KW, s)); break;
             case 4: KXC_TRY(stem_direct_pack_weights(static_cast<const float*>(src), w.ptr, w.O, w.C, w.KH, w.KW, s)); break;
+            case 5: KXC_TRY(stem_stacked_pack_weights(static_cast<const float*>(src), w.ptr, w.O, w.C, w.KW, s)); break;
             case 2: KXC_TRY(convert_rows(static_cast<const float*>(src), w.ptr, dt, w.O, w.C, w.cpad, s)); break;
             case 3: KXC_TRY(nchw_to_nhwc(src, w.ptr, dt, 1, w.C, w.O, w.cpad, s)); break;
         }
@@ -1106,6 +1130,9 @@ static int32_t plan_run_core(kxc_b200_plan* pl, void** packed_args, void* stream
                     if (st.out_is_graph_output) p.residual = out_ptr;
                     tc_finish_params(&p);
                     KXC_TRY(tc_launch(st.cfg, p, s));
+                } else if (st.direct == 4) {
+                    p.aux_in = arg_of(st.src_input);
+                    KXC_TRY(stem_pool_nchw_launch(p, s));
                 } else if (st.direct == 2) {
                     KXC_TRY(st.fused_pool ? stem_pool_launch(p, s) : stem_direct_launch(p, s));
                 } else if (st.direct == 3) {
@@ -1261,10 +1288,11 @@ extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, c
             const double out_elems = (double)p.N * p.OH * p.OW * w.O;
             fl = 2.0 * out_elems * w.C * w.KH * w.KW;  // padded taps counted, as the reference executes them
             if (st.weight2 >= 0) fl += 2.0 * out_elems * w.C;  // the 1x1 convolution computed by the same launch
-            const double in_bytes = (w.mode == 1 || w.mode == 4) ? (double)st.N * st.Hp * st.Wp * 4 * eb : (double)st.N * st.H * st.W * st.cpad * eb;
+            const double in_bytes = w.mode == 5 ? (double)st.N * st.C * st.H * st.W * 4.0
+                                                : ((w.mode == 1 || w.mode == 4) ? (double)st.N * st.Hp * st.Wp * 4 * eb : (double)st.N * st.H * st.W * st.cpad * eb);
             by = in_bytes + (double)w.bytes + out_elems * (st.fused_pool ? 0.25 : 1.0) * (st.out_is_graph_output ? 4.0 : eb) +
                  (st.in1 >= 0 ? out_elems * eb : 0.0) + 4.0 * w.O;
-            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d%s", st.direct == 2 ? (st.fused_pool ? "conv_stem_pool" : "conv_stem_direct") : (st.direct == 3 ? "conv_rowstack" : (st.direct ? "conv_direct" : "conv_igemm")), w.C, st.H, st.W, w.O, w.KH, w.KW,
+            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d%s", st.direct == 4 ? "conv_stem_pool_nchw" : st.direct == 2 ? (st.fused_pool ? "conv_stem_pool" : "conv_stem_direct") : (st.direct == 3 ? "conv_rowstack" : (st.direct ? "conv_direct" : "conv_igemm")), w.C, st.H, st.W, w.O, w.KH, w.KW,
                      p.stride, st.in1 >= 0 ? " +res" : "", st.relu ? " +relu" : "", p.BNI, p.BH, p.BW, st.cfg.bn,
                      st.cfg.ctas == 2 ? " pair" : (st.weight2 >= 0 ? " +1x1 second output" : (st.cfg.mt == 2 ? " x2 tiles" : "")));
             break;

@@ -3,6 +3,18 @@
 `CompiledGraph` plays the role of the reference's `CompiledModule` for one Relay function
 (src/api/compiler.cc:149-168): `run(input)` launches the graph with the packed argument list
 inputs ++ constants (lowering order) ++ output and returns the output tensor.
+
+Precisions and what they cost in accuracy, measured on ResNet-18 with the benchmark's synthetic weights (logits of
+magnitude ~300) against the reference's fp32 arithmetic, worst element of the logits:
+
+    "fp32"    CUDA cores in the reference's operation order            bit-identical
+    "tf32x3"  three tf32 tensor-core passes per contraction            8e-2 absolute, 2.6e-4 of the logit scale
+    "tf32"    one pass, operands rounded to tf32                       1.7e-1 absolute, 5.2e-4 of the logit scale
+    "bf16"    bf16 activations and weights, fp32 accumulate            1.4 absolute, 4.2e-3 of the logit scale
+
+"tf32x3" removes the operand rounding (a single layer then agrees to ~2e-5), but not the rounding inside the tensor
+core's own fp32 accumulation, which truncates as it aligns the partial products of a long reduction; over twenty
+layers that is what remains, so only "fp32" reproduces the reference to the last bits.
 """
 import ctypes
 

@@ -5,9 +5,12 @@
   config 5  int8 convolution sweep over the 11 distinct ResNet-18 shapes at N=256, requantize + ReLU
   config t  transpose / cast / softmax / reduce_mean / matmul on the operator ABI (the formats either side of the path)
 
-    python -m hdkx_aicompiler_b200.microbench [--config 1|2|5|t|all] [--iters 20]
+    python microbench.py [--config 1|2|3|5|t|all] [--iters 20]
 
-Prints one JSON line per measured kernel: CUDA-event time (L2 flushed between iterations by writing a
+  config 3  ResNet-18 fp32/tf32 at batch 32 through the plan executor (tf32, tf32x3 and the bit-exact fp32 mode)
+
+bench.py calls config1_plan / config2 / config3 of this file after the headline timing and puts their figures into its
+JSON line (`hbm_kernels`, `config1`, `config3`). Prints one JSON line per measured kernel: CUDA-event time (L2 flushed between iterations by writing a
 256 MB buffer), achieved GB/s or TOP/s and the fraction of the measured peak in MEASURED_PEAKS.json
 (copy bandwidth / bf16 GEMM; int8 is reported against 2x the bf16 figure, the nominal ratio).
 Inputs are synthetic with the configurations' shapes and value distributions.
@@ -16,12 +19,16 @@ import argparse
 import json
 import os
 
+import sys
+
 import numpy as np
 import torch
 
-from . import ops, resnet18
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+from hdkx_aicompiler_b200 import ops, resnet18  # noqa: E402
 
 
 def peaks():
@@ -68,8 +75,14 @@ def timeit_rotating(fns, iters, flush):
     return float(np.median(ts))
 
 
+QUIET = False
+
+
 def emit(**kw):
-    print(json.dumps(kw), flush=True)
+    """One JSON line per measurement (unless a caller collects the returned dicts itself)."""
+    if not QUIET:
+        print(json.dumps(kw), flush=True)
+    return kw
 
 
 def config1(iters, flush, hbm, tf, src):
@@ -85,9 +98,19 @@ def config1(iters, flush, hbm, tf, src):
              tflops=flops / ms / 1e9, frac_of_bf16_peak=flops / ms / 1e9 / tf, peak_source=src)
 
 
-    # the same layer inside a plan: operands resident in the kernels' layout, one CUDA-graph replay per call
-    # (input conversion, the row-stacked tensor-core kernel with fused bias + ReLU, conversion of the result back)
-    from . import plan, relay as R
+    return config1_plan(iters, flush, hbm, tf, src)
+
+
+def config1_plan(iters, flush, hbm, tf, src):
+    """Config 1 inside a plan: operands resident in the kernels' layout, one CUDA-graph replay per call (input conversion,
+    the row-stacked tensor-core kernel with fused bias + ReLU, conversion of the result back)."""
+    from hdkx_aicompiler_b200 import plan, relay as R
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.empty(1, 64, 56, 56, device="cuda").uniform_(-1, 1, generator=g)
+    w = torch.empty(64, 64, 3, 3, device="cuda").normal_(0, (2 / 576) ** 0.5, generator=g)
+    b = torch.empty(64, device="cuda").normal_(0, 0.01, generator=g)
+    out = torch.empty(1, 64, 56, 56, device="cuda")
+    flops = 2 * 64 * 56 * 56 * 64 * 9
     xv = R.Var("input", (1, 64, 56, 56))
     func = R.Function([xv], R.Call("nn_relu", [R.Call("nn_conv2d", [xv, R.Constant(w), R.Constant(b)],
                                                         R.Conv2DAttrs((1, 1), (1, 1, 1, 1), (1, 1), 1))]))
@@ -97,8 +120,8 @@ def config1(iters, flush, hbm, tf, src):
         ms = timeit(lambda: g.run(x, out=out), iters, flush)
         _, per = g.run_timed(x, out=out)
     names = [i[0].split()[0] for i in g.launch_info()]
-    emit(config=1, kernel="plan bf16, CUDA-graph replay: " + " + ".join(names), ms=ms, tflops=flops / ms / 1e9,
-         frac_of_bf16_peak=flops / ms / 1e9 / tf, launch_ms=dict(zip(names, [round(v, 4) for v in per])), peak_source=src)
+    return emit(config=1, kernel="plan bf16, CUDA-graph replay: " + " + ".join(names), ms=ms, tflops=flops / ms / 1e9,
+                frac_of_bf16_peak=flops / ms / 1e9 / tf, launch_ms=dict(zip(names, [round(v, 4) for v in per])), peak_source=src)
 
 
 def config2(iters, flush, hbm, tf, src):
@@ -118,10 +141,11 @@ def config2(iters, flush, hbm, tf, src):
         src_t = torch.empty(n, dtype=torch.float32, device="cuda").normal_()
         dst_t = torch.empty_like(src_t)
         cases.append((f"reference: copy_ of {nbytes / 2e6:.1f} MB (same bytes read + written)", nbytes, lambda d=dst_t, s_=src_t: d.copy_(s_)))
+    results = []
     for name, nbytes, fn in cases:
         ms = timeit(fn, iters, flush)
-        emit(config=2, kernel=name, ms=ms, algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, frac_of_hbm_peak=nbytes / ms / 1e6 / hbm,
-             peak_source=src)
+        results.append(emit(config=2, kernel=name, form="one launch between two events", ms=ms, algorithmic_bytes=nbytes,
+                            gbs=nbytes / ms / 1e6, frac_of_hbm_peak=nbytes / ms / 1e6 / hbm, peak_source=src))
     # the same four kernels, eight launches back to back on eight different input sets (8 x 51-154 MB, L2 is 126 MB)
     sets = 8
     xs = [torch.empty_like(x).uniform_(-1, 1, generator=g) for _ in range(sets)]
@@ -129,7 +153,7 @@ def config2(iters, flush, hbm, tf, src):
     os_ = [torch.empty_like(res) for _ in range(sets)]
     # straight through the C ABI with descriptors and argument lists built once: the Python wrappers in ops.py cost
     # 10-25 us per call, more than these kernels run
-    from . import _lib
+    from hdkx_aicompiler_b200 import _lib
     lib = _lib.load()
     stream = torch.cuda.current_stream().cuda_stream
     pool_desc = _lib.Pool2dDesc(32, 64, 112, 112, 3, 3, 2, 2, 1, 1, 1, 1, 0)
@@ -152,8 +176,29 @@ def config2(iters, flush, hbm, tf, src):
     ]
     for name, nbytes, fns in rotating:
         ms = timeit_rotating(fns, iters, flush)
-        emit(config=2, kernel=name + f" [{sets} launches back to back, rotating buffers]", ms=ms, algorithmic_bytes=nbytes,
-             gbs=nbytes / ms / 1e6, frac_of_hbm_peak=nbytes / ms / 1e6 / hbm, peak_source=src)
+        results.append(emit(config=2, kernel=name, form=f"{sets} launches back to back on rotating buffers, per launch", ms=ms,
+                            algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, frac_of_hbm_peak=nbytes / ms / 1e6 / hbm, peak_source=src))
+    return results
+
+
+def config3(iters, flush, hbm, tf, src):
+    """ResNet-18 at batch 32 (the fp32/tf32 configuration): device-timed CUDA-graph replays per precision."""
+    from hdkx_aicompiler_b200 import plan
+    N = 32
+    weights = resnet18.make_weights(seed=0)
+    x = torch.empty(N, 3, 224, 224, device="cuda").normal_(0, 1, generator=torch.Generator(device="cuda").manual_seed(3))
+    results = []
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for prec, reps in (("tf32", max(3, iters)), ("tf32x3", max(3, iters)), ("fp32", 2)):
+            g = plan.CompiledGraph(resnet18.build(N, weights, to_constant=lambda a: torch.from_numpy(a).cuda()), prec, cuda_graph=True)
+            out = torch.empty(g.out_shape, device="cuda")
+            ms = timeit(lambda: g.run(x, out=out), reps, flush)
+            ops.device_status()
+            results.append(emit(config=3, kernel=f"resnet18 batch {N} plan {prec}, CUDA-graph replay", ms=ms, img_per_s=N / ms * 1e3,
+                                launches=g.num_launches, tflops=3.628147e9 * N / ms / 1e9))
+            del g
+    return results
 
 
 def config5(iters, flush, hbm, tf, src):
@@ -230,13 +275,13 @@ def config_transform(iters, flush, hbm, tf, src):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="all")
+    ap.add_argument("--config", default="all", help="1, 2, 3, 5, t or all")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     assert torch.cuda.is_available(), "needs a GPU"
     hbm, tf, src = peaks()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
-    for c, fn in (("1", config1), ("2", config2), ("5", config5), ("t", config_transform)):
+    for c, fn in (("1", config1), ("2", config2), ("3", config3), ("5", config5), ("t", config_transform)):
         if args.config in ("all", c):
             fn(args.iters, flush, hbm, tf, src)
 
