@@ -66,6 +66,7 @@ struct Node {
     kxc_b200_conv2d_attrs conv{};
     kxc_b200_pool2d_attrs pool{};
     kxc_b200_gemm_attrs gemm{};
+    int flatten_axis = 1;
     bool fused_into_other = false;
 };
 
@@ -241,6 +242,12 @@ int32_t infer_shapes(kxc_b200_plan* pl) {
             out->shape = {in[0]->shape[0], in[0]->shape[1], 1, 1};
         } else if (op == "nn_flatten") {
             if (in.size() != 1 || in[0]->shape.empty()) return fail(KXC_B200_ERR_INVALID, "nn_flatten expects exactly 1 input");
+            {   // FlattenInferType (src/relay/type_infer.cc:446-450) honours the axis; only axis 1 is implemented here
+                const int rank = (int)in[0]->shape.size();
+                const int axis = n.flatten_axis < 0 ? n.flatten_axis + rank : n.flatten_axis;
+                if (axis != 1)
+                    return fail(KXC_B200_ERR_UNSUPPORTED, "plan: nn_flatten with axis %d (only axis 1 is supported inside a plan)", n.flatten_axis);
+            }
             int64_t rest = 1;
             for (size_t i = 1; i < in[0]->shape.size(); ++i) rest *= in[0]->shape[i];
             out->shape = {in[0]->shape[0], rest};
@@ -394,6 +401,8 @@ extern "C" int32_t kxc_b200_plan_add_kernel(kxc_b200_plan* plan, const char* op_
     } else if (n.op == "nn_gemm") {
         if (!attrs) return fail(KXC_B200_ERR_INVALID, "nn_gemm expects GemmAttrs");
         n.gemm = *static_cast<const kxc_b200_gemm_attrs*>(attrs);
+    } else if (n.op == "nn_flatten") {
+        if (attrs) n.flatten_axis = static_cast<const kxc_b200_flatten_attrs*>(attrs)->axis;
     }
     for (int id : n.in)
         if (!plan->find(id)) return fail(KXC_B200_ERR_INVALID, "plan: node '%s' reads undefined value %d", op_name, id);

@@ -44,9 +44,12 @@ def load(text):
     for key in ("num_values", "output_value", "nodes", "input_value_ids", "constant_value_ids", "value_info"):
         if key not in plan:
             raise ValueError(f"ExecutionPlan JSON is missing '{key}'")
+    # the reference's writer emits `null` for an undefined node and its reader skips such entries
+    # (src/base/execution_plan.cc:689-692): they are dropped here
+    plan["nodes"] = [n for n in plan["nodes"] if n is not None]
     for i, node in enumerate(plan["nodes"]):
-        if node.get("kind") not in ("kernel", "comm", "barrier"):
-            raise ValueError(f"ExecutionPlan JSON node {i} has unknown kind: {node.get('kind')}")
+        if not isinstance(node, dict) or node.get("kind") not in ("kernel", "comm", "barrier"):
+            raise ValueError(f"ExecutionPlan JSON node {i} has unknown kind: {node.get('kind') if isinstance(node, dict) else node}")
     return plan
 
 
@@ -138,6 +141,16 @@ def _run_kernel(op, a, args, precision):
         return ops.softmax(args[0], a.axis if a is not None else -1)
     if op == "matmul":
         return ops.matmul(args[0], args[1], precision=precision)
+    if op == "nn_avg_pool2d":
+        return ops.nn_avg_pool2d(args[0], tuple(a.pool_size[:2]), tuple(a.strides[:2]), tuple(a.padding), a.ceil_mode)
+    if op == "reduce_mean":
+        return ops.reduce_mean(args[0], tuple(a.axis), bool(a.keepdims))
+    if op == "transpose":
+        return ops.transpose(args[0], tuple(a.axes) if a is not None and a.axes else None)
+    if op == "reshape":
+        return ops.reshape(args[0], tuple(a.newshape), bool(a.allowzero))
+    if op == "cast":
+        return ops.cast(args[0], a.dtype)
     raise NotImplementedError(f"no kernel for op '{op}'")
 
 

@@ -35,7 +35,7 @@ def _attrs_to_json(call):
         return {"strides": list(a.strides), "pads": list(a.padding), "dilations": list(a.dilation),
                 "pool_size": list(a.pool_size), "layout": a.layout, "ceil_mode": bool(a.ceil_mode)}
     if call.op == "nn_flatten":
-        return {"axis": 1}
+        return {"axis": int(a.axis) if a is not None else 1}
     if call.op == "nn_gemm":
         return {"alpha": float(a.alpha), "beta": float(a.beta), "transA": int(a.transA), "transB": int(a.transB)}
     return {}
@@ -49,6 +49,8 @@ def _attrs_from_json(op, d):
                                 d.get("layout", "NCHW"), bool(d["ceil_mode"]))
     if op == "nn_gemm":
         return R.GemmAttrs(float(d["alpha"]), float(d["beta"]), int(d["transA"]), int(d["transB"]))
+    if op == "nn_flatten":  # the reference honours the axis (src/relay/op/tensor/transform.cc:145-165, type_infer.cc:446-450)
+        return R.FlattenAttrs(int(d.get("axis", 1)))
     return None
 
 

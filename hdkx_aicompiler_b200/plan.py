@@ -42,6 +42,10 @@ class SoftmaxAttrsC(ctypes.Structure):
     _fields_ = [("axis", i32)]
 
 
+class FlattenAttrsC(ctypes.Structure):
+    _fields_ = [("axis", i32)]
+
+
 _PLAN_SYMBOLS = {
     "kxc_b200_plan_create": (i32, [i32, ctypes.POINTER(vp)]),
     "kxc_b200_plan_destroy": (i32, [vp]),
@@ -82,6 +86,8 @@ def _attrs_c(call):
         return GemmAttrsC(a.alpha, a.beta, a.transA, a.transB)
     if call.op == "softmax":
         return SoftmaxAttrsC(int(a.axis) if a is not None else -1)
+    if call.op == "nn_flatten" and a is not None:
+        return FlattenAttrsC(int(a.axis))
     return None
 
 

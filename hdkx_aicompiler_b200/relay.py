@@ -64,6 +64,33 @@ class SoftmaxAttrs:
     axis: int = -1
 
 
+@dataclass
+class FlattenAttrs:
+    axis: int = 1  # FlattenAttrsNode (include/relay/op.h:353-358): dimensions before `axis` form the rows
+
+
+@dataclass
+class ReduceMeanAttrs:
+    axis: Sequence[int] = ()
+    keepdims: bool = True
+
+
+@dataclass
+class TransposeAttrs:
+    axes: Sequence[int] = ()  # empty = reverse the dimensions
+
+
+@dataclass
+class ReshapeAttrs:
+    newshape: Sequence[int] = ()
+    allowzero: bool = False
+
+
+@dataclass
+class CastAttrs:
+    dtype: str = "float32"  # the reference's dtype name
+
+
 @dataclass(eq=False)
 class Call(Expr):
     op: str  # Relay op name: "nn_conv2d", "nn_relu", "add", ...

@@ -62,6 +62,14 @@ typedef struct kxc_b200_softmax_attrs {
     int32_t axis; /* negative values count from the end */
 } kxc_b200_softmax_attrs;
 
+/* FlattenAttrsNode (include/relay/op.h:353-358), optional for "nn_flatten" (NULL = axis 1). The reference honours the
+ * axis (src/relay/op/tensor/transform.cc:145-165, src/relay/type_infer.cc:446-450); a plan flattens at axis 1 only
+ * (negative values count from the end) and refuses anything else at finalize with KXC_B200_ERR_UNSUPPORTED rather than
+ * produce another shape than the reference would. */
+typedef struct kxc_b200_flatten_attrs {
+    int32_t axis;
+} kxc_b200_flatten_attrs;
+
 /* precision: KXC_B200_PREC_BF16 (bf16 activations/weights, fp32 accumulate), KXC_B200_PREC_TF32 (fp32
  * activations, tf32-rounded operands, fp32 accumulate), KXC_B200_PREC_TF32X3 (full fp32 activations; every
  * convolution / dense node splits both operands into tf32 high and low parts and runs three tensor-core passes,

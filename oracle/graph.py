@@ -125,7 +125,12 @@ def run(func, inputs, operand_round=None, workers=1, backend=None):
             y = be.global_avg_pool2d(val(c.args[0]))
         elif c.op == "nn_flatten":
             v = val(c.args[0])
-            y = v.reshape(v.shape[0], -1)
+            axis = a.axis if a is not None else 1  # FlattenCompute (src/relay/op/tensor/transform.cc:140-182)
+            axis = axis + v.ndim if axis < 0 else axis
+            rows = 1
+            for d in v.shape[:axis]:
+                rows *= d
+            y = v.reshape(rows, -1)
         elif c.op == "nn_dense":
             y = be.dense(val(c.args[0], True), val(c.args[1], True))
         elif c.op == "nn_gemm":

@@ -64,6 +64,8 @@ def to_relay(desc, params, to_constant=None):
                                      "NCHW", bool(at["ceil_mode"]))
         elif op == "nn_gemm":
             attrs = R.GemmAttrs(at["alpha"], at["beta"], at["transA"], at["transB"])
+        elif op == "nn_flatten":
+            attrs = R.FlattenAttrs(int(at.get("axis", 1)))
         nodes[n["id"]] = R.Call(op, [ref(a) for a in n["args"]], attrs)
         shape = tuple(n["shape"])
     body = ref(desc["result"])

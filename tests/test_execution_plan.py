@@ -93,3 +93,47 @@ def test_execute_plan_on_gpu():
     g = kplan.CompiledGraph(xp.to_function(p, attrs, consts), "fp32")
     assert_bit_exact(g.run(x).cpu().numpy(), io["output"], "ExecutionPlan as one compiled graph, fp32")
     assert ops.device_status() == 0
+
+
+def test_null_nodes_are_skipped_like_the_reference_does():
+    """The reference's writer emits `null` for an undefined node and its reader skips it (src/base/execution_plan.cc:689-692)."""
+    text = open(os.path.join(GOLDEN, "import_block_plan.json")).read()
+    plan = json.loads(text)
+    n = len(plan["nodes"])
+    plan["nodes"].insert(1, None)
+    plan["nodes"].append(None)
+    loaded = xp.load(json.dumps(plan))
+    assert len(loaded["nodes"]) == n and all(node is not None for node in loaded["nodes"])
+    assert len(xp.kernel_nodes(loaded)) == len(xp.kernel_nodes(xp.load(text)))
+    assert xp.bind_kernel_symbols(loaded) == xp.bind_kernel_symbols(xp.load(text))
+
+
+@pytest.mark.gpu
+def test_every_bound_operator_executes():
+    """Every operator bind_kernel_symbols accepts is one execute_kernels can run: the five outside the ResNet path too."""
+    import torch
+    from conftest import assert_bit_exact
+    from hdkx_aicompiler_b200 import relay as R
+    from oracle import port
+    rng = np.random.default_rng(9)
+    x = rng.normal(0, 1, (2, 4, 6, 6)).astype(np.float32)
+    nodes = [
+        ("nn_avg_pool2d", R.MaxPool2DAttrs((2, 2), (0, 0, 0, 0), (1, 1), (2, 2), "NCHW", False)),
+        ("reduce_mean", R.ReduceMeanAttrs((2, 3), True)),
+        ("transpose", R.TransposeAttrs((1, 0, 2, 3))),
+        ("reshape", R.ReshapeAttrs((4, 2), False)),
+        ("cast", R.CastAttrs("int32")),
+    ]
+    plan = {"schema_version": 1, "num_values": 6, "output_value": 5, "input_value_ids": [0], "constant_value_ids": [],
+            "value_info": [{"value_id": 0, "shape": list(x.shape), "dtype": "float32"}],
+            "nodes": [{"kind": "kernel", "op_name": op, "kernel_symbol": "", "input_values": [i], "output_values": [i + 1], "worker_set": []}
+                      for i, (op, _) in enumerate(nodes)]}
+    bound = xp.bind_kernel_symbols(xp.load(json.dumps(plan)))
+    assert [n["kernel_symbol"] for n in bound["nodes"]] == ["kxc_b200_nn_avg_pool2d", "kxc_b200_reduce_mean", "kxc_b200_transpose",
+                                                            "kxc_b200_reshape", "kxc_b200_cast"]
+    got = xp.execute_kernels(bound, [a for _, a in nodes], [], [torch.from_numpy(x).cuda()]).cpu().numpy()
+    exp = port.avg_pool2d(x, (2, 2), (2, 2), (0, 0, 0, 0))
+    exp = port.reduce_mean(exp, (2, 3), True)
+    exp = np.ascontiguousarray(exp.transpose(1, 0, 2, 3)).reshape(4, 2).astype(np.int32)
+    assert got.dtype == np.int32 and got.shape == (4, 2)
+    assert np.array_equal(got, exp)

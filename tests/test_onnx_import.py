@@ -121,3 +121,45 @@ def test_committed_fixture():
     assert shape == tuple(ref["output"].shape)
     got = ograph.run(func, [ref["input"]])
     assert np.array_equal(got.view(np.uint32), ref["output"].view(np.uint32))
+
+
+@needs_ref
+def test_flatten_axis_is_carried_and_agrees_with_the_reference(tmp_path, rng):
+    """nn_flatten's axis survives the loader (the reference honours it: src/relay/op/tensor/transform.cc:145-165,
+    src/relay/type_infer.cc:446-450): for axis 2 both readers see the attribute and the reference's inferred result shape is
+    the one the CPU checker produces."""
+    w = rng.normal(0, 0.2, (4, 3, 3, 3)).astype(f32)
+    x = R.Var("input", (2, 3, 8, 8))
+    y = R.Call("nn_relu", [R.Call("nn_conv2d", [x, R.Constant(w, "w")], R.Conv2DAttrs((1, 1), (1, 1, 1, 1), (1, 1), 1))])
+    func = R.Function([x], R.Call("nn_flatten", [y], R.FlattenAttrs(2)))
+    j, p = str(tmp_path / "f.json"), str(tmp_path / "f.bin")
+    onnx_import.save_spec(func, (8, 64), j, p)
+    own, own_shape = onnx_import.load_spec(j, p)
+    assert R.post_order_calls(own)[-1].attrs == R.FlattenAttrs(2)
+    desc = oimp.describe(j, p)                       # the reference's importer + InferTypePass
+    ref_func, ref_shape = oimp.to_relay(desc, oimp.read_params(j, p))
+    assert ref_shape == own_shape == (8, 64)
+    assert signature(ref_func) == signature(own)
+    xin = rng.normal(0, 1, (2, 3, 8, 8)).astype(f32)
+    assert ograph.run(own, [xin]).shape == (8, 64)
+
+
+@pytest.mark.gpu
+def test_plan_refuses_flatten_at_another_axis(rng):
+    """A plan flattens at axis 1 (negative values normalised) and refuses anything else instead of silently producing a
+    shape the reference would not."""
+    import torch
+    from hdkx_aicompiler_b200 import KxcError, plan
+    w = torch.from_numpy(rng.normal(0, 0.2, (16, 16, 3, 3)).astype(f32)).cuda()
+
+    def build(axis):
+        x = R.Var("input", (2, 16, 8, 8))
+        y = R.Call("nn_relu", [R.Call("nn_conv2d", [x, R.Constant(w, "w")], R.Conv2DAttrs((1, 1), (1, 1, 1, 1), (1, 1), 1))])
+        y = R.Call("nn_global_avg_pool2d", [y])
+        return R.Function([x], R.Call("nn_relu", [R.Call("nn_flatten", [y], R.FlattenAttrs(axis))]))
+
+    for ok_axis in (1, -3):
+        g = plan.CompiledGraph(build(ok_axis), "fp32")
+        assert g.out_shape == (2, 16)
+    with pytest.raises(KxcError, match="axis"):
+        plan.CompiledGraph(build(2), "fp32")
