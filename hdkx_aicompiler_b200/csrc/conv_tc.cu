@@ -71,8 +71,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
     // two accumulator buffers (the epilogue of one work item overlaps the next item's main loop) where TMEM's 512
     // columns allow it, else one
     constexpr int kBufs = 2 * kAccCols <= 512 ? 2 : 1;
-    constexpr uint32_t kTmemCols = kBufs * kAccCols;  // 128, 256 or 512: a power of two
-    static_assert(kTmemCols <= 512, "TMEM has 512 columns");
+    constexpr uint32_t kTmemUsed = kBufs * kAccCols;
+    constexpr uint32_t kTmemCols = kTmemUsed <= 128 ? 128u : (kTmemUsed <= 256 ? 256u : 512u);  // allocations are powers of two
+    static_assert(kTmemUsed <= 512, "TMEM has 512 columns");
     static_assert(!kDual || (!kPair && kOutMode == kOutNHWC_BF16), "the dual kernel exists for single CTAs and bf16 NHWC output");
     constexpr uint32_t kIdesc =
         make_instr_desc(kKind == MmaKind::F16 ? kFmtBF16 : (kKind == MmaKind::TF32 ? kFmtTF32 : kFmtS8),
@@ -285,7 +286,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
         const EpiParams ep = {p.bias, p.residual, p.out, p.Cout, p.relu};
         const uint32_t stage_tile = ring + (uint32_t)(kStages * G::kStageBytes) + (uint32_t)((warp - 2) * kStoreBoxBytes);
         // Residual-free launches with store maps: the warp's values go into its swizzled box and leave by TMA store
-        const bool boxed = fast && p.store_box && !has_res && (BN >= 128);
+        // (boxes are 64 channels wide: a warp needs an even number of 32-column chunks, which the 192-wide tile lacks)
+        const bool boxed = fast && p.store_box && !has_res && (BN >= 128) && (kChunksPerWarp % 2 == 0);
         pdl_wait();  // residual reads and output writes must not overtake earlier kernels
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -508,6 +510,9 @@ int32_t launch_by_bn(const TcConfig& cfg, const TcParams& p, cudaStream_t s) {
     switch (cfg.bn) {
         case 64: return launch_by_out<kKind, KB_BYTES, 64, 1>(cfg, p, s);
         case 128: return launch_by_out<kKind, KB_BYTES, 128, 1>(cfg, p, s);
+        case 192:
+            if constexpr (KB_BYTES == 128) return launch_by_out<kKind, KB_BYTES, 192, 1>(cfg, p, s);
+            return fail(KXC_B200_ERR_INVALID, "tensor-core conv: the 192-wide tile exists for 128-byte K blocks only");
         case 256: return launch_by_out<kKind, KB_BYTES, 256, 1>(cfg, p, s);
         default: return fail(KXC_B200_ERR_INVALID, "tensor-core conv: unsupported N tile %d", cfg.bn);
     }
@@ -619,7 +624,7 @@ int32_t tc_bind_store(TcParams* p, const TcConfig& cfg) {
         return !(e != nullptr && e[0] == '0');
     }();
     auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
-    if (!enabled || cfg.dtype != kTcBF16 || cfg.out_mode != kOutNHWC_BF16 || cfg.bn < 128 || p->out == nullptr || (p->Cout & 63) != 0 ||
+    if (!enabled || cfg.dtype != kTcBF16 || cfg.out_mode != kOutNHWC_BF16 || cfg.bn < 128 || cfg.bn == 192 || p->out == nullptr || (p->Cout & 63) != 0 ||
         !pow2(p->BW) || !pow2(p->BH) || !pow2(p->BNI) || p->BW * p->BH * p->BNI != 128 || p->BW > 32)
         return KXC_B200_OK;
     // a warp's 32 consecutive tile rows as a box of the output tensor
@@ -706,7 +711,29 @@ int32_t tc_setup_conv(TcParams* p, TcConfig* cfg, TcDType dtype, TcOutMode out_m
     // Measured: pairs gain 5-7 % with the 256-wide tile and lose 3-10 % with the 128-wide one (the pair's MMA is
     // no faster there and the handshakes cross SMs), so only the 256-wide tile uses them. "2" forces them for 128 too.
     static const bool pair_all = [] { const char* e = getenv("KXC_B200_CTA_PAIR"); return e != nullptr && e[0] == '2'; }();
-    const int ctas = (pair_enabled && bn >= (pair_all ? 128 : 256) && kb_bytes == 128 && m_tiles >= 2) ? 2 : 1;
+    int ctas = (pair_enabled && bn >= (pair_all ? 128 : 256) && kb_bytes == 128 && m_tiles >= 2) ? 2 : 1;
+    // Launches with few tiles (small per-GPU batches in the deep layers): the 256-wide tile leaves SMs idle, e.g. 98 tiles
+    // (49-50 pairs) on 148 SMs. 512 channels in 192-wide tiles on 49 pixel tiles are 147 CTAs, one wave, and an
+    // M = 128, K = 16 instruction takes ~99 cycles at N = 192 against ~131 at N = 256 (measured). The narrower tile is
+    // taken when the modelled makespan (waves x cycles per instruction) gains 10 %: layer 4 at 128 / 256 images per GPU
+    // 37 -> 35 / 61 -> 57 us. (A 128-wide tile was measured slower there, 38 -> 45 us: without the pair's halved weight
+    // fetch each CTA's operand stream from L2 becomes the limit.) KXC_B200_TILE_MODEL=0 keeps the widest tile.
+    static const bool tile_model = [] {
+        const char* e = getenv("KXC_B200_TILE_MODEL");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    if (tile_model && bn == 256 && kb_bytes == 128 && (dtype == kTcBF16 || dtype == kTcS8)) {
+        auto waves = [](long long items, long long slots) { return (items + slots - 1) / slots; };
+        const long long span256 = ctas == 2 ? waves(((m_tiles + 1) / 2) * ((Cout + 255) / 256), kNumSMs / 2) * 131
+                                            : waves(m_tiles * ((Cout + 255) / 256), kNumSMs) * 131;
+        const long long span192 = waves(m_tiles * ((Cout + 191) / 192), kNumSMs) * 99;
+        int pick = 256;
+        if (span192 * 10 <= span256 * 9) pick = 192;
+        if (pick != 256) {
+            bn = pick;
+            ctas = 1;
+        }
+    }
     cfg->dtype = dtype; cfg->kb_bytes = kb_bytes; cfg->bn = bn; cfg->out_mode = out_mode; cfg->ctas = ctas;
     // Two pixel tiles per work item for the 128-wide bf16 tile: measured 0.285/0.277/0.284 -> 0.231/0.221/0.234 ms on the
     // 128->128 layers (the tensor core then sits on its operand-fetch bound: 8 KB per instruction at ~64 B/clk). With the
