@@ -25,33 +25,68 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
     const size_t pix = ((size_t)n * p.OH + oh) * p.OW + ow;
 
     if constexpr (kOutMode == kOutNHWC_S8 || kOutMode == kOutNCHW_S8) {
-        int8_t q[32];
+        uint32_t qw[8];  // the chunk's 32 int8 results, four per word (bytes in channel order)
+        bool done = false;
+        if (nch == 32 && p.vec_ok) {
+            // Per-channel constants as 16-byte loads (the same addresses in every lane). With 2 <= shift <= 31 the
+            // rounding term 2^(S-1), S = 31 + shift >= 33, is a multiple of 2^32, so only the high word of the 64-bit
+            // product matters: floor((t + 2^(S-1)) / 2^S) = (hi(t) + 2^(shift-2)) >> (shift-1) exactly, because the low
+            // word adds a fraction < 1 to an integer that is then floored by at least one more bit.
+            // (out-of-range shifts are detected on the way; the chunk is then redone by the general formula)
+            uint32_t in_range = 1;
+            const int32_t lo = p.relu ? 0 : -128;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const int c = c0 + j;
-            if (j < nch) {
-                const int32_t acc = (int32_t)v[j] + __ldg(p.bias_i32 + c);
-                q[j] = requantize_s8(acc, __ldg(p.multiplier + c), __ldg(p.shift + c), p.relu);
-            } else {
-                q[j] = 0;
+            for (int j = 0; j < 32; j += 4) {
+                const int4 b = __ldg(reinterpret_cast<const int4*>(p.bias_i32 + c0 + j));
+                const int4 m = __ldg(reinterpret_cast<const int4*>(p.multiplier + c0 + j));
+                const int4 t = __ldg(reinterpret_cast<const int4*>(p.shift + c0 + j));
+                const int32_t bb[4] = {b.x, b.y, b.z, b.w};
+                const int32_t mm[4] = {m.x, m.y, m.z, m.w};
+                const int32_t ss[4] = {t.x, t.y, t.z, t.w};
+                uint32_t rr[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    in_range &= (uint32_t)((uint32_t)(ss[k] - 2) <= 29u);
+                    const int32_t acc = (int32_t)((uint32_t)v[j + k] + (uint32_t)bb[k]);
+                    int32_t r = (__mulhi(acc, mm[k]) + (int32_t)(1u << ((ss[k] - 2) & 31))) >> ((ss[k] - 1) & 31);
+                    r = r < lo ? lo : r;
+                    r = r > 127 ? 127 : r;
+                    rr[k] = (uint32_t)r;
+                }
+                qw[j >> 2] = __byte_perm(__byte_perm(rr[0], rr[1], 0x0040), __byte_perm(rr[2], rr[3], 0x0040), 0x5410);
+            }
+            done = in_range != 0;
+        }
+        if (!done) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) qw[j] = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int c = c0 + j;
+                if (j < nch) {
+                    const int32_t acc = (int32_t)((uint32_t)v[j] + (uint32_t)__ldg(p.bias_i32 + c));
+                    const int8_t r = requantize_s8(acc, __ldg(p.multiplier + c), __ldg(p.shift + c), p.relu);
+                    qw[j >> 2] |= (uint32_t)(uint8_t)r << (8 * (j & 3));
+                }
             }
         }
         int8_t* out = static_cast<int8_t*>(p.out);
         if constexpr (kOutMode == kOutNHWC_S8) {
             int8_t* dst = out + pix * p.Cout + c0;
             if (nch == 32 && (p.Cout & 15) == 0 && p.vec_ok) {
-                const uint4* src = reinterpret_cast<const uint4*>(q);
-                reinterpret_cast<uint4*>(dst)[0] = src[0];
-                reinterpret_cast<uint4*>(dst)[1] = src[1];
+                reinterpret_cast<uint4*>(dst)[0] = make_uint4(qw[0], qw[1], qw[2], qw[3]);
+                reinterpret_cast<uint4*>(dst)[1] = make_uint4(qw[4], qw[5], qw[6], qw[7]);
             } else {
-                for (int j = 0; j < nch; ++j) dst[j] = q[j];
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < nch) dst[j] = (int8_t)(qw[j >> 2] >> (8 * (j & 3)));
             }
         } else {
             const size_t plane = (size_t)p.OH * p.OW;
             int8_t* dst = out + ((size_t)n * p.Cout + c0) * plane + (size_t)oh * p.OW + ow;
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-                if (j < nch) dst[(size_t)j * plane] = q[j];
+                if (j < nch) dst[(size_t)j * plane] = (int8_t)(qw[j >> 2] >> (8 * (j & 3)));
         }
         return;
     } else {

@@ -51,9 +51,13 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
                  : "memory");
 }
 
+// kKind = F16: packed bf16 pixels [4 channels], bf16 NHWC output. kKind = I8: packed int8 pixels [8 channels] (the same
+// 8 bytes per pixel, so every address below is unchanged; one instruction covers K = 32 bytes either way), int32
+// accumulators, fixed-point requantize to int8 in the output layout kOutMode.
+template <MmaKind kKind, int kOutMode>
 __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __grid_constant__ TcParams p) {
     constexpr uint32_t kTmemCols = 2 * kBN;
-    constexpr uint32_t kIdesc = make_instr_desc(kFmtBF16, kAccF32, kBN);
+    constexpr uint32_t kIdesc = kKind == MmaKind::I8 ? make_instr_desc(kFmtS8, kAccS32, kBN) : make_instr_desc(kFmtBF16, kAccF32, kBN);
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_w;
@@ -150,8 +154,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __g
                     uint32_t a_lo = desc_lo(strip_base + (uint32_t)(2 * rr * row_bytes), 16);
                     uint32_t b_lo = desc_lo(w_smem, kBN * 16);
                     for (int kh = 0; kh < KH; ++kh) {
-                        umma_f16_split(d_tmem, a_lo, ab_hi, b_lo, ab_hi, kIdesc, kh != 0 ? 1u : 0u);
-                        umma_f16_split(d_tmem, a_lo + 2u, ab_hi, b_lo + (uint32_t)((2 * kBN * 16) >> 4), ab_hi, kIdesc, 1u);
+                        if constexpr (kKind == MmaKind::I8) {
+                            umma_i8_split(d_tmem, a_lo, ab_hi, b_lo, ab_hi, kIdesc, kh != 0 ? 1u : 0u);
+                            umma_i8_split(d_tmem, a_lo + 2u, ab_hi, b_lo + (uint32_t)((2 * kBN * 16) >> 4), ab_hi, kIdesc, 1u);
+                        } else {
+                            umma_f16_split(d_tmem, a_lo, ab_hi, b_lo, ab_hi, kIdesc, kh != 0 ? 1u : 0u);
+                            umma_f16_split(d_tmem, a_lo + 2u, ab_hi, b_lo + (uint32_t)((2 * kBN * 16) >> 4), ab_hi, kIdesc, 1u);
+                        }
                         a_lo += (uint32_t)(row_bytes >> 4);
                         b_lo += (uint32_t)((4 * kBN * 16) >> 4);
                     }
@@ -189,7 +198,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __g
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
-                if (col_ok) {
+                if constexpr (kKind == MmaKind::I8) {
+                    epilogue_chunk<kOutMode>(p, v, c0, col_ok, n, oh0 + rr, ow);
+                } else if (col_ok) {
                     const size_t pix = ((size_t)n * p.OH + (oh0 + rr)) * p.OW + ow;
                     const uint4 no_res[4] = {};
                     epilogue_fast_bf16(p, v, c0, pix, no_res, false);
@@ -510,7 +521,88 @@ __global__ void stem_pack_weights_core_kernel(const float* __restrict__ w, __nv_
     }
 }
 
+// int8 stem: NCHW int8 [N,C<=8,H,W] -> packed [N][Hp][Wp][8] int8 with a zero border (8 bytes per pixel)
+// (kNhwcIn: the input is [N,H,W,C] instead of [N,C,H,W])
+template <bool kNhwcIn>
+__global__ void __launch_bounds__(256) stem_pack_s8_kernel(const int8_t* __restrict__ x, uint2* __restrict__ out, int N, int C, int H,
+                                                            int W, int Hp, int Wp, int pad_h, int pad_w) {
+    const int64_t total = (int64_t)N * Hp * Wp;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+        const int wp = (int)(i % Wp);
+        int64_t t = i / Wp;
+        const int hp = (int)(t % Hp);
+        const int n = (int)(t / Hp);
+        const int h = hp - pad_h, w = wp - pad_w;
+        uint32_t lo = 0, hi = 0;
+        if (h >= 0 && h < H && w >= 0 && w < W) {
+            for (int c = 0; c < C; ++c) {
+                const uint32_t b = kNhwcIn ? (uint8_t)__ldg(x + (((int64_t)n * H + h) * W + w) * C + c)
+                                           : (uint8_t)__ldg(x + (((int64_t)n * C + c) * H + h) * W + w);
+                if (c < 4) lo |= b << (8 * c);
+                else hi |= b << (8 * (c - 4));
+            }
+        }
+        out[i] = make_uint2(lo, hi);
+    }
+}
+
+// int8 stem weights in core-matrix order: [KH][4 k-chunks][64 cout][16 bytes]; byte e of chunk j = pixel 2j + e/8,
+// channel e%8; zero for kw >= KW or c >= C.
+// (kOhwi: the weights are [O,KH,KW,C] instead of [O,C,KH,KW])
+template <bool kOhwi>
+__global__ void stem_pack_weights_core_s8_kernel(const int8_t* __restrict__ w, int8_t* __restrict__ out, int O, int C, int KH, int KW) {
+    const int total = KH * 4 * kBN * 16;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int e = i & 15, o = (i >> 4) & (kBN - 1), j = (i >> 10) & 3, kh = i >> 12;
+        const int kw = 2 * j + (e >> 3), c = e & 7;
+        int8_t v = 0;
+        if (o < O && c < C && kw < KW) v = kOhwi ? w[((o * KH + kh) * KW + kw) * C + c] : w[((o * C + c) * KH + kh) * KW + kw];
+        out[i] = v;
+    }
+}
+
 }  // namespace
+
+bool stem_direct_s8_applicable(int C, int O, int KH, int KW, int stride, int dil, int W, int OW, int Wp) {
+    return C <= 8 && O == kBN && KH <= kMaxKH && KW <= 8 && stride == 2 && dil == 1 && W >= 8 && OW <= 128 && Wp * 8 <= kMaxRowBytes &&
+           (Wp * 8) % 16 == 0;
+}
+
+int32_t stem_direct_s8_pack(const int8_t* x, const int8_t* w, void* packed_x, void* packed_w, int N, int C, int H, int W, int O, int KH,
+                            int KW, int Hp, int Wp, int pad_h, int pad_w, bool nhwc, cudaStream_t s) {
+    const int64_t total = (int64_t)N * Hp * Wp;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > (int64_t)kNumSMs * 16) blocks = (int64_t)kNumSMs * 16;
+    const int wblocks = (KH * 4 * kBN * 16 + 255) / 256;
+    if (nhwc) {
+        stem_pack_s8_kernel<true><<<(int)blocks, 256, 0, s>>>(x, static_cast<uint2*>(packed_x), N, C, H, W, Hp, Wp, pad_h, pad_w);
+        KXC_TRY(check_launch("stem_pack_s8"));
+        stem_pack_weights_core_s8_kernel<true><<<wblocks, 256, 0, s>>>(w, static_cast<int8_t*>(packed_w), O, C, KH, KW);
+    } else {
+        stem_pack_s8_kernel<false><<<(int)blocks, 256, 0, s>>>(x, static_cast<uint2*>(packed_x), N, C, H, W, Hp, Wp, pad_h, pad_w);
+        KXC_TRY(check_launch("stem_pack_s8"));
+        stem_pack_weights_core_s8_kernel<false><<<wblocks, 256, 0, s>>>(w, static_cast<int8_t*>(packed_w), O, C, KH, KW);
+    }
+    return check_launch("stem_pack_weights_core_s8");
+}
+
+template <MmaKind kKind, int kOutMode>
+static int32_t stem_direct_launch_as(const TcParams& p, cudaStream_t stream) {
+    static PerDeviceOnce smem_once;
+    auto kernel = conv_stem_direct_kernel<kKind, kOutMode>;
+    KXC_TRY(smem_opt_in(smem_once, kernel, kSmemBytes));
+    const long long strips = (long long)((p.OH + kStripRows - 1) / kStripRows) * p.N;
+    if (strips <= 0) return KXC_B200_OK;
+    const int grid = (int)(strips < kNumSMs ? strips : kNumSMs);
+    KXC_CUDA_TRY(launch_kernel(kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, /*pdl=*/true, 1, p));
+    return check_launch("conv_stem_direct_kernel");
+}
+
+int32_t stem_direct_s8_launch(const TcParams& p, bool nhwc_out, cudaStream_t stream) {
+    if (p.out == nullptr || p.bias_i32 == nullptr || p.multiplier == nullptr || p.shift == nullptr)
+        return fail(KXC_B200_ERR_INVALID, "int8 stem conv: missing tensors");
+    return nhwc_out ? stem_direct_launch_as<MmaKind::I8, kOutNHWC_S8>(p, stream) : stem_direct_launch_as<MmaKind::I8, kOutNCHW_S8>(p, stream);
+}
 
 bool stem_direct_applicable(TcDType dtype, int C, int O, int KH, int KW, int OW, int Wp) {
     return dtype == kTcBF16 && C <= 4 && O == kBN && KH <= kMaxKH && KW <= 8 && OW <= 128 && Wp * 8 <= kMaxRowBytes &&
@@ -554,14 +646,8 @@ int32_t stem_pool_launch(const TcParams& p, cudaStream_t stream) {
 }
 
 int32_t stem_direct_launch(const TcParams& p, cudaStream_t stream) {
-    static PerDeviceOnce smem_once;
-    KXC_TRY(smem_opt_in(smem_once, conv_stem_direct_kernel, kSmemBytes));
     if (!p.vec_ok || p.out == nullptr) return fail(KXC_B200_ERR_INVALID, "direct stem conv: pointers must be 16-byte aligned");
-    const long long strips = (long long)((p.OH + kStripRows - 1) / kStripRows) * p.N;
-    if (strips <= 0) return KXC_B200_OK;
-    const int grid = (int)(strips < kNumSMs ? strips : kNumSMs);
-    KXC_CUDA_TRY(launch_kernel(conv_stem_direct_kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, /*pdl=*/true, 1, p));
-    return check_launch("conv_stem_direct_kernel");
+    return stem_direct_launch_as<MmaKind::F16, kOutNHWC_BF16>(p, stream);
 }
 
 }  // namespace kxc_b200

@@ -11,6 +11,13 @@ size_t stem_direct_weight_bytes(int KH);
 int32_t stem_direct_pack_weights(const float* w, void* out, int O, int C, int KH, int KW, cudaStream_t s);
 int32_t stem_direct_setup(TcParams* p, const void* packed_in, const void* packed_w, int N, int OH, int OW, int KH, int Hp, int Wp);
 int32_t stem_direct_launch(const TcParams& p, cudaStream_t stream);
+// int8 form of the same kernel (tcgen05 kind::i8, int32 accumulate, fixed-point requantize): packed pixels hold 8 int8
+// channels. stem_direct_s8_pack writes the packed input [N][Hp][Wp][8] and the core-matrix weights; the launch takes the
+// parameters stem_direct_setup fills plus bias_i32 / multiplier / shift / out / relu.
+bool stem_direct_s8_applicable(int C, int O, int KH, int KW, int stride, int dil, int W, int OW, int Wp);
+int32_t stem_direct_s8_pack(const int8_t* x, const int8_t* w, void* packed_x, void* packed_w, int N, int C, int H, int W, int O, int KH,
+                            int KW, int Hp, int Wp, int pad_h, int pad_w, bool nhwc, cudaStream_t s);
+int32_t stem_direct_s8_launch(const TcParams& p, bool nhwc_out, cudaStream_t stream);
 // Fused variant: conv + bias + ReLU + max_pool2d(3x3, s2, p1); `p.out` is the POOLED bf16 NHWC tensor
 // [N, OH/2, OW/2, 64], p.OH / p.OW stay the convolution's output extent. Same setup as stem_direct_setup.
 bool stem_pool_applicable(int OH, int OW, int pool_k, int pool_s, int pool_pad);

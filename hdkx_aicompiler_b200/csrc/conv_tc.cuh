@@ -41,7 +41,7 @@ struct alignas(64) TcParams {
     int tiles_w, tiles_h, tiles_n, tiles_c;
     int relu;
     int round_out_tf32;          // kOutNHWC_F32 only: round stored values to tf32 (they feed another tf32 contraction)
-    int vec_ok;                  // bias/residual/out base pointers are 16-byte aligned: vector epilogue allowed
+    int vec_ok;                  // bias/residual/out (int8: bias/multiplier/shift/out) base pointers are 16-byte aligned: vector epilogue allowed
     const float* bias;           // fp32 bias (float paths), may be null
     const int32_t* bias_i32;     // int32 bias (int8 path)
     const int32_t* multiplier;   // int8 path
@@ -79,7 +79,7 @@ struct TcConfig {
 // Sets vec_ok from the epilogue pointers; call after filling bias/residual/out.
 inline void tc_finish_params(TcParams* p) {
     auto al = [](const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
-    p->vec_ok = al(p->bias) && al(p->residual) && al(p->out) ? 1 : 0;
+    p->vec_ok = al(p->bias) && al(p->residual) && al(p->out) && al(p->bias_i32) && al(p->multiplier) && al(p->shift) ? 1 : 0;
 }
 
 // Launches the persistent kernel for the given configuration. `p` must be fully populated.

@@ -7,10 +7,39 @@
 #include "conv_tc.cuh"
 #include "layout.cuh"
 #include "sm100.cuh"
+#include "conv_stem.cuh"
+
+#include <mutex>
 
 namespace kxc_b200 {
 
 namespace {
+
+// The library's own stream-ordered memory pool, one per device, that keeps what it has allocated (release threshold =
+// unlimited). The device's default pool gives freed memory back to the driver at the next synchronisation, so a caller that
+// synchronises between calls would pay a fresh device allocation (milliseconds for tens of MB) inside every call.
+int32_t scratch_pool(cudaMemPool_t* out) {
+    static std::mutex mu;
+    static cudaMemPool_t pools[PerDeviceOnce::kMaxDevices] = {};
+    int dev = 0;
+    KXC_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= PerDeviceOnce::kMaxDevices) return fail(KXC_B200_ERR_INVALID, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (pools[dev] == nullptr) {
+        cudaMemPoolProps props = {};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = dev;
+        cudaMemPool_t pool = nullptr;
+        KXC_CUDA_TRY(cudaMemPoolCreate(&pool, &props));
+        uint64_t keep = UINT64_MAX;
+        KXC_CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        pools[dev] = pool;
+    }
+    *out = pools[dev];
+    return KXC_B200_OK;
+}
 
 // Stream-ordered scratch: allocated and freed on the caller's stream, so the call stays asynchronous.
 struct StreamScratch {
@@ -18,7 +47,9 @@ struct StreamScratch {
     cudaStream_t stream;
     explicit StreamScratch(cudaStream_t s) : stream(s) {}
     int32_t alloc(size_t bytes) {
-        cudaError_t e = cudaMallocAsync(&ptr, bytes, stream);
+        cudaMemPool_t pool = nullptr;
+        KXC_TRY(scratch_pool(&pool));
+        cudaError_t e = cudaMallocFromPoolAsync(&ptr, bytes, pool, stream);
         if (e != cudaSuccess) {
             ptr = nullptr;
             return fail(KXC_B200_ERR_NOMEM, "workspace of %zu bytes: %s", bytes, cudaGetErrorString(e));
@@ -102,9 +133,34 @@ int32_t conv2d_s8_dispatch(const int8_t* data, const int8_t* weight, const int32
                            cudaStream_t s) {
     const TcDType dt = kTcS8;
     const int cpad = tc_channel_pad(dt, d.C);
+    // few-channel stride-2 first layer (the 7x7 stem): pixels packed to 8 bytes, direct kernel, K = 7 x 64 bytes instead of
+    // 49 taps x 32 padded channels. Both layouts of the entry point take it (NHWC: data [N,H,W,C], weight [O,KH,KW,C]).
+    const int stem_hp = (d.H + 2 * d.PH + 1) & ~1;
+    const int stem_wp = ((d.W + 2 * d.PW > 2 * (d.OW - 1) + 8 ? d.W + 2 * d.PW : 2 * (d.OW - 1) + 8) + 3) / 4 * 4;
+    const bool stem_ok = !force_simt && tc_shape_ok(d) && d.SH == 2 && d.SW == 2 && d.DH == 1 && d.DW == 1 &&
+                         stem_direct_s8_applicable(d.C, d.O, d.KH, d.KW, 2, 1, d.W, d.OW, stem_wp);
+    auto run_stem = [&](bool nhwc_layout) -> int32_t {
+        const size_t x_bytes = align_up((size_t)d.N * stem_hp * stem_wp * 8, 1024);
+        const size_t w_bytes = align_up(stem_direct_weight_bytes(d.KH), 1024);
+        StreamScratch ws(s);
+        KXC_TRY(ws.alloc(x_bytes + w_bytes));
+        uint8_t* px = static_cast<uint8_t*>(ws.ptr);
+        uint8_t* pw = px + x_bytes;
+        KXC_TRY(stem_direct_s8_pack(data, weight, px, pw, d.N, d.C, d.H, d.W, d.O, d.KH, d.KW, stem_hp, stem_wp, d.PH, d.PW, nhwc_layout, s));
+        TcParams p{};
+        KXC_TRY(stem_direct_setup(&p, px, pw, d.N, d.OH, d.OW, d.KH, stem_hp, stem_wp));
+        p.bias_i32 = bias;
+        p.multiplier = multiplier;
+        p.shift = shift;
+        p.out = out;
+        p.relu = relu;
+        tc_finish_params(&p);
+        return stem_direct_s8_launch(p, nhwc_layout, s);
+    };
     if (nhwc) {
         // operands already NHWC / OHWI with the kernel's channel granularity: straight to the tensor-core kernel
         if (force_simt || !tc_shape_ok(d)) return fail(KXC_B200_ERR_UNSUPPORTED, "nn_conv2d_s8: the NHWC form exists for the tensor-core path only");
+        if (stem_ok && d.C <= 8 && aligned16(out)) return run_stem(true);
         if (cpad != d.C || (d.O & 15) != 0 || !aligned16(data) || !aligned16(weight) || !aligned16(out))
             return fail(KXC_B200_ERR_INVALID, "nn_conv2d_s8: NHWC operands need C = 32/64/128k channels, O a multiple of 16 and 16-byte aligned pointers");
         TcParams p{};
@@ -120,25 +176,37 @@ int32_t conv2d_s8_dispatch(const int8_t* data, const int8_t* weight, const int32
         return tc_launch(cfg, p, s);
     }
     if (force_simt || !tc_shape_ok(d)) return conv2d_s8_exact(data, weight, bias, multiplier, shift, out, d, relu, s);
+    if (stem_ok) return run_stem(false);
     const size_t act_bytes = align_up((size_t)d.N * d.H * d.W * cpad, 1024);
     const size_t w_bytes = align_up((size_t)d.O * d.KH * d.KW * cpad, 1024);
+    // Result layout. A thread of the epilogue owns one pixel, so its NCHW stores are single bytes whose neighbours in
+    // memory belong to the next pixel of the same tile row: runs of BW bytes. With the narrow tiles of the deep layers
+    // (BW <= 2) that costs more than the kernel itself (512 -> 512 channels at 7x7, 256 images: 100 us against 35 us for
+    // the NHWC form), so those layers store NHWC into the workspace and a byte transpose writes the reference layout.
+    int bw = 0, bh = 0, bni = 0;
+    tc_pick_tile(d.N, d.OH, d.OW, &bw, &bh, &bni);
+    const bool two_step = bw <= 2 && (d.O & 15) == 0;
+    const size_t out_bytes = two_step ? align_up((size_t)d.N * d.OH * d.OW * d.O, 1024) : 0;
     StreamScratch ws(s);
-    KXC_TRY(ws.alloc(act_bytes + w_bytes));
+    KXC_TRY(ws.alloc(act_bytes + w_bytes + out_bytes));
     uint8_t* act = static_cast<uint8_t*>(ws.ptr);
     uint8_t* wp = act + act_bytes;
+    int8_t* out_nhwc = reinterpret_cast<int8_t*>(wp + w_bytes);
     KXC_TRY(nchw_to_nhwc(data, act, dt, d.N, d.C, d.H * d.W, cpad, s));
     KXC_TRY(pack_weights_ohwi(weight, wp, dt, d.O, d.C, d.KH, d.KW, cpad, s));
     TcParams p{};
     TcConfig cfg{};
-    KXC_TRY(tc_setup_conv(&p, &cfg, dt, kOutNCHW_S8, act, wp, d.N, d.H, d.W, cpad, d.O, d.KH, d.KW, d.SH, d.PH, d.PW, d.DH,
-                          d.DW));
+    KXC_TRY(tc_setup_conv(&p, &cfg, dt, two_step ? kOutNHWC_S8 : kOutNCHW_S8, act, wp, d.N, d.H, d.W, cpad, d.O, d.KH, d.KW, d.SH, d.PH,
+                          d.PW, d.DH, d.DW));
     p.bias_i32 = bias;
     p.multiplier = multiplier;
     p.shift = shift;
-    p.out = out;
+    p.out = two_step ? out_nhwc : out;
     p.relu = relu;
     tc_finish_params(&p);
-    return tc_launch(cfg, p, s);
+    KXC_TRY(tc_launch(cfg, p, s));
+    if (two_step) return nhwc_to_nchw_s8(out_nhwc, out, d.N, d.O, d.OH * d.OW, s);
+    return KXC_B200_OK;
 }
 
 int32_t gemm_tensor_core(const float* a, const float* b, const float* c, float* out, const kxc_b200_gemm_desc& g,

@@ -60,6 +60,54 @@ __global__ void nchw_to_nhwc_kernel(const TIn* __restrict__ in, TOut* __restrict
     }
 }
 
+// int8 form: 64 channels x 64 pixels per block, four bytes per thread on both sides (64-byte runs in HBM instead of the
+// 32-byte runs the element-wise kernel makes of 1-byte elements). grid (ceil(HW/64), ceil(cpad/64), N), block 256.
+// It is a batched byte transpose [C][HW] -> [HW][cpad] (rows c >= C read as zero), so it also serves NHWC -> NCHW with
+// the roles of the two extents exchanged; vec_out = 0 when the destination rows are not 4-byte multiples.
+__global__ void __launch_bounds__(256) nchw_to_nhwc_s8_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, int C, int HW,
+                                                               int cpad, int vec_in, int vec_out) {
+    __shared__ __align__(4) int8_t tile[64][68];
+    const int n = blockIdx.z;
+    const int hw0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
+    const int8_t* src = in + (size_t)n * C * HW;
+    int8_t* dst = out + (size_t)n * HW * cpad;
+    const int q = threadIdx.x & 15, r = threadIdx.x >> 4;  // 16 four-byte columns x 16 rows per pass
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int c = c0 + r + 16 * k, hw = hw0 + 4 * q;
+        uint32_t v = 0;
+        if (c < C) {
+            const int8_t* s4 = src + (size_t)c * HW + hw;
+            if (vec_in && hw + 3 < HW) {
+                v = __ldg(reinterpret_cast<const uint32_t*>(s4));
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (hw + e < HW) v |= (uint32_t)(uint8_t)__ldg(s4 + e) << (8 * e);
+            }
+        }
+        *reinterpret_cast<uint32_t*>(&tile[r + 16 * k][4 * q]) = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int hw = hw0 + r + 16 * k, c = c0 + 4 * q;
+        if (hw < HW && c < cpad) {
+            const int hl = r + 16 * k;
+            const uint32_t v = (uint32_t)(uint8_t)tile[4 * q][hl] | ((uint32_t)(uint8_t)tile[4 * q + 1][hl] << 8) |
+                               ((uint32_t)(uint8_t)tile[4 * q + 2][hl] << 16) | ((uint32_t)(uint8_t)tile[4 * q + 3][hl] << 24);
+            int8_t* d4 = dst + (size_t)hw * cpad + c;
+            if (vec_out) {  // cpad is a multiple of 4: the four bytes are in or out together
+                *reinterpret_cast<uint32_t*>(d4) = v;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (c + e < cpad) d4[e] = (int8_t)(v >> (8 * e));
+            }
+        }
+    }
+}
+
 template <typename TIn, typename TOut>
 __global__ void pack_weights_kernel(const TIn* __restrict__ w, TOut* __restrict__ out, int O, int C, int KH, int KW, int cpad) {
     const int64_t total = (int64_t)O * KH * KW * cpad;
@@ -108,10 +156,25 @@ int32_t nchw_to_nhwc(const void* in, void* out, TcDType dtype, int N, int C, int
                 nchw_to_nhwc_kernel<float, float><<<grid, block, 0, s>>>(static_cast<const float*>(in), static_cast<float*>(out), C, HW, cpad);
             break;
         case kTcS8:
-            nchw_to_nhwc_kernel<int8_t, int8_t><<<grid, block, 0, s>>>(static_cast<const int8_t*>(in), static_cast<int8_t*>(out), C, HW, cpad);
+            if ((cpad & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 3u) == 0) {
+                const int vec_in = ((HW & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 3u) == 0) ? 1 : 0;
+                nchw_to_nhwc_s8_kernel<<<dim3((HW + 63) / 64, (cpad + 63) / 64, N), 256, 0, s>>>(static_cast<const int8_t*>(in),
+                                                                                                static_cast<int8_t*>(out), C, HW, cpad, vec_in, 1);
+            } else {
+                nchw_to_nhwc_kernel<int8_t, int8_t><<<grid, block, 0, s>>>(static_cast<const int8_t*>(in), static_cast<int8_t*>(out), C, HW, cpad);
+            }
             break;
     }
     return check_launch("nchw_to_nhwc");
+}
+
+int32_t nhwc_to_nchw_s8(const int8_t* in, int8_t* out, int N, int C, int HW, cudaStream_t s) {
+    if (N == 0 || C == 0 || HW == 0) return KXC_B200_OK;
+    // source rows = pixels (C bytes each), destination rows = channels (HW bytes each)
+    const int vec_in = ((C & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 3u) == 0) ? 1 : 0;
+    const int vec_out = ((HW & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 3u) == 0) ? 1 : 0;
+    nchw_to_nhwc_s8_kernel<<<dim3((C + 63) / 64, (HW + 63) / 64, N), 256, 0, s>>>(in, out, HW, C, HW, vec_in, vec_out);
+    return check_launch("nhwc_to_nchw_s8");
 }
 
 int32_t pack_weights_ohwi(const void* w, void* out, TcDType dtype, int O, int C, int KH, int KW, int cpad, cudaStream_t s, bool tf32_lo) {

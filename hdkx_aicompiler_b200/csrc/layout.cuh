@@ -14,6 +14,9 @@ namespace kxc_b200 {
 // rounded away, nearest even), or int8 (copied).
 int32_t nchw_to_nhwc(const void* in, void* out, TcDType dtype, int N, int C, int HW, int cpad, cudaStream_t s, bool tf32_lo = false);
 
+// int8 NHWC [N][HW][C] -> NCHW [N][C][HW] (the reference layout of a requantized result).
+int32_t nhwc_to_nchw_s8(const int8_t* in, int8_t* out, int N, int C, int HW, cudaStream_t s);
+
 // OIHW (fp32 or int8) -> [O][KH][KW][cpad] in the operand type.
 int32_t pack_weights_ohwi(const void* w, void* out, TcDType dtype, int O, int C, int KH, int KW, int cpad, cudaStream_t s, bool tf32_lo = false);
 

@@ -94,7 +94,9 @@ def nn_conv2d_s8(data, weight, bias, multiplier, shift, strides=(1, 1), padding=
     """int8 convolution, int32 accumulate + bias, fixed-point requantize to int8 (optionally fused relu).
 
     nhwc=True: data [N,H,W,C], weight [O,KH,KW,C] and the result [N,OH,OW,O] stay in the tensor-core kernel's layout
-    (a quantized pipeline's resident activations): no conversion kernels, no workspace."""
+    (a quantized pipeline's resident activations): no conversion kernels, no workspace. C must be a multiple of the
+    kernel's K block (32), except for a stride-2 first layer of <= 8 channels and 64 filters (the image stem), whose
+    pixels the library packs to 8 bytes for its direct kernel."""
     data = _req(data, torch.int8, "nn_conv2d_s8 data")
     weight = _req(weight, torch.int8, "nn_conv2d_s8 weight")
     bias = _req(bias, torch.int32, "nn_conv2d_s8 bias")

@@ -130,7 +130,9 @@ int64_t kxc_b200_static_scratch_bytes(void);
  * With KXC_B200_NHWC (tensor-core path only) the tensors stay in the kernel's own layout from call to call, as in a
  * quantized pipeline: data int8[N,H,W,C], weight int8[O,KH,KW,C], out int8[N,OH,OW,O], with C a multiple of 32 up to
  * 128 or a multiple of 128, O a multiple of 16 and 16-byte aligned pointers; no conversion kernels run and no
- * workspace is allocated. The values are those of the reference layout, permuted. */
+ * workspace is allocated. One exception to the channel rule: a stride-2 first layer with C <= 8, O == 64 and a
+ * filter of at most 7 x 8 (an image stem) keeps its raw [N,H,W,C] pixels; the library packs them to 8 bytes each in a
+ * workspace and runs its direct stem kernel. The values are those of the reference layout, permuted. */
 int32_t kxc_b200_nn_conv2d_s8(void** packed_args, const kxc_b200_conv2d_desc* desc, void* stream);
 
 /* nn_relu — topi::relu (include/te/topi/nn.h:19-30) via ReluCompute (src/relay/op/nn/activation.cc:14-19).

@@ -222,7 +222,8 @@ def config5(iters, flush, hbm, tf, src):
              peak_source=src)
         # the same convolution with the tensors resident in the kernel's layout (NHWC int8, channels padded to the
         # K-block granularity), as between the layers of a quantized network: the kernel alone
-        cp = 32 if cin <= 32 else (64 if cin <= 64 else (cin + 127) // 128 * 128)
+        # (a first layer of <= 8 channels keeps its raw NHWC pixels: the library packs them for its direct stem kernel)
+        cp = cin if cin <= 8 else 32 if cin <= 32 else (64 if cin <= 64 else (cin + 127) // 128 * 128)
         xh = torch.zeros((N, h, h, cp), dtype=torch.int8, device="cuda")
         xh[..., :cin] = x.permute(0, 2, 3, 1)
         wh = torch.zeros((cout, k, k, cp), dtype=torch.int8, device="cuda")
