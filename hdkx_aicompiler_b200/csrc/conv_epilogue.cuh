@@ -16,6 +16,55 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// int8 requantize of one chunk: 32 int32 accumulators of consecutive channels c0.. (the first `nch` are real) -> 32 int8
+// results, four per word, bytes in channel order.
+__device__ __forceinline__ void requant_chunk(const TcParams& p, const uint32_t (&v)[32], int c0, int nch, uint32_t (&qw)[8]) {
+    bool done = false;
+    if (nch == 32 && p.vec_ok) {
+        // Per-channel constants as 16-byte loads (the same addresses in every lane). With 2 <= shift <= 31 the
+        // rounding term 2^(S-1), S = 31 + shift >= 33, is a multiple of 2^32, so only the high word of the 64-bit
+        // product matters: floor((t + 2^(S-1)) / 2^S) = (hi(t) + 2^(shift-2)) >> (shift-1) exactly, because the low
+        // word adds a fraction < 1 to an integer that is then floored by at least one more bit.
+        // (out-of-range shifts are detected on the way; the chunk is then redone by the general formula)
+        uint32_t in_range = 1;
+        const int32_t lo = p.relu ? 0 : -128;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const int4 b = __ldg(reinterpret_cast<const int4*>(p.bias_i32 + c0 + j));
+            const int4 m = __ldg(reinterpret_cast<const int4*>(p.multiplier + c0 + j));
+            const int4 t = __ldg(reinterpret_cast<const int4*>(p.shift + c0 + j));
+            const int32_t bb[4] = {b.x, b.y, b.z, b.w};
+            const int32_t mm[4] = {m.x, m.y, m.z, m.w};
+            const int32_t ss[4] = {t.x, t.y, t.z, t.w};
+            uint32_t rr[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                in_range &= (uint32_t)((uint32_t)(ss[k] - 2) <= 29u);
+                const int32_t acc = (int32_t)((uint32_t)v[j + k] + (uint32_t)bb[k]);
+                int32_t r = (__mulhi(acc, mm[k]) + (int32_t)(1u << ((ss[k] - 2) & 31))) >> ((ss[k] - 1) & 31);
+                r = r < lo ? lo : r;
+                r = r > 127 ? 127 : r;
+                rr[k] = (uint32_t)r;
+            }
+            qw[j >> 2] = __byte_perm(__byte_perm(rr[0], rr[1], 0x0040), __byte_perm(rr[2], rr[3], 0x0040), 0x5410);
+        }
+        done = in_range != 0;
+    }
+    if (!done) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) qw[j] = 0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int c = c0 + j;
+            if (j < nch) {
+                const int32_t acc = (int32_t)((uint32_t)v[j] + (uint32_t)__ldg(p.bias_i32 + c));
+                const int8_t r = requantize_s8(acc, __ldg(p.multiplier + c), __ldg(p.shift + c), p.relu);
+                qw[j >> 2] |= (uint32_t)(uint8_t)r << (8 * (j & 3));
+            }
+        }
+    }
+}
+
 // Epilogue for one 32-column chunk held by one thread (= one output pixel, 32 consecutive channels).
 template <int kOutMode>
 __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t (&v)[32], int c0, bool valid, int n,
@@ -26,50 +75,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, const uint32_t
 
     if constexpr (kOutMode == kOutNHWC_S8 || kOutMode == kOutNCHW_S8) {
         uint32_t qw[8];  // the chunk's 32 int8 results, four per word (bytes in channel order)
-        bool done = false;
-        if (nch == 32 && p.vec_ok) {
-            // Per-channel constants as 16-byte loads (the same addresses in every lane). With 2 <= shift <= 31 the
-            // rounding term 2^(S-1), S = 31 + shift >= 33, is a multiple of 2^32, so only the high word of the 64-bit
-            // product matters: floor((t + 2^(S-1)) / 2^S) = (hi(t) + 2^(shift-2)) >> (shift-1) exactly, because the low
-            // word adds a fraction < 1 to an integer that is then floored by at least one more bit.
-            // (out-of-range shifts are detected on the way; the chunk is then redone by the general formula)
-            uint32_t in_range = 1;
-            const int32_t lo = p.relu ? 0 : -128;
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-                const int4 b = __ldg(reinterpret_cast<const int4*>(p.bias_i32 + c0 + j));
-                const int4 m = __ldg(reinterpret_cast<const int4*>(p.multiplier + c0 + j));
-                const int4 t = __ldg(reinterpret_cast<const int4*>(p.shift + c0 + j));
-                const int32_t bb[4] = {b.x, b.y, b.z, b.w};
-                const int32_t mm[4] = {m.x, m.y, m.z, m.w};
-                const int32_t ss[4] = {t.x, t.y, t.z, t.w};
-                uint32_t rr[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    in_range &= (uint32_t)((uint32_t)(ss[k] - 2) <= 29u);
-                    const int32_t acc = (int32_t)((uint32_t)v[j + k] + (uint32_t)bb[k]);
-                    int32_t r = (__mulhi(acc, mm[k]) + (int32_t)(1u << ((ss[k] - 2) & 31))) >> ((ss[k] - 1) & 31);
-                    r = r < lo ? lo : r;
-                    r = r > 127 ? 127 : r;
-                    rr[k] = (uint32_t)r;
-                }
-                qw[j >> 2] = __byte_perm(__byte_perm(rr[0], rr[1], 0x0040), __byte_perm(rr[2], rr[3], 0x0040), 0x5410);
-            }
-            done = in_range != 0;
-        }
-        if (!done) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) qw[j] = 0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int c = c0 + j;
-                if (j < nch) {
-                    const int32_t acc = (int32_t)((uint32_t)v[j] + (uint32_t)__ldg(p.bias_i32 + c));
-                    const int8_t r = requantize_s8(acc, __ldg(p.multiplier + c), __ldg(p.shift + c), p.relu);
-                    qw[j >> 2] |= (uint32_t)(uint8_t)r << (8 * (j & 3));
-                }
-            }
-        }
+        requant_chunk(p, v, c0, nch, qw);
         int8_t* out = static_cast<int8_t*>(p.out);
         if constexpr (kOutMode == kOutNHWC_S8) {
             int8_t* dst = out + pix * p.Cout + c0;

@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_rowstack_kernel(const __g
             int stage = 0, rb = 0;
             uint32_t phase = 0, rphase = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-                int r = tile;
+                int r = p.reverse ? total_tiles - 1 - tile : tile;
                 const int tw = r % p.tiles_w; r /= p.tiles_w;
                 const int th = r % p.tiles_h;
                 const int tn = r / p.tiles_h;
@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_rowstack_kernel(const __g
         int acc = 0, rb = 0, ob = 0;
         uint32_t acc_phase = 0, rphase = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            int r = tile;
+            int r = p.reverse ? total_tiles - 1 - tile : tile;
             const int tw = r % p.tiles_w; r /= p.tiles_w;
             const int th = r % p.tiles_h;
             const int n = r / p.tiles_h;
@@ -287,6 +287,206 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_rowstack_kernel(const __g
     if (threadIdx.x == 0 && *abort_ptr && p.status != nullptr) atomicExch(p.status, KXC_B200_ERR_DEVICE_WAIT);
 }
 
+
+// ------------------------------------------------------------------------------------------------------
+// int8 form (tcgen05 kind::i8, int32 accumulators, fixed-point requantize): the same tiling with 64-byte pixels.
+// The general implicit-GEMM kernel fetches every input pixel nine times in boxes of 64-byte rows, and at 64 bytes per
+// row the copy engine's row rate, not bandwidth, bounds it (~4 cycles per row measured: 170 us for 256 images of
+// 56 x 56). Here a tile is ONE box of 160 rows; six instructions of N = 192, K = 32 bytes do its 3 x 3 x 64 reduction.
+// The sum over the three filter rows is an int32 sum (exact in any order), the result is requantized and stored by the
+// thread that owns the pixel (32 bytes per thread, no staging).
+constexpr int kPx8 = 64;                                // bytes per int8 pixel
+constexpr int kHaloBytes8 = kHaloW * kRows * kPx8;      // 10240
+constexpr int kTapBytes8 = kBN * kPx8;                  // 12288
+constexpr int kWeightBytes8 = 3 * kTapBytes8;           // 36864
+constexpr int kStages8 = 6;
+constexpr int kSmemBytes8 = kWeightBytes8 + kStages8 * kHaloBytes8 + 1024;
+
+__global__ void __launch_bounds__(kThreads, 1) conv3x3_rowstack_s8_kernel(const __grid_constant__ TcParams p) {
+    constexpr uint32_t kTmemCols = 2 * kAccStride;
+    constexpr uint32_t kIdesc = make_instr_desc(kFmtS8, kAccS32, kBN);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_w;
+    __shared__ __align__(8) uint64_t bar_full[kStages8];
+    __shared__ __align__(8) uint64_t bar_empty[kStages8];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+    // per output channel {bias, multiplier, 2^(shift-2), shift-1}: the constants of the high-word requantize (see
+    // requant_chunk), prepared once; q_fast = 0 when some shift is outside 2..31 (the general formula is used then)
+    __shared__ __align__(16) int4 q_tab[kO];
+    __shared__ int q_fast;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t w_smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t halo_smem = w_smem + kWeightBytes8;
+
+    if (threadIdx.x == 0) q_fast = 1;
+    __syncthreads();
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + kO) {  // the quantization constants are call arguments, not a producer's output
+        const int c = threadIdx.x - 64;
+        const int sh = __ldg(p.shift + c);
+        const bool in_range = (uint32_t)(sh - 2) <= 29u;
+        q_tab[c] = make_int4(__ldg(p.bias_i32 + c), __ldg(p.multiplier + c), in_range ? (1 << (sh - 2)) : 0, in_range ? sh - 1 : 0);
+        if (!in_range) q_fast = 0;
+    }
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar_w), 1);
+        for (int s = 0; s < kStages8; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bar_acc_full[a]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[a]), 8);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort_ptr = &abort_flag;
+    pdl_launch_dependents();
+
+    const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&p.tmA[0]);
+            tma_prefetch_desc(&p.tmB);
+            mbar_arrive_expect_tx(smem_u32(&bar_w), kWeightBytes8);
+            for (int kw = 0; kw < 3; ++kw)
+                for (int r = 0; r < 3; ++r)
+                    tma_load_2d(w_smem + kw * kTapBytes8 + r * (kO * kPx8), &p.tmB, smem_u32(&bar_w), (r * 3 + kw) * kC, 0);
+            pdl_wait();
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                int r = tile;
+                const int tw = r % p.tiles_w; r /= p.tiles_w;
+                const int th = r % p.tiles_h;
+                const int tn = r / p.tiles_h;
+                if (!mbar_wait_bounded(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr)) break;
+                const uint32_t full = smem_u32(&bar_full[stage]);
+                mbar_arrive_expect_tx(full, kHaloBytes8);
+                tma_load_4d(halo_smem + stage * kHaloBytes8, &p.tmA[0], full, 0, th * kOutRows - 1, tw * kTileW - 1, tn);
+                if (++stage == kStages8) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = mbar_wait_bounded(smem_u32(&bar_w), 0, abort_ptr);
+            const uint32_t hi = desc_hi(8 * kPx8, kLayoutSw64);  // both operands: 8-row groups of contiguous 64-byte rows
+            const uint32_t b_lo0 = desc_lo(w_smem, 16);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr)) break;
+                if (!mbar_wait_bounded(smem_u32(&bar_full[stage]), phase, abort_ptr)) break;
+                tc_fence_after_sync();
+                const uint32_t d = tmem_base + (uint32_t)(acc * kAccStride);
+                const uint32_t a_lo0 = desc_lo(halo_smem + stage * kHaloBytes8, 16);
+#pragma unroll
+                for (int kw = 0; kw < 3; ++kw) {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const uint32_t a_lo = a_lo0 + (uint32_t)((kw * (kRows * kPx8) + k * 32) >> 4);
+                        const uint32_t b_lo = b_lo0 + (uint32_t)((kw * kTapBytes8 + k * 32) >> 4);
+                        umma_i8_split(d, a_lo, hi, b_lo, hi, kIdesc, (kw | k) != 0 ? 1u : 0u);
+                    }
+                }
+                umma_commit(smem_u32(&bar_empty[stage]));
+                umma_commit(smem_u32(&bar_acc_full[acc]));
+                if (++stage == kStages8) { stage = 0; phase ^= 1u; }
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;  // output channels [32*half, 32*half+32)
+        const int h_l = lane & 15;         // accumulator row = input row of the tile
+        const int w_l = 2 * quad + (lane >> 4);
+        const int c0 = half * 32;
+        const bool in_box = (h_l >= 1) && (h_l <= kOutRows);
+        int8_t* out = static_cast<int8_t*>(p.out);
+        pdl_wait();
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            int r = tile;
+            const int tw = r % p.tiles_w; r /= p.tiles_w;
+            const int th = r % p.tiles_h;
+            const int n = r / p.tiles_h;
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr))) break;
+            tc_fence_after_sync();
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccStride + c0);
+            uint32_t v0[32], v1[32], v2[32];
+            tmem_ld_32x32(t_addr, v0);           // D_0: wanted by the row below
+            tmem_ld_32x32(t_addr + kO, v1);      // D_1: this row
+            tmem_ld_32x32(t_addr + 2 * kO, v2);  // D_2: wanted by the row above
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                v1[j] += __shfl_up_sync(0xffffffffu, v0[j], 1) + __shfl_down_sync(0xffffffffu, v2[j], 1);
+            const int oh = th * kOutRows + h_l - 1, ow = tw * kTileW + w_l;
+            if (in_box && oh < p.OH && ow < p.OW) {
+                uint32_t qw[8];
+                if (q_fast) {
+                    const int32_t lo = p.relu ? 0 : -128;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        uint32_t rr[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int4 q = q_tab[c0 + j + k];  // same address in every lane: a broadcast
+                            int32_t r = (__mulhi((int32_t)(v1[j + k] + (uint32_t)q.x), q.y) + q.z) >> q.w;
+                            r = r < lo ? lo : r;
+                            r = r > 127 ? 127 : r;
+                            rr[k] = (uint32_t)r;
+                        }
+                        qw[j >> 2] = __byte_perm(__byte_perm(rr[0], rr[1], 0x0040), __byte_perm(rr[2], rr[3], 0x0040), 0x5410);
+                    }
+                } else {
+                    requant_chunk(p, v1, c0, 32, qw);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(out + (((size_t)n * p.OH + oh) * p.OW + ow) * kO + c0);
+                dst[0] = make_uint4(qw[0], qw[1], qw[2], qw[3]);
+                dst[1] = make_uint4(qw[4], qw[5], qw[6], qw[7]);
+            }
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    if (*abort_ptr) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_ptr && p.status != nullptr) atomicExch(p.status, KXC_B200_ERR_DEVICE_WAIT);
+}
+
 }  // namespace
 
 bool rowstack3x3_applicable(TcDType dtype, int C, int O, int KH, int KW, int stride, int pad_h, int pad_w, int dil_h, int dil_w,
@@ -319,6 +519,45 @@ int32_t rowstack3x3_setup(TcParams* p, const void* act_nhwc, const void* w_packe
     KXC_TRY(tc_make_tmap(&p->tmB, kTcBF16, 2, const_cast<void*>(w_packed), bdims, bstr, bbox, 128));
     KXC_TRY(tc_status_word(&p->status));
     return KXC_B200_OK;
+}
+
+bool rowstack3x3_s8_applicable(int C, int O, int KH, int KW, int stride, int pad_h, int pad_w, int dil_h, int dil_w) {
+    return C == kC && O == kO && KH == 3 && KW == 3 && stride == 1 && pad_h == 1 && pad_w == 1 && dil_h == 1 && dil_w == 1;
+}
+
+int32_t rowstack3x3_s8_setup(TcParams* p, const void* act_nhwc, const void* w_packed, int N, int H, int W) {
+    p->N = N; p->OH = H; p->OW = W; p->Cout = kO;
+    p->taps_h = 3; p->taps_w = 3; p->stride = 1; p->pad_h = 1; p->pad_w = 1; p->dil_h = 1; p->dil_w = 1;
+    p->cblocks = 1; p->kb_elems = kC;
+    p->BW = kTileW; p->BH = kOutRows; p->BNI = 1;
+    p->tiles_w = (W + kTileW - 1) / kTileW;
+    p->tiles_h = (H + kOutRows - 1) / kOutRows;
+    p->tiles_n = N;
+    p->tiles_c = 1;
+    const uint64_t px = kPx8;
+    const uint64_t dims[4] = {(uint64_t)kC, (uint64_t)H, (uint64_t)W, (uint64_t)N};
+    const uint64_t strides[3] = {(uint64_t)W * px, px, (uint64_t)H * W * px};
+    const uint32_t box[4] = {(uint32_t)kC, (uint32_t)kRows, (uint32_t)kHaloW, 1u};
+    KXC_TRY(tc_make_tmap(&p->tmA[0], kTcS8, 4, const_cast<void*>(act_nhwc), dims, strides, box, kPx8));
+    for (int i = 1; i < 4; ++i) p->tmA[i] = p->tmA[0];
+    const uint64_t ktot = (uint64_t)9 * kC;
+    const uint64_t bdims[2] = {ktot, (uint64_t)kO};
+    const uint64_t bstr[1] = {ktot};
+    const uint32_t bbox[2] = {(uint32_t)kC, (uint32_t)kO};
+    KXC_TRY(tc_make_tmap(&p->tmB, kTcS8, 2, const_cast<void*>(w_packed), bdims, bstr, bbox, kPx8));
+    KXC_TRY(tc_status_word(&p->status));
+    return KXC_B200_OK;
+}
+
+int32_t rowstack3x3_s8_launch(const TcParams& p, cudaStream_t stream) {
+    static PerDeviceOnce smem_once;
+    KXC_TRY(smem_opt_in(smem_once, conv3x3_rowstack_s8_kernel, kSmemBytes8));
+    if (!p.vec_ok || p.out == nullptr) return fail(KXC_B200_ERR_INVALID, "row-stacked 3x3 int8 conv: pointers must be 16-byte aligned");
+    const long long tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n;
+    if (tiles <= 0) return KXC_B200_OK;
+    const int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
+    KXC_CUDA_TRY(launch_kernel(conv3x3_rowstack_s8_kernel, dim3(grid), dim3(kThreads), kSmemBytes8, stream, /*pdl=*/true, 1, p));
+    return check_launch("conv3x3_rowstack_s8_kernel");
 }
 
 int32_t rowstack3x3_bind(TcParams* p) {

@@ -143,7 +143,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+            for (int item = first_tile; ok && item < total_tiles; item += tile_step) {
+                const int tile = p.reverse ? total_tiles - 1 - item : item;
                 const int ct = tile % p.tiles_c;
                 int ow0[kMT], oh0[kMT], n0[kMT];
 #pragma unroll
@@ -292,7 +293,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_igemm_kernel(const __grid_
         int acc = 0;
         uint32_t acc_phase = 0;
         bool alive = true;
-        for (int tile = first_tile; alive && tile < total_tiles; tile += tile_step) {
+        for (int item = first_tile; alive && item < total_tiles; item += tile_step) {
+          const int tile = p.reverse ? total_tiles - 1 - item : item;
           const int ct = tile % p.tiles_c;
 #pragma unroll 1
           for (int t = 0; t < kMT; ++t) {

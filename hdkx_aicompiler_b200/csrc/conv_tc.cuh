@@ -53,6 +53,9 @@ struct alignas(64) TcParams {
     const void* aux_in;
     const void* aux_w;
     int aux_row_bytes, aux_hp;
+    // 1: work items are taken from the last to the first. A plan alternates the direction from launch to launch, so a
+    // kernel starts on the images its producer wrote last, which are still in L2 (same items, same results).
+    int reverse;
     int aux_c, aux_h, aux_w_px;  // fused-input stem kernel (conv_stem_fused.cu): channels, height, width of the NCHW fp32 input
     // second output of the dual kernel: a 1x1 convolution of the same stride over the same input (the residual
     // branch's downsample next to a block's first 3x3 stride-2 convolution); its reduction runs as extra K blocks

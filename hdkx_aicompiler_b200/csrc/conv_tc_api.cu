@@ -7,6 +7,7 @@
 #include "conv_tc.cuh"
 #include "layout.cuh"
 #include "sm100.cuh"
+#include "conv_rowstack.cuh"
 #include "conv_stem.cuh"
 
 #include <mutex>
@@ -139,6 +140,13 @@ int32_t conv2d_s8_dispatch(const int8_t* data, const int8_t* weight, const int32
     const int stem_wp = ((d.W + 2 * d.PW > 2 * (d.OW - 1) + 8 ? d.W + 2 * d.PW : 2 * (d.OW - 1) + 8) + 3) / 4 * 4;
     const bool stem_ok = !force_simt && tc_shape_ok(d) && d.SH == 2 && d.SW == 2 && d.DH == 1 && d.DW == 1 &&
                          stem_direct_s8_applicable(d.C, d.O, d.KH, d.KW, 2, 1, d.W, d.OW, stem_wp);
+    // 64 -> 64 channels, 3x3, stride 1: the row-stacked kernel (one box load per tile instead of nine)
+    static const bool rowstack_enabled = [] {
+        const char* e = getenv("KXC_B200_ROWSTACK_S8");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    const bool rowstack_ok = rowstack_enabled && !force_simt && tc_shape_ok(d) &&
+                             rowstack3x3_s8_applicable(d.C, d.O, d.KH, d.KW, d.SH == d.SW ? d.SH : 0, d.PH, d.PW, d.DH, d.DW);
     auto run_stem = [&](bool nhwc_layout) -> int32_t {
         const size_t x_bytes = align_up((size_t)d.N * stem_hp * stem_wp * 8, 1024);
         const size_t w_bytes = align_up(stem_direct_weight_bytes(d.KH), 1024);
@@ -164,6 +172,16 @@ int32_t conv2d_s8_dispatch(const int8_t* data, const int8_t* weight, const int32
         if (cpad != d.C || (d.O & 15) != 0 || !aligned16(data) || !aligned16(weight) || !aligned16(out))
             return fail(KXC_B200_ERR_INVALID, "nn_conv2d_s8: NHWC operands need C = 32/64/128k channels, O a multiple of 16 and 16-byte aligned pointers");
         TcParams p{};
+        if (rowstack_ok) {
+            KXC_TRY(rowstack3x3_s8_setup(&p, data, weight, d.N, d.H, d.W));
+            p.bias_i32 = bias;
+            p.multiplier = multiplier;
+            p.shift = shift;
+            p.out = out;
+            p.relu = relu;
+            tc_finish_params(&p);
+            return rowstack3x3_s8_launch(p, s);
+        }
         TcConfig cfg{};
         KXC_TRY(tc_setup_conv(&p, &cfg, dt, kOutNHWC_S8, data, weight, d.N, d.H, d.W, cpad, d.O, d.KH, d.KW, d.SH, d.PH, d.PW, d.DH,
                               d.DW));
@@ -185,7 +203,7 @@ int32_t conv2d_s8_dispatch(const int8_t* data, const int8_t* weight, const int32
     // the NHWC form), so those layers store NHWC into the workspace and a byte transpose writes the reference layout.
     int bw = 0, bh = 0, bni = 0;
     tc_pick_tile(d.N, d.OH, d.OW, &bw, &bh, &bni);
-    const bool two_step = bw <= 2 && (d.O & 15) == 0;
+    const bool two_step = (bw <= 2 && (d.O & 15) == 0) || rowstack_ok;  // (the row-stacked kernel writes NHWC only)
     const size_t out_bytes = two_step ? align_up((size_t)d.N * d.OH * d.OW * d.O, 1024) : 0;
     StreamScratch ws(s);
     KXC_TRY(ws.alloc(act_bytes + w_bytes + out_bytes));
@@ -196,15 +214,23 @@ int32_t conv2d_s8_dispatch(const int8_t* data, const int8_t* weight, const int32
     KXC_TRY(pack_weights_ohwi(weight, wp, dt, d.O, d.C, d.KH, d.KW, cpad, s));
     TcParams p{};
     TcConfig cfg{};
-    KXC_TRY(tc_setup_conv(&p, &cfg, dt, two_step ? kOutNHWC_S8 : kOutNCHW_S8, act, wp, d.N, d.H, d.W, cpad, d.O, d.KH, d.KW, d.SH, d.PH,
-                          d.PW, d.DH, d.DW));
+    if (rowstack_ok) {
+        KXC_TRY(rowstack3x3_s8_setup(&p, act, wp, d.N, d.H, d.W));
+    } else {
+        KXC_TRY(tc_setup_conv(&p, &cfg, dt, two_step ? kOutNHWC_S8 : kOutNCHW_S8, act, wp, d.N, d.H, d.W, cpad, d.O, d.KH, d.KW, d.SH,
+                              d.PH, d.PW, d.DH, d.DW));
+    }
     p.bias_i32 = bias;
     p.multiplier = multiplier;
     p.shift = shift;
     p.out = two_step ? out_nhwc : out;
     p.relu = relu;
     tc_finish_params(&p);
-    KXC_TRY(tc_launch(cfg, p, s));
+    if (rowstack_ok) {
+        KXC_TRY(rowstack3x3_s8_launch(p, s));
+    } else {
+        KXC_TRY(tc_launch(cfg, p, s));
+    }
     if (two_step) return nhwc_to_nchw_s8(out_nhwc, out, d.N, d.O, d.OH * d.OW, s);
     return KXC_B200_OK;
 }

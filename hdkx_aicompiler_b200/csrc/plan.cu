@@ -1093,6 +1093,13 @@ static int32_t plan_run_core(kxc_b200_plan* pl, void** packed_args, void* stream
         w.source = src;
     }
 
+    // Tensor-core launches alternate the direction in which they walk their work items (KXC_B200_TILE_ORDER=0: all
+    // forward): a launch then begins with the images its producer finished last, whose lines are still in L2.
+    static const bool alternate_order = [] {
+        const char* e = getenv("KXC_B200_TILE_ORDER");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    int tc_index = 0;
     size_t step_index = 0;
     if (events) KXC_CUDA_TRY(cudaEventRecord(events[0], s));
     for (auto& st : pl->steps) {
@@ -1113,6 +1120,7 @@ static int32_t plan_run_core(kxc_b200_plan* pl, void** packed_args, void* stream
                 p.bias = st.bias_const >= 0 ? static_cast<const float*>(arg_of(st.bias_const)) : nullptr;
                 p.bias2 = st.bias2_const >= 0 ? static_cast<const float*>(arg_of(st.bias2_const)) : nullptr;
                 if (st.out_is_graph_output) p.out = out_ptr;
+                p.reverse = (alternate_order && !pl->x3 && (tc_index++ & 1)) ? 1 : 0;
                 tc_finish_params(&p);
                 if (st.weight2 >= 0 && ((reinterpret_cast<uintptr_t>(p.bias2) | reinterpret_cast<uintptr_t>(p.out2)) & 15u)) p.vec_ok = 0;
                 if (pl->x3) {

@@ -312,7 +312,8 @@ def test_reduce_mean_keepdims_inner_axis_rejected(ops, rng):
 
 
 @pytest.mark.parametrize("n,c,h,o,k,s,p", [(3, 64, 14, 64, 3, 1, 1), (2, 128, 9, 256, 3, 2, 1), (2, 32, 8, 48, 1, 1, 0), (1, 256, 7, 512, 1, 2, 0),
-                                           (2, 3, 32, 64, 7, 2, 3), (1, 4, 37, 64, 7, 2, 3), (3, 8, 20, 64, 5, 2, 2), (1, 3, 224, 64, 7, 2, 3)])
+                                           (2, 3, 32, 64, 7, 2, 3), (1, 4, 37, 64, 7, 2, 3), (3, 8, 20, 64, 5, 2, 2), (1, 3, 224, 64, 7, 2, 3),
+                                           (2, 64, 56, 64, 3, 1, 1), (5, 64, 17, 64, 3, 1, 1), (1, 64, 1, 64, 3, 1, 1), (40, 64, 29, 64, 3, 1, 1)])
 def test_conv2d_s8_resident_nhwc_layout(ops, rng, n, c, h, o, k, s, p):
     """int8 convolution with the tensors already in the kernel's NHWC / OHWI layout: the same integers as the
     reference-layout call (and therefore as the oracle), permuted."""
@@ -330,36 +331,37 @@ def test_conv2d_s8_resident_nhwc_layout(ops, rng, n, c, h, o, k, s, p):
 
 
 @pytest.mark.parametrize("nhwc", [False, True])
-def test_conv2d_s8_requantize_every_shift(ops, rng, nhwc):
-    """The tensor-core epilogue requantizes from the high word of the 64-bit product when 2 <= shift <= 31 and by the
+@pytest.mark.parametrize("c,o", [(32, 128), (64, 64)])
+def test_conv2d_s8_requantize_every_shift(ops, rng, nhwc, c, o):
+    """The tensor-core epilogues requantize from the high word of the 64-bit product when 2 <= shift <= 31 and by the
     general formula otherwise: every shift from -8 to 31, both multiplier signs, small and large multipliers, with and
-    without ReLU, against the oracle's integers. Channel groups of 32 are arranged so that some hold only in-range shifts
-    and some mix both kinds."""
-    n, c, h, o, k = 2, 32, 12, 128, 3
+    without ReLU, against the oracle's integers. Two shift sets: all in range (the fast form everywhere), and mixed, with
+    channel groups of 32 that hold only in-range shifts next to groups that fall back. (c, o) = (64, 64) takes the
+    row-stacked kernel, the other shape the general one."""
+    n, h, k = 2, 12, 3
     x = rng.integers(-128, 128, (n, c, h, h)).astype(np.int8)
     w = rng.integers(-127, 128, (o, c, k, k)).astype(np.int8)
     b = rng.integers(-2 ** 20, 2 ** 20, (o,)).astype(np.int32)
     m = rng.integers(-2 ** 31, 2 ** 31, (o,)).astype(np.int64).astype(np.int32)
     m[::7] = rng.integers(-3, 4, m[::7].shape).astype(np.int32)
-    sh = np.empty((o,), np.int32)
-    sh[:32] = rng.integers(2, 32, 32)             # fast form only
-    sh[32:64] = np.arange(32) % 30 + 2            # every in-range value
-    sh[64:96] = np.arange(-8, 24)                 # mixed: the whole group falls back
-    sh[96:] = rng.integers(2, 32, 32)
-    sh[100] = 1
-    sh[32], sh[33] = 2, 31
-    for relu in (True, False):
-        exp = port.conv2d_s8_requant(x, w, b, m, sh, relu=relu, stride=(1, 1), pad=(1, 1))
-        if nhwc:
-            xh = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
-            wh = torch.from_numpy(np.ascontiguousarray(w.transpose(0, 2, 3, 1))).cuda()
-            got = ops.nn_conv2d_s8(xh, wh, dev(b), dev(m), dev(sh), (1, 1), (1, 1), relu=relu, nhwc=True).permute(0, 3, 1, 2)
-        else:
-            got = ops.nn_conv2d_s8(dev(x), dev(w), dev(b), dev(m), dev(sh), (1, 1), (1, 1), relu=relu)
-        assert ops.device_status() == 0
-        assert np.array_equal(got.cpu().numpy(), exp), f"relu={relu}: {np.count_nonzero(got.cpu().numpy() != exp)} differ"
-        simt = ops.nn_conv2d_s8(dev(x), dev(w), dev(b), dev(m), dev(sh), (1, 1), (1, 1), relu=relu, simt=True)
-        assert np.array_equal(simt.cpu().numpy(), exp)
+    in_range = (np.arange(o) % 30 + 2).astype(np.int32)   # every value 2..31
+    mixed = rng.integers(2, 32, o).astype(np.int32)
+    mixed[o // 2:o // 2 + 32] = np.arange(-8, 24)          # one whole group of 32 falls back
+    mixed[-3] = 1
+    mixed[0], mixed[1] = 2, 31
+    for sh in (in_range, mixed):
+        for relu in (True, False):
+            exp = port.conv2d_s8_requant(x, w, b, m, sh, relu=relu, stride=(1, 1), pad=(1, 1))
+            if nhwc:
+                xh = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
+                wh = torch.from_numpy(np.ascontiguousarray(w.transpose(0, 2, 3, 1))).cuda()
+                got = ops.nn_conv2d_s8(xh, wh, dev(b), dev(m), dev(sh), (1, 1), (1, 1), relu=relu, nhwc=True).permute(0, 3, 1, 2)
+            else:
+                got = ops.nn_conv2d_s8(dev(x), dev(w), dev(b), dev(m), dev(sh), (1, 1), (1, 1), relu=relu)
+            assert ops.device_status() == 0
+            assert np.array_equal(got.cpu().numpy(), exp), f"relu={relu}: {np.count_nonzero(got.cpu().numpy() != exp)} differ"
+            simt = ops.nn_conv2d_s8(dev(x), dev(w), dev(b), dev(m), dev(sh), (1, 1), (1, 1), relu=relu, simt=True)
+            assert np.array_equal(simt.cpu().numpy(), exp)
 
 
 # ---------------------------------------------------------------- matmul / transpose / reshape / cast
