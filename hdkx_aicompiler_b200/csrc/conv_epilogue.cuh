@@ -5,6 +5,8 @@
 
 #include <cuda_bf16.h>
 
+#include <climits>
+
 #include "conv_tc.cuh"
 
 namespace kxc_b200 {
@@ -14,6 +16,39 @@ __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// High-word requantize with prepared per-channel constants q = {M, K.lo, K.hi, shift - 1}, K = bias * M + 2^(shift-2+32):
+// for 2 <= shift <= 31 (see requant_chunk) and |bias| small enough that acc + bias cannot leave int32,
+//   (acc + bias) * M + 2^(S-1) = acc * M + K,   S = 31 + shift,
+// so one mad.wide gives the 64-bit sum, its high word shifted by shift-1 is the result before clamping. cvt.pack.sat
+// clamps to [-128, 127] and packs two results per instruction; lo_cap = 0 with ReLU, else INT32_MIN (no-op).
+// Bytes in channel order.
+__device__ __forceinline__ bool requant_prepare(int32_t bias, int32_t mult, int32_t shift, int64_t max_abs_acc, int4* q) {
+    const bool ok = (uint32_t)(shift - 2) <= 29u && (int64_t)bias <= (int64_t)INT32_MAX - max_abs_acc &&
+                    (int64_t)bias >= (int64_t)INT32_MIN + max_abs_acc;
+    const int64_t k = ok ? (int64_t)bias * (int64_t)mult + ((int64_t)1 << (shift - 2 + 32)) : 0;
+    *q = make_int4(mult, (int32_t)(uint32_t)(k & 0xffffffffll), (int32_t)(k >> 32), ok ? shift - 1 : 0);
+    return ok;
+}
+__device__ __forceinline__ uint32_t requant4_prepared(const uint32_t (&v)[4], const int4 (&q)[4], int32_t lo_cap) {
+    int32_t r[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        int32_t t;
+        asm("{\n\t.reg .b64 kk, tt;\n\t.reg .b32 tl;\n\t"
+            "mov.b64 kk, {%2, %3};\n\t"
+            "mad.wide.s32 tt, %1, %4, kk;\n\t"
+            "mov.b64 {tl, %0}, tt;\n\t}"
+            : "=r"(t)
+            : "r"((int32_t)v[k]), "r"(q[k].y), "r"(q[k].z), "r"(q[k].x));
+        t >>= q[k].w;
+        r[k] = t < lo_cap ? lo_cap : t;
+    }
+    uint32_t hi16, out;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi16) : "r"(r[3]), "r"(r[2]), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(r[1]), "r"(r[0]), "r"(hi16));
+    return out;
 }
 
 // int8 requantize of one chunk: 32 int32 accumulators of consecutive channels c0.. (the first `nch` are real) -> 32 int8

@@ -25,6 +25,7 @@
 // accumulators (the epilogue of one tile overlaps the next tile's MMAs); every wait bounded.
 #include "conv_rowstack.cuh"
 
+#include <climits>
 #include <mutex>
 
 #include "common.cuh"
@@ -301,8 +302,12 @@ constexpr int kTapBytes8 = kBN * kPx8;                  // 12288
 constexpr int kWeightBytes8 = 3 * kTapBytes8;           // 36864
 constexpr int kStages8 = 6;
 constexpr int kSmemBytes8 = kWeightBytes8 + kStages8 * kHaloBytes8 + 1024;
+// Two sets of eight epilogue warps, one per accumulator: the epilogue (three TMEM loads, 64 shuffles and the requantize
+// per thread) is latency-bound with eight warps (2900 cycles per tile against ~900 issue cycles), so consecutive tiles
+// are drained concurrently. 18 warps leave 113 registers per thread: a thread takes its 32 channels in two passes of 16.
+constexpr int kThreads8 = 64 + 2 * 256;
 
-__global__ void __launch_bounds__(kThreads, 1) conv3x3_rowstack_s8_kernel(const __grid_constant__ TcParams p) {
+__global__ void __launch_bounds__(kThreads8, 1) conv3x3_rowstack_s8_kernel(const __grid_constant__ TcParams p) {
     constexpr uint32_t kTmemCols = 2 * kAccStride;
     constexpr uint32_t kIdesc = make_instr_desc(kFmtS8, kAccS32, kBN);
 
@@ -314,8 +319,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_rowstack_s8_kernel(const 
     __shared__ __align__(8) uint64_t bar_acc_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
-    // per output channel {bias, multiplier, 2^(shift-2), shift-1}: the constants of the high-word requantize (see
-    // requant_chunk), prepared once; q_fast = 0 when some shift is outside 2..31 (the general formula is used then)
+    // per output channel the constants of the high-word requantize (requant_prepare), prepared once; q_fast = 0 when
+    // some channel does not qualify (the general formula is used then)
     __shared__ __align__(16) int4 q_tab[kO];
     __shared__ int q_fast;
 
@@ -328,10 +333,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_rowstack_s8_kernel(const 
     __syncthreads();
     if (threadIdx.x >= 64 && threadIdx.x < 64 + kO) {  // the quantization constants are call arguments, not a producer's output
         const int c = threadIdx.x - 64;
-        const int sh = __ldg(p.shift + c);
-        const bool in_range = (uint32_t)(sh - 2) <= 29u;
-        q_tab[c] = make_int4(__ldg(p.bias_i32 + c), __ldg(p.multiplier + c), in_range ? (1 << (sh - 2)) : 0, in_range ? sh - 1 : 0);
-        if (!in_range) q_fast = 0;
+        // |accumulator| <= 128 * 128 * (9 taps * 64 channels)
+        if (!requant_prepare(__ldg(p.bias_i32 + c), __ldg(p.multiplier + c), __ldg(p.shift + c), 128ll * 128 * 9 * kC, &q_tab[c])) q_fast = 0;
     }
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -415,61 +418,71 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_rowstack_s8_kernel(const 
         }
     } else {
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;  // output channels [32*half, 32*half+32)
-        const int h_l = lane & 15;         // accumulator row = input row of the tile
+        const int half = ((warp - 2) >> 2) & 1;  // output channels [32*half, 32*half+32)
+        const int set = (warp - 2) >> 3;         // the accumulator this warp drains: tiles of that parity
+        const int h_l = lane & 15;               // accumulator row = input row of the tile
         const int w_l = 2 * quad + (lane >> 4);
-        const int c0 = half * 32;
         const bool in_box = (h_l >= 1) && (h_l <= kOutRows);
         int8_t* out = static_cast<int8_t*>(p.out);
+        const int32_t lo = p.relu ? 0 : INT32_MIN;
+        const bool fast = q_fast != 0;
         pdl_wait();
-        int acc = 0;
         uint32_t acc_phase = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            int r = tile;
-            const int tw = r % p.tiles_w; r /= p.tiles_w;
-            const int th = r % p.tiles_h;
-            const int n = r / p.tiles_h;
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr))) break;
+        // this set's tiles: blockIdx.x + (2 i + set) gridDim.x; the tile coordinates advance by a fixed step with carries
+        const int step = 2 * (int)gridDim.x;
+        const int s_tw = step % p.tiles_w, s_th = (step / p.tiles_w) % p.tiles_h, s_n = step / (p.tiles_w * p.tiles_h);
+        int tile = (int)blockIdx.x + set * (int)gridDim.x;
+        int tw = tile % p.tiles_w, th = (tile / p.tiles_w) % p.tiles_h, n = tile / (p.tiles_w * p.tiles_h);
+        for (; tile < total_tiles; tile += step) {
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_acc_full[set]), acc_phase, abort_ptr))) break;
             tc_fence_after_sync();
-            const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccStride + c0);
-            uint32_t v0[32], v1[32], v2[32];
-            tmem_ld_32x32(t_addr, v0);           // D_0: wanted by the row below
-            tmem_ld_32x32(t_addr + kO, v1);      // D_1: this row
-            tmem_ld_32x32(t_addr + 2 * kO, v2);  // D_2: wanted by the row above
-            tmem_ld_wait();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                v1[j] += __shfl_up_sync(0xffffffffu, v0[j], 1) + __shfl_down_sync(0xffffffffu, v2[j], 1);
             const int oh = th * kOutRows + h_l - 1, ow = tw * kTileW + w_l;
-            if (in_box && oh < p.OH && ow < p.OW) {
-                uint32_t qw[8];
-                if (q_fast) {
-                    const int32_t lo = p.relu ? 0 : -128;
+            const bool store = in_box && oh < p.OH && ow < p.OW;
+            int8_t* dst = out + (((size_t)n * p.OH + oh) * p.OW + ow) * kO;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        uint32_t rr[4];
+            for (int hp = 0; hp < 2; ++hp) {
+                const int c0 = half * 32 + hp * 16;
+                const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(set * kAccStride + c0);
+                uint32_t v0[16], v1[16], v2[16];
+                tmem_ld_32x16(t_addr, v0);           // D_0: wanted by the row below
+                tmem_ld_32x16(t_addr + kO, v1);      // D_1: this row
+                tmem_ld_32x16(t_addr + 2 * kO, v2);  // D_2: wanted by the row above
+                tmem_ld_wait();
+                if (hp == 1) {  // the accumulator is in registers now
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[set]));
+                }
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const int4 q = q_tab[c0 + j + k];  // same address in every lane: a broadcast
-                            int32_t r = (__mulhi((int32_t)(v1[j + k] + (uint32_t)q.x), q.y) + q.z) >> q.w;
-                            r = r < lo ? lo : r;
-                            r = r > 127 ? 127 : r;
-                            rr[k] = (uint32_t)r;
-                        }
-                        qw[j >> 2] = __byte_perm(__byte_perm(rr[0], rr[1], 0x0040), __byte_perm(rr[2], rr[3], 0x0040), 0x5410);
+                for (int j = 0; j < 16; ++j)
+                    v1[j] += __shfl_up_sync(0xffffffffu, v0[j], 1) + __shfl_down_sync(0xffffffffu, v2[j], 1);
+                uint32_t qw[4];
+                if (fast) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) {
+                        const uint32_t vv[4] = {v1[j], v1[j + 1], v1[j + 2], v1[j + 3]};
+                        // (the same addresses in every lane: broadcasts)
+                        const int4 qq[4] = {q_tab[c0 + j], q_tab[c0 + j + 1], q_tab[c0 + j + 2], q_tab[c0 + j + 3]};
+                        qw[j >> 2] = requant4_prepared(vv, qq, lo);
                     }
                 } else {
-                    requant_chunk(p, v1, c0, 32, qw);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) qw[j] = 0;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int8_t x = requantize_s8((int32_t)(v1[j] + (uint32_t)__ldg(p.bias_i32 + c0 + j)), __ldg(p.multiplier + c0 + j),
+                                                       __ldg(p.shift + c0 + j), p.relu);
+                        qw[j >> 2] |= (uint32_t)(uint8_t)x << (8 * (j & 3));
+                    }
                 }
-                uint4* dst = reinterpret_cast<uint4*>(out + (((size_t)n * p.OH + oh) * p.OW + ow) * kO + c0);
-                dst[0] = make_uint4(qw[0], qw[1], qw[2], qw[3]);
-                dst[1] = make_uint4(qw[4], qw[5], qw[6], qw[7]);
+                if (store) *reinterpret_cast<uint4*>(dst + c0) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
             }
-            acc ^= 1;
-            if (acc == 0) acc_phase ^= 1u;
+            acc_phase ^= 1u;
+            tw += s_tw;
+            if (tw >= p.tiles_w) { tw -= p.tiles_w; ++th; }
+            th += s_th;
+            if (th >= p.tiles_h) { th -= p.tiles_h; ++n; }
+            n += s_n;
         }
     }
 
@@ -556,7 +569,7 @@ int32_t rowstack3x3_s8_launch(const TcParams& p, cudaStream_t stream) {
     const long long tiles = (long long)p.tiles_w * p.tiles_h * p.tiles_n;
     if (tiles <= 0) return KXC_B200_OK;
     const int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
-    KXC_CUDA_TRY(launch_kernel(conv3x3_rowstack_s8_kernel, dim3(grid), dim3(kThreads), kSmemBytes8, stream, /*pdl=*/true, 1, p));
+    KXC_CUDA_TRY(launch_kernel(conv3x3_rowstack_s8_kernel, dim3(grid), dim3(kThreads8), kSmemBytes8, stream, /*pdl=*/true, 1, p));
     return check_launch("conv3x3_rowstack_s8_kernel");
 }
 

@@ -349,7 +349,10 @@ def test_conv2d_s8_requantize_every_shift(ops, rng, nhwc, c, o):
     mixed[o // 2:o // 2 + 32] = np.arange(-8, 24)          # one whole group of 32 falls back
     mixed[-3] = 1
     mixed[0], mixed[1] = 2, 31
-    for sh in (in_range, mixed):
+    big_bias = b.copy()  # a bias near the int32 limit (no actual overflow): kernels that fold the bias must fall back
+    big_bias[5] = 2 ** 31 - 1 - 5_000_000
+    big_bias[6] = -2 ** 31 + 5_000_000
+    for sh, b in ((in_range, b), (mixed, b), (in_range, big_bias)):
         for relu in (True, False):
             exp = port.conv2d_s8_requant(x, w, b, m, sh, relu=relu, stride=(1, 1), pad=(1, 1))
             if nhwc:
