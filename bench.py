@@ -3,9 +3,9 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--batch B]
 
-One "step" = one pass of the whole graph (stem pack, 20 fused tensor-core convolutions, max pool,
-global average pool, dense) over the global batch of 1024 synthetic images, bf16 operands with fp32
-accumulation, sharded data-parallel over N GPUs (1024/N images per GPU, weights replicated, logits
+One "step" = one pass of the whole graph (the stem kernel that reads the fp32 NCHW images and writes the pooled
+activation, 19 more convolutions in 16 launches with bias / residual / ReLU fused, global average pool, dense)
+over the global batch of 1024 synthetic images, bf16 operands with fp32 accumulation, sharded data-parallel over N GPUs (1024/N images per GPU, weights replicated, logits
 gathered to rank 0 with one NCCL gather inside the step). Prints ONE JSON line on rank 0.
 
 value     device-timed (CUDA events, max over ranks) with the inputs resident in HBM
