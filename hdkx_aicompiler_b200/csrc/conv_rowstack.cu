@@ -37,7 +37,12 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kThreads = 320;
+// Two sets of eight epilogue warps, one per accumulator: set s drains the CTA's tiles of parity s, so the epilogues of
+// consecutive tiles (three TMEM loads, 64 shuffles, residual, packing: latency-bound with eight warps) overlap. 18 warps
+// leave 113 registers per thread, so a thread takes its 32 channels in two passes of 16. Per launch at 1024 images,
+// without / with residual: 0.199 / 0.238 ms, against 0.201 / 0.258 with one set of eight warps x 32 channels and
+// 0.211 / 0.268 with sixteen warps x 16 channels on one accumulator.
+constexpr int kThreads = 64 + 2 * 256;  // producer warp, MMA warp, two sets of eight epilogue warps
 constexpr int kC = 64;      // input channels = one 128-byte row
 constexpr int kO = 64;      // output channels
 constexpr int kBN = 3 * kO; // MMA N: the three filter rows side by side
@@ -94,7 +99,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_rowstack_kernel(const __g
         }
         for (int b = 0; b < kResBufs; ++b) {
             mbar_init(smem_u32(&bar_res_full[b]), 1);
-            mbar_init(smem_u32(&bar_res_empty[b]), 8);  // one arrival per epilogue warp once it has read its pixels
+            mbar_init(smem_u32(&bar_res_empty[b]), 8);  // one arrival per warp of the set that read it
         }
         mbar_fence_init();
     }
@@ -177,99 +182,103 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_rowstack_kernel(const __g
         }
     } else {
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;  // output channels [32*half, 32*half+32)
-        const int h_l = lane & 15;         // accumulator row = input row of the tile
+        const int half = ((warp - 2) >> 2) & 1;  // output channels [32*half, 32*half+32)
+        const int set = (warp - 2) >> 3;
+        const int h_l = lane & 15;               // accumulator row = input row of the tile
         const int w_l = 2 * quad + (lane >> 4);
-        const int c0 = half * 32;
-        const bool issuer = threadIdx.x == 64;  // the epilogue thread that owns the TMA stores' async groups
+        const bool issuer = threadIdx.x == 64 + set * kEpiThreads;  // owns this set's TMA stores (async groups)
         // this thread's pixel inside an 8 x 14 box ([column][row][channel], 128-byte rows, SWIZZLE_128B: the 16-byte
         // chunk j of a row sits at chunk j ^ (row index & 7); the boxes are 1024-byte aligned)
         const bool in_box = (h_l >= 1) && (h_l <= kOutRows);
         const uint32_t box_row = (uint32_t)(w_l * kOutRows + (h_l - 1));
         const uint32_t row_off = box_row * 128u;
         const uint32_t sw = box_row & 7u;
-        float bias[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) bias[j] = p.bias != nullptr ? __ldg(p.bias + c0 + j) : 0.0f;
+        const uint32_t out_box = out_smem + set * kBoxBytes;  // kOutBufs == 2: one box per set
         pdl_wait();
-        int acc = 0, rb = 0, ob = 0;
-        uint32_t acc_phase = 0, rphase = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        uint32_t acc_phase = 0;
+        int it = set;
+        for (int tile = blockIdx.x + set * gridDim.x; tile < total_tiles; tile += 2 * gridDim.x, it += 2) {
             int r = p.reverse ? total_tiles - 1 - tile : tile;
             const int tw = r % p.tiles_w; r /= p.tiles_w;
             const int th = r % p.tiles_h;
             const int n = r / p.tiles_h;
-            // A wait that runs out must not leave some of the eight warps behind at the barriers below: the failure is
+            const int rb = it % kResBufs;  // the residual ring is filled in tile order
+            const uint32_t rphase = (uint32_t)(it / kResBufs) & 1u;
+            // A wait that runs out must not leave some of the set's warps behind at the barriers below: the failure is
             // carried to the first barrier, where all of them learn of it and leave together.
-            bool bad = !__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr));
-            float f[32];
-            if (!bad) {
-                tc_fence_after_sync();
-                const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kAccStride + c0);
-                uint32_t v0[32], v1[32], v2[32];
-                tmem_ld_32x32(t_addr, v0);           // D_0: wanted by the row below
-                tmem_ld_32x32(t_addr + kO, v1);      // D_1: this row
-                tmem_ld_32x32(t_addr + 2 * kO, v2);  // D_2: wanted by the row above
+            bool bad = !__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_acc_full[set]), acc_phase, abort_ptr));
+            if (has_res && !bad) bad = !__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_res_full[rb]), rphase, abort_ptr));
+            // this set's output box must have been read by its previous TMA store before it is overwritten
+            if (issuer) bulk_wait_group_read<0>();
+            if (named_barrier_or(1 + 2 * set, kEpiThreads, bad)) break;
+            tc_fence_after_sync();
+#pragma unroll
+            for (int hp = 0; hp < 2; ++hp) {
+                const int c0 = half * 32 + hp * 16;
+                const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(set * kAccStride + c0);
+                uint32_t v0[16], v1[16], v2[16];
+                tmem_ld_32x16(t_addr, v0);           // D_0: wanted by the row below
+                tmem_ld_32x16(t_addr + kO, v1);      // D_1: this row
+                tmem_ld_32x16(t_addr + 2 * kO, v2);  // D_2: wanted by the row above
                 tmem_ld_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));  // accumulator is in registers now
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float up = __uint_as_float(__shfl_up_sync(0xffffffffu, v0[j], 1));      // D_0 of row oh - 1
-                    const float down = __uint_as_float(__shfl_down_sync(0xffffffffu, v2[j], 1));  // D_2 of row oh + 1
-                    f[j] = __fadd_rn(__fadd_rn(__fadd_rn(up, __uint_as_float(v1[j])), down), bias[j]);
+                if (hp == 1) {  // accumulator is in registers now
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[set]));
                 }
-            }
-            if (has_res && !bad) {
-                bad = !__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bar_res_full[rb]), rphase, abort_ptr));
-                if (!bad) {
-                    if (in_box) {
-                        const uint32_t base = res_smem + rb * kBoxBytes + row_off;
+                float f[16];
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            const uint4 rv = ld_shared_v4(base + ((((uint32_t)(half * 4 + g)) ^ sw) << 4));
-                            const uint32_t w[4] = {rv.x, rv.y, rv.z, rv.w};
+                for (int j = 0; j < 16; j += 4) {
+                    const float4 b = p.bias != nullptr ? __ldg(reinterpret_cast<const float4*>(p.bias + c0 + j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float bb[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                f[g * 8 + 2 * k] = __fadd_rn(f[g * 8 + 2 * k], bf16_lo(w[k]));
-                                f[g * 8 + 2 * k + 1] = __fadd_rn(f[g * 8 + 2 * k + 1], bf16_hi(w[k]));
-                            }
+                    for (int k = 0; k < 4; ++k) {
+                        const float up = __uint_as_float(__shfl_up_sync(0xffffffffu, v0[j + k], 1));      // D_0 of row oh - 1
+                        const float down = __uint_as_float(__shfl_down_sync(0xffffffffu, v2[j + k], 1));  // D_2 of row oh + 1
+                        f[j + k] = __fadd_rn(__fadd_rn(__fadd_rn(up, __uint_as_float(v1[j + k])), down), bb[k]);
+                    }
+                }
+                if (has_res && in_box) {
+                    const uint32_t base = res_smem + rb * kBoxBytes + row_off;
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) {
+                        const uint4 rv = ld_shared_v4(base + ((((uint32_t)(half * 4 + hp * 2 + g)) ^ sw) << 4));
+                        const uint32_t w[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            f[g * 8 + 2 * k] = __fadd_rn(f[g * 8 + 2 * k], bf16_lo(w[k]));
+                            f[g * 8 + 2 * k + 1] = __fadd_rn(f[g * 8 + 2 * k + 1], bf16_hi(w[k]));
                         }
                     }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bar_res_empty[rb]));
-                    if (++rb == kResBufs) { rb = 0; rphase ^= 1u; }
+                }
+                if (p.relu) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) f[j] = f[j] > 0.0f ? f[j] : 0.0f;
+                }
+                if (in_box) {
+                    const uint32_t base = out_box + row_off;
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) {
+                        uint4 o;
+                        o.x = pack_bf16(f[g * 8 + 0], f[g * 8 + 1]);
+                        o.y = pack_bf16(f[g * 8 + 2], f[g * 8 + 3]);
+                        o.z = pack_bf16(f[g * 8 + 4], f[g * 8 + 5]);
+                        o.w = pack_bf16(f[g * 8 + 6], f[g * 8 + 7]);
+                        st_shared_v4(base + ((((uint32_t)(half * 4 + hp * 2 + g)) ^ sw) << 4), o);
+                    }
                 }
             }
-            if (p.relu) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) f[j] = f[j] > 0.0f ? f[j] : 0.0f;
-            }
-            // the output box used two tiles ago must have been read by its TMA store before it is overwritten
-            if (issuer) bulk_wait_group_read<kOutBufs - 1>();
-            if (named_barrier_or(1, kEpiThreads, bad)) break;
-            if (in_box) {
-                const uint32_t base = out_smem + ob * kBoxBytes + row_off;
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint4 o;
-                    o.x = pack_bf16(f[g * 8 + 0], f[g * 8 + 1]);
-                    o.y = pack_bf16(f[g * 8 + 2], f[g * 8 + 3]);
-                    o.z = pack_bf16(f[g * 8 + 4], f[g * 8 + 5]);
-                    o.w = pack_bf16(f[g * 8 + 6], f[g * 8 + 7]);
-                    st_shared_v4(base + ((((uint32_t)(half * 4 + g)) ^ sw) << 4), o);
-                }
+            if (has_res) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_res_empty[rb]));
             }
             fence_proxy_async_shared();
-            named_barrier(2, kEpiThreads);
+            named_barrier(2 + 2 * set, kEpiThreads);
             if (issuer) {  // pixels beyond the image's last row or column are clipped by the store
-                tma_store_4d(&p.tmA[2], out_smem + ob * kBoxBytes, 0, th * kOutRows, tw * kTileW, n);
+                tma_store_4d(&p.tmA[2], out_box, 0, th * kOutRows, tw * kTileW, n);
                 bulk_commit_group();
             }
-            ob ^= 1;
-            acc ^= 1;
-            if (acc == 0) acc_phase ^= 1u;
+            acc_phase ^= 1u;
         }
         if (issuer) bulk_wait_group_all();
     }

@@ -15,6 +15,12 @@ int32_t rowstack3x3_setup(TcParams* p, const void* act_nhwc, const void* w_packe
 int32_t rowstack3x3_bind(TcParams* p);
 int32_t rowstack3x3_launch(const TcParams& p, cudaStream_t stream);
 
+// 128 -> 128 channel form on CTA pairs with resident weights (conv_rowstack128.cu); same calling sequence.
+bool rowstack128_applicable(TcDType dtype, int C, int O, int KH, int KW, int stride, int pad_h, int pad_w, int dil_h, int dil_w);
+int32_t rowstack128_setup(TcParams* p, const void* act_nhwc, const void* w_packed, int N, int H, int W);
+int32_t rowstack128_bind(TcParams* p);
+int32_t rowstack128_launch(const TcParams& p, cudaStream_t stream);
+
 // int8 form (kind::i8, requantized int8 NHWC result written by the epilogue threads; no residual). The caller fills
 // bias_i32 / multiplier / shift / out / relu and calls tc_finish_params before the launch.
 bool rowstack3x3_s8_applicable(int C, int O, int KH, int KW, int stride, int pad_h, int pad_w, int dil_h, int dil_w);

@@ -18,6 +18,8 @@
 // bounded waits).
 #include "conv_stem.cuh"
 
+#include <climits>
+
 #include <cuda_bf16.h>
 
 #include <cmath>
@@ -67,6 +69,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __g
     __shared__ __align__(8) uint64_t bar_acc_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
+    // int8: per output channel the constants of the high-word requantize (requant_prepare), prepared once per CTA;
+    // q_fast = 0 when some channel does not qualify (the general formula is used then)
+    __shared__ __align__(16) int4 q_tab[kKind == MmaKind::I8 ? kBN : 1];
+    __shared__ int q_fast;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -74,6 +80,16 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __g
     const uint32_t strip_smem = w_smem + kWeightBytes;
 
     const int KH = p.taps_h;
+    if constexpr (kKind == MmaKind::I8) {
+        if (threadIdx.x == 0) q_fast = 1;
+        __syncthreads();
+        // |accumulator| <= 128 * 128 * (KH rows * 8 columns * 8 channels); the constants are call arguments
+        if (threadIdx.x >= 64 && threadIdx.x < 64 + kBN) {
+            const int c = threadIdx.x - 64;
+            if (!requant_prepare(__ldg(p.bias_i32 + c), __ldg(p.multiplier + c), __ldg(p.shift + c), 128ll * 128 * 64 * KH, &q_tab[c]))
+                q_fast = 0;
+        }
+    }
     const int row_bytes = p.aux_row_bytes;          // Wp * 8
     const int Hp = p.aux_hp;
     const int strips_per_image = (p.OH + kStripRows - 1) / kStripRows;
@@ -199,7 +215,31 @@ __global__ void __launch_bounds__(kThreads, 1) conv_stem_direct_kernel(const __g
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
                 if constexpr (kKind == MmaKind::I8) {
-                    epilogue_chunk<kOutMode>(p, v, c0, col_ok, n, oh0 + rr, ow);
+                    if (q_fast && p.vec_ok) {
+                        if (col_ok) {
+                            const int32_t lo = p.relu ? 0 : INT32_MIN;
+                            uint32_t qw[8];
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const uint32_t vv[4] = {v[j], v[j + 1], v[j + 2], v[j + 3]};
+                                const int4 qq[4] = {q_tab[c0 + j], q_tab[c0 + j + 1], q_tab[c0 + j + 2], q_tab[c0 + j + 3]};  // broadcasts
+                                qw[j >> 2] = requant4_prepared(vv, qq, lo);
+                            }
+                            int8_t* out = static_cast<int8_t*>(p.out);
+                            if constexpr (kOutMode == kOutNHWC_S8) {
+                                uint4* dst = reinterpret_cast<uint4*>(out + (((size_t)n * p.OH + (oh0 + rr)) * p.OW + ow) * kBN + c0);
+                                dst[0] = make_uint4(qw[0], qw[1], qw[2], qw[3]);
+                                dst[1] = make_uint4(qw[4], qw[5], qw[6], qw[7]);
+                            } else {  // NCHW: consecutive lanes are consecutive columns, a channel's store is one 32-byte run
+                                const size_t plane = (size_t)p.OH * p.OW;
+                                int8_t* dst = out + ((size_t)n * kBN + c0) * plane + (size_t)(oh0 + rr) * p.OW + ow;
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) dst[(size_t)j * plane] = (int8_t)(qw[j >> 2] >> (8 * (j & 3)));
+                            }
+                        }
+                    } else {
+                        epilogue_chunk<kOutMode>(p, v, c0, col_ok, n, oh0 + rr, ow);
+                    }
                 } else if (col_ok) {
                     const size_t pix = ((size_t)n * p.OH + (oh0 + rr)) * p.OW + ow;
                     const uint4 no_res[4] = {};

@@ -314,6 +314,18 @@ int32_t setup_stem(kxc_b200_plan* pl, Step& st, int N, int C, int H, int W, int 
 
 }  // namespace
 
+// The 128 -> 128 channel 3x3 layers: the row-stacked CTA-pair kernel with resident weights or the implicit-GEMM kernel.
+// Measured per launch at 28 x 28 (ms, row-stacked against implicit GEMM): without a residual 0.191 / 0.215 at 1024 images
+// and 0.033 / 0.037 at 128; with a residual 0.235 / 0.227 at 1024 and 0.037-0.039 / 0.040-0.041 at 128. So: always without
+// a residual, with one only for small launches. KXC_B200_ROWSTACK128 = 0: never, 2: always (A/B runs); read at every
+// plan build.
+static bool rowstack128_wanted(bool has_residual, long long pixels) {
+    const char* e = getenv("KXC_B200_ROWSTACK128");
+    if (e != nullptr && e[0] == '0') return false;
+    if (e != nullptr && e[0] == '2') return true;
+    return !has_residual || pixels <= 128ll * 28 * 28;
+}
+
 static int32_t finalize_exact(kxc_b200_plan* pl);
 static int32_t run_exact(kxc_b200_plan* pl, void** packed_args, void* stream, cudaEvent_t* events);
 
@@ -939,6 +951,14 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
                     st.direct = 3;
                     KXC_TRY(rowstack3x3_setup(&st.params, pl->storage(st.in0), pw.ptr, st.N, st.H, st.W));
                     st.cfg = TcConfig{dt, 128, 64, om};
+                } else if (rowstack128_wanted(st.in1 >= 0, (long long)st.N * st.H * st.W) && !st.out_is_graph_output && !pl->x3 &&
+                           st.weight2 < 0 &&
+                           rowstack128_applicable(dt, st.C, pw.O, pw.KH, pw.KW, st.pool.strides[0], st.pad_h, st.pad_w,
+                                                  st.pool.pool_size[0], st.pool.pool_size[1])) {
+                    st.direct = 5;
+                    KXC_TRY(rowstack128_setup(&st.params, pl->storage(st.in0), pw.ptr, st.N, st.H, st.W));
+                    st.cfg = TcConfig{dt, 128, 192, om};
+                    st.cfg.ctas = 2;
                 } else if (direct_mode > 0 && !st.out_is_graph_output &&
                     direct3x3_applicable(dt, st.C, pw.O, pw.KH, pw.KW, st.pool.strides[0], st.pad_h, st.pad_w, st.pool.pool_size[0],
                                          st.pool.pool_size[1], (int)ov->shape[3])) {
@@ -979,6 +999,7 @@ static int32_t finalize_core(kxc_b200_plan* pl) {
                 st.params_hilo.residual = st.params.out;
             }
             if (st.direct == 3) KXC_TRY(rowstack3x3_bind(&st.params));
+            if (st.direct == 5) KXC_TRY(rowstack128_bind(&st.params));
             if (st.direct == 0 && pw.mode == 0 && !st.out_is_graph_output) KXC_TRY(tc_bind_store(&st.params, st.cfg));
             (void)ov;
         } else if (st.kind == SKind::Gemm) {
@@ -1154,6 +1175,8 @@ static int32_t plan_run_core(kxc_b200_plan* pl, void** packed_args, void* stream
                     KXC_TRY(st.fused_pool ? stem_pool_launch(p, s) : stem_direct_launch(p, s));
                 } else if (st.direct == 3) {
                     KXC_TRY(rowstack3x3_launch(p, s));
+                } else if (st.direct == 5) {
+                    KXC_TRY(rowstack128_launch(p, s));
                 } else if (st.direct == 1) {
                     KXC_TRY(direct3x3_launch(p, s));
                 } else {
@@ -1309,7 +1332,7 @@ extern "C" int32_t kxc_b200_plan_launch_info(kxc_b200_plan* pl, int32_t index, c
                                                 : ((w.mode == 1 || w.mode == 4) ? (double)st.N * st.Hp * st.Wp * 4 * eb : (double)st.N * st.H * st.W * st.cpad * eb);
             by = in_bytes + (double)w.bytes + out_elems * (st.fused_pool ? 0.25 : 1.0) * (st.out_is_graph_output ? 4.0 : eb) +
                  (st.in1 >= 0 ? out_elems * eb : 0.0) + 4.0 * w.O;
-            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d%s", st.direct == 4 ? "conv_stem_pool_nchw" : st.direct == 2 ? (st.fused_pool ? "conv_stem_pool" : "conv_stem_direct") : (st.direct == 3 ? "conv_rowstack" : (st.direct ? "conv_direct" : "conv_igemm")), w.C, st.H, st.W, w.O, w.KH, w.KW,
+            snprintf(buf, sizeof(buf), "%s c%d h%d w%d -> o%d k%dx%d s%d%s%s tile %dx%dx%d bn%d%s", st.direct == 4 ? "conv_stem_pool_nchw" : st.direct == 2 ? (st.fused_pool ? "conv_stem_pool" : "conv_stem_direct") : (st.direct == 3 ? "conv_rowstack" : (st.direct == 5 ? "conv_rowstack128" : (st.direct ? "conv_direct" : "conv_igemm"))), w.C, st.H, st.W, w.O, w.KH, w.KW,
                      p.stride, st.in1 >= 0 ? " +res" : "", st.relu ? " +relu" : "", p.BNI, p.BH, p.BW, st.cfg.bn,
                      st.cfg.ctas == 2 ? " pair" : (st.weight2 >= 0 ? " +1x1 second output" : (st.cfg.mt == 2 ? " x2 tiles" : "")));
             break;

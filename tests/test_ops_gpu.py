@@ -331,14 +331,14 @@ def test_conv2d_s8_resident_nhwc_layout(ops, rng, n, c, h, o, k, s, p):
 
 
 @pytest.mark.parametrize("nhwc", [False, True])
-@pytest.mark.parametrize("c,o", [(32, 128), (64, 64)])
-def test_conv2d_s8_requantize_every_shift(ops, rng, nhwc, c, o):
+@pytest.mark.parametrize("c,o,k,st,pd,h", [(32, 128, 3, 1, 1, 12), (64, 64, 3, 1, 1, 12), (3, 64, 7, 2, 3, 22)])
+def test_conv2d_s8_requantize_every_shift(ops, rng, nhwc, c, o, k, st, pd, h):
     """The tensor-core epilogues requantize from the high word of the 64-bit product when 2 <= shift <= 31 and by the
     general formula otherwise: every shift from -8 to 31, both multiplier signs, small and large multipliers, with and
     without ReLU, against the oracle's integers. Two shift sets: all in range (the fast form everywhere), and mixed, with
     channel groups of 32 that hold only in-range shifts next to groups that fall back. (c, o) = (64, 64) takes the
-    row-stacked kernel, the other shape the general one."""
-    n, h, k = 2, 12, 3
+    row-stacked kernel, 3 channels with a 7x7 stride-2 filter the stem kernel, the other shape the general one."""
+    n = 2
     x = rng.integers(-128, 128, (n, c, h, h)).astype(np.int8)
     w = rng.integers(-127, 128, (o, c, k, k)).astype(np.int8)
     b = rng.integers(-2 ** 20, 2 ** 20, (o,)).astype(np.int32)
@@ -354,16 +354,16 @@ def test_conv2d_s8_requantize_every_shift(ops, rng, nhwc, c, o):
     big_bias[6] = -2 ** 31 + 5_000_000
     for sh, b in ((in_range, b), (mixed, b), (in_range, big_bias)):
         for relu in (True, False):
-            exp = port.conv2d_s8_requant(x, w, b, m, sh, relu=relu, stride=(1, 1), pad=(1, 1))
+            exp = port.conv2d_s8_requant(x, w, b, m, sh, relu=relu, stride=(st, st), pad=(pd, pd))
             if nhwc:
                 xh = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
                 wh = torch.from_numpy(np.ascontiguousarray(w.transpose(0, 2, 3, 1))).cuda()
-                got = ops.nn_conv2d_s8(xh, wh, dev(b), dev(m), dev(sh), (1, 1), (1, 1), relu=relu, nhwc=True).permute(0, 3, 1, 2)
+                got = ops.nn_conv2d_s8(xh, wh, dev(b), dev(m), dev(sh), (st, st), (pd, pd), relu=relu, nhwc=True).permute(0, 3, 1, 2)
             else:
-                got = ops.nn_conv2d_s8(dev(x), dev(w), dev(b), dev(m), dev(sh), (1, 1), (1, 1), relu=relu)
+                got = ops.nn_conv2d_s8(dev(x), dev(w), dev(b), dev(m), dev(sh), (st, st), (pd, pd), relu=relu)
             assert ops.device_status() == 0
             assert np.array_equal(got.cpu().numpy(), exp), f"relu={relu}: {np.count_nonzero(got.cpu().numpy() != exp)} differ"
-            simt = ops.nn_conv2d_s8(dev(x), dev(w), dev(b), dev(m), dev(sh), (1, 1), (1, 1), relu=relu, simt=True)
+            simt = ops.nn_conv2d_s8(dev(x), dev(w), dev(b), dev(m), dev(sh), (st, st), (pd, pd), relu=relu, simt=True)
             assert np.array_equal(simt.cpu().numpy(), exp)
 
 

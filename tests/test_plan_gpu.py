@@ -357,6 +357,47 @@ def test_64_channel_3x3_kernels_agree(kxc, monkeypatch, n, h, w):
     assert float(np.abs(outs["direct"] - outs["igemm"]).max()) <= 2e-2 * scale
 
 
+@pytest.mark.parametrize("n,h,w", [(2, 28, 28), (3, 30, 20), (1, 7, 5), (3, 14, 8), (1, 15, 9), (40, 28, 28)])
+def test_128_channel_3x3_kernels_agree(kxc, monkeypatch, n, h, w):
+    """Three 128 -> 128 3x3 layers (+bias, +relu, the last with a residual) through the row-stacked CTA-pair kernel with
+    resident weights and through the general implicit-GEMM kernel: same bf16 operands and fp32 accumulation, only the
+    summation order differs; both against the same-rounding oracle. Ragged sizes exercise the zero-filled borders, the
+    partial last tiles and an odd number of tiles (a pair whose second tile does not exist); 40 images give every pair
+    several work items."""
+    R = kxc.relay
+    rng = np.random.default_rng(6)
+    x = rng.uniform(-1, 1, (n, 128, h, w)).astype(f32)
+    ws = [rng.normal(0, (2 / 1152) ** 0.5, (128, 128, 3, 3)).astype(f32) for _ in range(3)]
+    bs = [rng.normal(0, 0.1, (128,)).astype(f32) for _ in range(3)]
+
+    def build(to):
+        xv = R.Var("input", x.shape)
+        conv = lambda d, i: R.Call("nn_conv2d", [d, R.Constant(to(ws[i])), R.Constant(to(bs[i]))],
+                                   R.Conv2DAttrs((1, 1), (1, 1, 1, 1), (1, 1), 1))
+        y0 = R.Call("nn_relu", [conv(xv, 0)])
+        y1 = R.Call("nn_relu", [conv(y0, 1)])
+        y2 = R.Call("nn_relu", [R.Call("add", [conv(y1, 2), y0])])
+        return R.Function([xv], R.Call("nn_relu", [y2]))  # a trailing op: y2 stays an internal NHWC tensor
+
+    outs = {}
+    for name, flag in (("rowstack128", "2"), ("igemm", "0")):
+        monkeypatch.setenv("KXC_B200_ROWSTACK128", flag)
+        outs[name], g = run_plan(kxc, build(cuda_const), x, "bf16")
+        kinds = [l[0].split()[0] for l in g.launch_info()]
+        assert kinds.count("conv_rowstack128") == (3 if flag == "2" else 0)
+    from hdkx_aicompiler_b200 import ops
+    assert ops.device_status() == 0
+    if n <= 3:
+        emu = ograph.run(build(lambda a: a), [x], operand_round=port.round_bf16, workers=4)
+        scale = float(np.abs(emu).max())
+        for name, got in outs.items():
+            err = float(np.abs(got - emu).max())
+            assert err <= 2e-2 * scale, f"{name}: max_abs {err:.3e} against the same-rounding oracle (scale {scale:.2f})"
+    else:
+        scale = float(np.abs(outs["igemm"]).max())
+    assert float(np.abs(outs["rowstack128"] - outs["igemm"]).max()) <= 2e-2 * scale
+
+
 @pytest.mark.parametrize("precision", ["bf16", "tf32"])
 def test_resnet18_stem_plan(kxc, precision):
     """The packed-stem path alone (7x7 stride-2 convolution over 3 channels + bias + relu): against the oracle on
