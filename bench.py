@@ -173,7 +173,7 @@ def main():
     import torch.distributed as dist
 
     from hdkx_aicompiler_b200 import ops, plan, resnet18
-    from hdkx_aicompiler_b200.parallel import GatherToWorker0, PeerStoreToWorker0, shard_range
+    from hdkx_aicompiler_b200.parallel import GatherToWorker0, PeerStoreToWorker0, bind_to_device_numa_node, shard_range
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -184,6 +184,7 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    numa_cpus = bind_to_device_numa_node(local_rank) if world > 1 else None  # before the pinned buffers are allocated
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     shard_begin, shard_end = shard_range(rank, world, args.batch)
@@ -337,7 +338,8 @@ def main():
                                + (" by peer stores from the dense layer's epilogue" if peers else ""),
                    "global_batch": args.batch, "per_gpu_batch": per_gpu, "parallelism": f"dp{world}",
                    "l2": "inputs larger than L2 (616 MB of images and >1 GB of activations per step per GPU at N=1)",
-                   "pipelining": "steps overlap: input copy of step i+1 and gather/read-back of step i-1 run beside the kernels of step i"},
+                   "pipelining": "steps overlap: input copy of step i+1 and gather/read-back of step i-1 run beside the kernels of step i",
+                   "host_numa_binding": (f"rank 0 bound to {len(numa_cpus)} CPUs next to its GPU" if numa_cpus else "none")},
         "clocks": clocks,
         "e2e": {"value": args.batch / (e2e_ms / args.steps / 1e3), "unit": UNIT,
                 "h2d_bytes_per_step": int(host_in.numel() * 4 * world), "d2h_bytes_per_step": int(args.batch * graph.out_shape[1] * 4)},

@@ -6,8 +6,58 @@ Every image is independent through all 49 calls of the graph, so rank r of G sim
 (CpuCCLBackend::GatherToWorker0 / ConcatFirstDim, src/base/disco/ccl_cpu.cc:274-294, :134-174).
 Works on any torch.distributed backend (NCCL on GPUs, gloo on CPU for the tests).
 """
+import os
+
 import torch
 import torch.distributed as dist
+
+
+def parse_cpu_list(text):
+    """'0-3,8,10-11' -> {0, 1, 2, 3, 8, 10, 11} (the format of sysfs cpulist files)."""
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def numa_cpus_of_pci_device(bdf, sysfs_root="/sys"):
+    """CPUs of the NUMA node a PCI device ('0000:1b:00.0') is attached to, or None when the kernel does not say."""
+    try:
+        with open(os.path.join(sysfs_root, "bus/pci/devices", bdf.lower(), "numa_node")) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(os.path.join(sysfs_root, "devices/system/node", f"node{node}", "cpulist")) as f:
+            return parse_cpu_list(f.read()) or None
+    except (OSError, ValueError):
+        return None
+
+
+def bind_to_device_numa_node(device_index, sysfs_root="/sys"):
+    """Restricts this process to the CPUs next to GPU `device_index`, so that the pinned host buffers it allocates
+    afterwards (and the threads that fill them) live on the memory of the socket the GPU's PCIe link hangs off. With one
+    process per GPU on a two-socket host, half of the ranks otherwise stage their 600 MB per step through the other
+    socket. Returns the CPU set it bound to, or None when the topology is unknown or the binding is not permitted
+    (nothing is changed then)."""
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        bdf = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+    except (AttributeError, RuntimeError, AssertionError):
+        return None
+    cpus = numa_cpus_of_pci_device(bdf, sysfs_root)
+    if not cpus:
+        return None
+    try:
+        allowed = os.sched_getaffinity(0) & cpus
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return allowed
+    except (OSError, AttributeError):
+        return None
 
 
 def shard_range(rank, world, batch):

@@ -98,3 +98,21 @@ def test_shard_range():
     assert [shard_range(r, 4, 1024) for r in range(4)] == [(0, 256), (256, 512), (512, 768), (768, 1024)]
     with pytest.raises(ValueError):
         shard_range(0, 3, 1024)
+
+
+def test_numa_cpus_of_pci_device_reads_sysfs(tmp_path):
+    """The CPU set next to a GPU comes from two sysfs files; unknown topology (-1, missing files) gives None."""
+    from hdkx_aicompiler_b200.parallel import numa_cpus_of_pci_device, parse_cpu_list
+    assert parse_cpu_list("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert parse_cpu_list("") == set()
+    dev = tmp_path / "bus/pci/devices/0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices/system/node/node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("32-63,96-127\n")
+    cpus = numa_cpus_of_pci_device("0000:1B:00.0", sysfs_root=str(tmp_path))
+    assert cpus == set(range(32, 64)) | set(range(96, 128))
+    (dev / "numa_node").write_text("-1\n")
+    assert numa_cpus_of_pci_device("0000:1b:00.0", sysfs_root=str(tmp_path)) is None
+    assert numa_cpus_of_pci_device("0000:aa:00.0", sysfs_root=str(tmp_path)) is None
