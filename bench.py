@@ -40,9 +40,10 @@ GLOBAL_BATCH = 1024
 # would break the size rule for captures). Outputs of 205-411 MB no longer fit the 126 MB L2 at that size, as at 1024.
 NCU_TRAFFIC_BATCH = 512
 NCU_DRAM_BYTES_PER_IMAGE = {
-    "conv_stem_pool_nchw": 0.920e6,   # 1 launch: 308.4 MB read (= the fp32 input, once) + 162.7 MB written
-    "conv_rowstack": 3.680e6,         # 4 launches: 1234 MB read + 650 MB written
-    "conv_igemm": 3.293e6,            # 12 launches: 1254 MB read + 432 MB written
+    "conv_stem_pool_nchw": 0.920e6,   # 1 launch: 308.4 MB read (= the fp32 input, once) + 162.6 MB written
+    "conv_rowstack": 3.690e6,         # 4 launches: 1234 MB read + 655 MB written
+    "conv_rowstack128": 0.317e6,      # 1 launch: 103.1 MB read + 59.1 MB written
+    "conv_igemm": 3.101e6,            # 12 launches (11 at 512 images): 1204 MB read + 384 MB written
     "dense_igemm": 0.003e6,
 }
 
