@@ -484,9 +484,10 @@ template <MmaKind kKind, int KB_BYTES>
 int32_t launch_by_bn(const TcConfig& cfg, const TcParams& p, cudaStream_t s) {
     if constexpr (KB_BYTES == 128 && kKind == MmaKind::F16) {
         if (cfg.dual) {
-            if (cfg.bn != 128 || cfg.ctas != 1 || cfg.out_mode != kOutNHWC_BF16 || !p.vec_ok || (p.Cout & 31) != 0)
-                return fail(KXC_B200_ERR_INVALID, "tensor-core conv: the two-output kernel needs a 128-wide tile, bf16 NHWC output and aligned pointers");
-            return launch_one<kKind, KB_BYTES, 128, kOutNHWC_BF16, 1, true>(p, s);
+            if ((cfg.bn != 128 && cfg.bn != 192) || cfg.ctas != 1 || cfg.out_mode != kOutNHWC_BF16 || !p.vec_ok || (p.Cout & 31) != 0)
+                return fail(KXC_B200_ERR_INVALID, "tensor-core conv: the two-output kernel needs a 128- or 192-wide tile, bf16 NHWC output and aligned pointers");
+            return cfg.bn == 192 ? launch_one<kKind, KB_BYTES, 192, kOutNHWC_BF16, 1, true>(p, s)
+                                 : launch_one<kKind, KB_BYTES, 128, kOutNHWC_BF16, 1, true>(p, s);
         }
     }
     if (cfg.dual) return fail(KXC_B200_ERR_INVALID, "tensor-core conv: no two-output kernel for this configuration");
@@ -657,8 +658,18 @@ bool tc_dual_applicable(TcDType dtype, TcOutMode out_mode, int cpad, int Cout, i
 int32_t tc_setup_dual(TcParams* p, TcConfig* cfg, const void* act_nhwc, const void* w_packed, const void* w2_packed, int N,
                       int H, int W, int cpad, int Cout, int KH, int KW, int stride, int pad_h, int pad_w) {
     KXC_TRY(tc_setup_conv(p, cfg, kTcBF16, kOutNHWC_BF16, act_nhwc, w_packed, N, H, W, cpad, Cout, KH, KW, stride, pad_h, pad_w, 1, 1));
-    // the two accumulators of a buffer share TMEM: 128-wide tiles, single CTAs
-    const int bn = 128;
+    // The two accumulators of a buffer share TMEM: 128-wide tiles (two buffers of 2 x 128 columns), single CTAs. When
+    // that leaves a launch with a second, mostly empty wave and 192-wide tiles fit one wave (256 -> 512 channels at 128
+    // images: 196 tiles against 147 for 148 SMs), the 192-wide form is taken: one buffer of 2 x 192 columns, so the
+    // epilogue no longer overlaps the next item's MMAs, which a CTA with a single work item does not miss.
+    int bn = 128;
+    {
+        const long long m_tiles = (long long)p->tiles_w * p->tiles_h * p->tiles_n;
+        auto waves = [](long long items) { return (items + kNumSMs - 1) / kNumSMs; };
+        const long long t128 = m_tiles * ((Cout + 127) / 128), t192 = m_tiles * ((Cout + 191) / 192);
+        static const bool model = [] { const char* e = getenv("KXC_B200_TILE_MODEL"); return !(e != nullptr && e[0] == '0'); }();
+        if (model && p->kb_elems * 2 == 128 && waves(t192) == 1 && waves(t128) >= 2) bn = 192;  // (192-wide tiles need 128-byte K blocks)
+    }
     cfg->bn = bn; cfg->ctas = 1; cfg->dual = 1;
     p->tiles_c = (Cout + bn - 1) / bn;
     const uint64_t ktot = (uint64_t)KH * KW * cpad;

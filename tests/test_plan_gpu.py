@@ -277,13 +277,13 @@ def test_stem_pool_fusion_is_bit_identical(kxc, monkeypatch):
     assert np.mean(fused != exp) < 1e-3 and np.abs(fused - exp).max() <= 2.0 ** -7 * np.abs(exp).max()
 
 
-@pytest.mark.parametrize("cin,cout,hw", [(64, 128, 56), (128, 256, 28), (64, 64, 30)])
-def test_downsample_block_two_output_kernel_is_bit_identical(kxc, monkeypatch, cin, cout, hw):
+@pytest.mark.parametrize("cin,cout,hw,N", [(64, 128, 56, 3), (128, 256, 28, 3), (64, 64, 30, 3), (256, 512, 14, 128)])
+def test_downsample_block_two_output_kernel_is_bit_identical(kxc, monkeypatch, cin, cout, hw, N):
     """A ResNet downsample block: conv3x3(s2)+relu and the residual branch's conv1x1(s2) read the same tensor and
-    are computed by ONE launch (second accumulator over the centre tap); the bits equal those of two launches."""
+    are computed by ONE launch (second accumulator over the centre tap); the bits equal those of two launches.
+    256 -> 512 channels at 128 images is the case that takes the 192-wide, single-buffered form of that kernel."""
     R = kxc.relay
     rng = np.random.default_rng(21)
-    N = 3
     x = rng.normal(0, 1, (N, cin, hw, hw)).astype(f32)
     w0 = rng.normal(0, (2 / (cin * 9)) ** 0.5, (cin, cin, 3, 3)).astype(f32)   # a layer in front: the shared tensor is internal
     w1 = rng.normal(0, (2 / (cin * 9)) ** 0.5, (cout, cin, 3, 3)).astype(f32)
@@ -308,9 +308,14 @@ def test_downsample_block_two_output_kernel_is_bit_identical(kxc, monkeypatch, c
     unfused, gu = run_plan(kxc, build(cuda_const), x, "bf16")
     assert gf.num_launches == gu.num_launches - 1
     assert any("second output" in l[0] for l in gf.launch_info())
+    if N == 128:
+        assert any("second output" in l[0] and "bn192" in l[0] for l in gf.launch_info())
     assert np.array_equal(fused, unfused)
-    emu = ograph.run(build(lambda a: a), [x], operand_round=port.round_bf16, workers=4)
-    assert_close(fused, emu, 2e-2, "downsample block vs same-rounding oracle")
+    if N <= 8:  # the CPU oracle at 128 images would take minutes; the bits above are the property under test there
+        emu = ograph.run(build(lambda a: a), [x], operand_round=port.round_bf16, workers=4)
+        assert_close(fused, emu, 2e-2, "downsample block vs same-rounding oracle")
+    else:
+        assert np.isfinite(fused).all() and float(np.abs(fused).max()) > 0
 
 
 @pytest.mark.parametrize("n,h,w", [(2, 56, 56), (3, 30, 20), (1, 7, 5), (2, 14, 8), (1, 15, 9)])
