@@ -95,8 +95,7 @@ class PeerStoreToWorker0:
     ConcatFirstDim, src/base/disco/ccl_cpu.cc:134-174) and is passed as `out=` of CompiledGraph.run; `complete()`
     is a device-side barrier on the current stream after which rank 0 may read `gathered()`.
 
-    NCCL's gather (GatherToWorker0) is the default; this class is checked against it bit for bit on 2 GPUs
-    (tests/test_parallel_gpu.py)."""
+    Checked against NCCL's gather (GatherToWorker0) bit for bit on 2 GPUs (tests/test_parallel_gpu.py)."""
 
     def __init__(self, shard_shape, dtype, device, group=None):
         import torch.distributed._symmetric_memory as symm
