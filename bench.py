@@ -213,14 +213,23 @@ def main():
         # Measured at 8 GPUs, 30 steps: 0.574 ms per step with peer stores against 0.592 with the NCCL gather, whose kernel
         # holds SMs while the next step's first (persistent) kernel starts. All ranks take the same form: one that
         # cannot set up symmetric memory sends every rank back to NCCL.
+        # The set-up is collective, so the ranks first agree that each of them can take part (the module exists and every
+        # other GPU of the node is peer-accessible) and only then enter it; a failure inside is agreed on the same way.
         try:
-            peers = [PeerStoreToWorker0(graph.out_shape, torch.float32, device) for _ in range(2)]
-            ok = torch.ones(1, device=device)
+            import torch.distributed._symmetric_memory  # noqa: F401
+            able = all(torch.cuda.can_device_access_peer(local_rank, o) for o in range(world) if o != local_rank)
         except Exception:  # noqa: BLE001
-            ok = torch.zeros(1, device=device)
+            able = False
+        ok = torch.tensor([1.0 if able else 0.0], device=device)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if ok.item() < 1:
-            peers = None
+        if ok.item() >= 1:
+            try:
+                peers = [PeerStoreToWorker0(graph.out_shape, torch.float32, device) for _ in range(2)]
+            except Exception:  # noqa: BLE001
+                ok.zero_()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() < 1:
+                peers = None
     exchange = "peer stores from the last kernel" if peers else ("nccl gather" if world > 1 else "none (one GPU)")
     host_out = torch.empty((args.batch if rank == 0 else per_gpu, graph.out_shape[1]), dtype=torch.float32).pin_memory()
 
