@@ -63,14 +63,38 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML read-outs from a thread of this process
+    every 2 ms (a region of a few milliseconds still gets samples), or, without the NVML module, an nvidia-smi child
+    process printing every 20 ms. Read-only: nothing of the GPU's state is changed."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    NVML_BITS = [0x8, 0x40, 0x20, 0x4]  # nvmlClocksEventReason*: HwSlowdown, HwThermalSlowdown, SwThermalSlowdown, SwPowerCap
 
     def __init__(self, index):
         self.samples, self.proc, self.thread, self.index = [], None, None, index
+        self.nvml, self.handle, self.stop_flag = None, None, threading.Event()
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:  # by PCI address: NVML's numbering ignores CUDA_VISIBLE_DEVICES
+            import torch
+            pr = torch.cuda.get_device_properties(self.index)
+            handle = pynvml.nvmlDeviceGetHandleByPciBusId("%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id))
+        except Exception:  # noqa: BLE001
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        return pynvml, handle
 
     def start(self):
+        try:
+            self.nvml, self.handle = self._nvml_handle()
+            self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # noqa: BLE001
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE, text=True)
@@ -78,6 +102,22 @@ class ClockSampler:
             return
         self.thread = threading.Thread(target=self._read, daemon=True)
         self.thread.start()
+        t0 = time.time()
+        while not self.samples and time.time() - t0 < 3.0:  # the child needs a moment before its first line
+            time.sleep(0.01)
+
+    def _poll(self):
+        n = self.nvml
+        reasons_fn = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(n, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        mx = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
+        while not self.stop_flag.is_set():
+            try:
+                mask = int(reasons_fn(self.handle))
+                self.samples.append([str(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)), str(mx)] +
+                                    ["Active" if mask & b else "Not Active" for b in self.NVML_BITS])
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.002)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -86,19 +126,22 @@ class ClockSampler:
                 self.samples.append(parts)
 
     def stop(self):
-        if self.proc is None:
+        if self.nvml is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+        elif self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()  # the exact process started above
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+        else:
+            self.proc.terminate()  # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
         mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
         mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        reasons = [n for i, n in enumerate(self.NAMES) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(self.samples)}
+                "samples": len(self.samples), "source": "nvml" if self.nvml is not None else "nvidia-smi"}
 
 
 # ------------------------------------------------------------------------------------------------
