@@ -195,7 +195,14 @@ int32_t conv2d_s8_dispatch(const int8_t* data, const int8_t* weight, const int32
     }
     if (force_simt || !tc_shape_ok(d)) return conv2d_s8_exact(data, weight, bias, multiplier, shift, out, d, relu, s);
     if (stem_ok) return run_stem(false);
-    const size_t act_bytes = align_up((size_t)d.N * d.H * d.W * cpad, 1024);
+    // A 1x1 convolution of stride > 1 without padding reads one pixel in stride^2: only those are converted, and the
+    // kernel runs as a stride-1 convolution over the subsampled tensor (a quarter of the conversion and of the kernel's
+    // loads for the downsample branches of a ResNet).
+    const bool subsample = d.KH == 1 && d.KW == 1 && d.PH == 0 && d.PW == 0 && d.SH == d.SW && d.SH > 1 && (cpad & 3) == 0 &&
+                           d.N <= 65535;
+    const int in_h = d.H, in_w = d.W;
+    const int conv_h = subsample ? d.OH : d.H, conv_w = subsample ? d.OW : d.W;  // the tensor the kernel convolves
+    const size_t act_bytes = align_up((size_t)d.N * conv_h * conv_w * cpad, 1024);
     const size_t w_bytes = align_up((size_t)d.O * d.KH * d.KW * cpad, 1024);
     // Result layout. A thread of the epilogue owns one pixel, so its NCHW stores are single bytes whose neighbours in
     // memory belong to the next pixel of the same tile row: runs of BW bytes. With the narrow tiles of the deep layers
@@ -210,15 +217,19 @@ int32_t conv2d_s8_dispatch(const int8_t* data, const int8_t* weight, const int32
     uint8_t* act = static_cast<uint8_t*>(ws.ptr);
     uint8_t* wp = act + act_bytes;
     int8_t* out_nhwc = reinterpret_cast<int8_t*>(wp + w_bytes);
-    KXC_TRY(nchw_to_nhwc(data, act, dt, d.N, d.C, d.H * d.W, cpad, s));
+    if (subsample) {
+        KXC_TRY(nchw_to_nhwc_s8_subsample(data, reinterpret_cast<int8_t*>(act), d.N, d.C, in_h, in_w, d.OH, d.OW, d.SH, cpad, s));
+    } else {
+        KXC_TRY(nchw_to_nhwc(data, act, dt, d.N, d.C, d.H * d.W, cpad, s));
+    }
     KXC_TRY(pack_weights_ohwi(weight, wp, dt, d.O, d.C, d.KH, d.KW, cpad, s));
     TcParams p{};
     TcConfig cfg{};
     if (rowstack_ok) {
         KXC_TRY(rowstack3x3_s8_setup(&p, act, wp, d.N, d.H, d.W));
     } else {
-        KXC_TRY(tc_setup_conv(&p, &cfg, dt, two_step ? kOutNHWC_S8 : kOutNCHW_S8, act, wp, d.N, d.H, d.W, cpad, d.O, d.KH, d.KW, d.SH,
-                              d.PH, d.PW, d.DH, d.DW));
+        KXC_TRY(tc_setup_conv(&p, &cfg, dt, two_step ? kOutNHWC_S8 : kOutNCHW_S8, act, wp, d.N, conv_h, conv_w, cpad, d.O, d.KH, d.KW,
+                              subsample ? 1 : d.SH, d.PH, d.PW, d.DH, d.DW));
     }
     p.bias_i32 = bias;
     p.multiplier = multiplier;

@@ -108,6 +108,49 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_s8_kernel(const int8_t* __re
     }
 }
 
+// int8 NCHW -> NHWC of the pixels a 1x1 convolution of stride `st` (no padding) reads: out[n][p][c] =
+// in[n][c][(p / OW) * st][(p % OW) * st], p = oh * OW + ow. grid (ceil(OH*OW/64), ceil(cpad/64), N), block 256: the same
+// 64 x 64 byte transpose as above with gathered source pixels; the rows the convolution skips are never touched.
+__global__ void __launch_bounds__(256) nchw_to_nhwc_s8_subsample_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, int C,
+                                                                         int H, int W, int OH, int OW, int st, int cpad) {
+    __shared__ __align__(4) int8_t tile[64][68];
+    const int n = blockIdx.z;
+    const int p0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
+    const int P = OH * OW;
+    const int8_t* src = in + (size_t)n * C * H * W;
+    int8_t* dst = out + (size_t)n * P * cpad;
+    const int q = threadIdx.x & 15, r = threadIdx.x >> 4;
+    int off[4];  // source offsets of this thread's four pixels inside a channel plane (-1: beyond the last pixel)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int p = p0 + 4 * q + e;
+        off[e] = p < P ? (p / OW) * st * W + (p % OW) * st : -1;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int c = c0 + r + 16 * k;
+        uint32_t v = 0;
+        if (c < C) {
+            const int8_t* plane = src + (size_t)c * H * W;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (off[e] >= 0) v |= (uint32_t)(uint8_t)__ldg(plane + off[e]) << (8 * e);
+        }
+        *reinterpret_cast<uint32_t*>(&tile[r + 16 * k][4 * q]) = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int p = p0 + r + 16 * k, c = c0 + 4 * q;
+        if (p < P && c < cpad) {  // cpad is a multiple of 4
+            const int pl = r + 16 * k;
+            const uint32_t v = (uint32_t)(uint8_t)tile[4 * q][pl] | ((uint32_t)(uint8_t)tile[4 * q + 1][pl] << 8) |
+                               ((uint32_t)(uint8_t)tile[4 * q + 2][pl] << 16) | ((uint32_t)(uint8_t)tile[4 * q + 3][pl] << 24);
+            *reinterpret_cast<uint32_t*>(dst + (size_t)p * cpad + c) = v;
+        }
+    }
+}
+
 template <typename TIn, typename TOut>
 __global__ void pack_weights_kernel(const TIn* __restrict__ w, TOut* __restrict__ out, int O, int C, int KH, int KW, int cpad) {
     const int64_t total = (int64_t)O * KH * KW * cpad;
@@ -166,6 +209,15 @@ int32_t nchw_to_nhwc(const void* in, void* out, TcDType dtype, int N, int C, int
             break;
     }
     return check_launch("nchw_to_nhwc");
+}
+
+int32_t nchw_to_nhwc_s8_subsample(const int8_t* in, int8_t* out, int N, int C, int H, int W, int OH, int OW, int stride, int cpad,
+                                  cudaStream_t s) {
+    if (N == 0 || C == 0 || OH == 0 || OW == 0) return KXC_B200_OK;
+    if ((cpad & 3) != 0 || (reinterpret_cast<uintptr_t>(out) & 3u) != 0 || N > 65535 || (long long)H * W > 0x7fffffffll)
+        return fail(KXC_B200_ERR_UNSUPPORTED, "nchw_to_nhwc_s8_subsample: %d padded channels, %d images", cpad, N);
+    nchw_to_nhwc_s8_subsample_kernel<<<dim3((OH * OW + 63) / 64, (cpad + 63) / 64, N), 256, 0, s>>>(in, out, C, H, W, OH, OW, stride, cpad);
+    return check_launch("nchw_to_nhwc_s8_subsample");
 }
 
 int32_t nhwc_to_nchw_s8(const int8_t* in, int8_t* out, int N, int C, int HW, cudaStream_t s) {

@@ -14,6 +14,11 @@ namespace kxc_b200 {
 // rounded away, nearest even), or int8 (copied).
 int32_t nchw_to_nhwc(const void* in, void* out, TcDType dtype, int N, int C, int HW, int cpad, cudaStream_t s, bool tf32_lo = false);
 
+// int8 NCHW -> NHWC of only the pixels a 1x1 convolution of stride `stride` without padding reads:
+// out[n][oh][ow][c] = in[n][c][oh*stride][ow*stride], channels zero-filled up to cpad (a multiple of 4).
+int32_t nchw_to_nhwc_s8_subsample(const int8_t* in, int8_t* out, int N, int C, int H, int W, int OH, int OW, int stride, int cpad,
+                                  cudaStream_t s);
+
 // int8 NHWC [N][HW][C] -> NCHW [N][C][HW] (the reference layout of a requantized result).
 int32_t nhwc_to_nchw_s8(const int8_t* in, int8_t* out, int N, int C, int HW, cudaStream_t s);
 
