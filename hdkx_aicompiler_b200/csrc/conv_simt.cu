@@ -105,12 +105,28 @@ __global__ void __launch_bounds__(kTileThreads) conv2d_tiled_f32_kernel(const fl
 #pragma unroll
         for (int e = 0; e < kPT; ++e) acc[j][e] = 0.0f;
     const int64_t plane_in = (int64_t)d.H * d.W;
+    // 16-byte weight loads need every block's run to start on a 16-byte boundary
+    const bool w_vec = ((reinterpret_cast<uintptr_t>(weight) & 15u) == 0) && (((int64_t)d.C * taps) & 3) == 0 && ((rc_block * taps) & 3) == 0;
     for (int c0 = 0; c0 < d.C; c0 += rc_block) {
         const int nrc = (d.C - c0) < rc_block ? (d.C - c0) : rc_block;
         __syncthreads();  // the previous block of weights has been used
-        for (int i = threadIdx.x; i < nrc * taps * kTileO; i += kTileThreads) {
-            const int o = i % kTileO, t = (i / kTileO) % taps, rc = i / (kTileO * taps);
-            w_s[i] = (o0 + o < d.O) ? __ldg(weight + ((int64_t)(o0 + o) * d.C + (c0 + rc)) * taps + t) : 0.0f;
+        // A channel's nrc * taps weights of this block are contiguous in the OIHW tensor. Consecutive threads take
+        // consecutive channels (distinct shared-memory banks) and 16 bytes each where the run allows it: with 4-byte
+        // loads every value costs a 32-byte sector of its own, which made the 512-channel layers weight-bound.
+        const int run = nrc * taps;
+        if (w_vec && (run & 3) == 0) {
+            for (int i = threadIdx.x; i < (run >> 2) * kTileO; i += kTileThreads) {
+                const int o = i % kTileO, jq = i / kTileO;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (o0 + o < d.O) v = __ldg(reinterpret_cast<const float4*>(weight + ((int64_t)(o0 + o) * d.C + c0) * taps) + jq);
+                float* dst = w_s + (4 * jq) * kTileO + o;
+                dst[0] = v.x; dst[kTileO] = v.y; dst[2 * kTileO] = v.z; dst[3 * kTileO] = v.w;
+            }
+        } else {
+            for (int i = threadIdx.x; i < run * kTileO; i += kTileThreads) {
+                const int o = i % kTileO, j = i / kTileO;
+                w_s[i] = (o0 + o < d.O) ? __ldg(weight + ((int64_t)(o0 + o) * d.C + c0) * taps + j) : 0.0f;
+            }
         }
         __syncthreads();
         for (int rc = 0; rc < nrc; ++rc) {
