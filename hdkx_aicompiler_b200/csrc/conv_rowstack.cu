@@ -21,7 +21,7 @@
 //     contiguous 128-pixel block that starts at column kw (a 2 KiB, swizzle-atom aligned offset);
 //   * the 72 KiB of weights stay resident, ordered [kw][r][cout][cin] by nine TMA loads of the ordinary packed tensor.
 //
-// Roles as in conv_tc.cu: warp 0 producer, warp 1 MMA issuer + TMEM owner, warps 2..9 epilogue; two TMEM
+// Roles as in conv_tc.cu: warp 0 producer, warp 1 MMA issuer + TMEM owner, warps 2..17 epilogue (two sets); two TMEM
 // accumulators (the epilogue of one tile overlaps the next tile's MMAs); every wait bounded.
 #include "conv_rowstack.cuh"
 
