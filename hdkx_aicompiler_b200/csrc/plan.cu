@@ -316,14 +316,14 @@ int32_t setup_stem(kxc_b200_plan* pl, Step& st, int N, int C, int H, int W, int 
 
 // The 128 -> 128 channel 3x3 layers: the row-stacked CTA-pair kernel with resident weights or the implicit-GEMM kernel.
 // Measured per launch at 28 x 28 (ms, row-stacked against implicit GEMM): without a residual 0.191 / 0.215 at 1024 images
-// and 0.033 / 0.037 at 128; with a residual 0.235 / 0.227 at 1024 and 0.037-0.039 / 0.040-0.041 at 128. So: always without
-// a residual, with one only for small launches. KXC_B200_ROWSTACK128 = 0: never, 2: always (A/B runs); read at every
+// and 0.033 / 0.037 at 128; with a residual 0.235 / 0.227 at 1024, 0.127 / 0.121-0.125 at 512, 0.067-0.068 / 0.070-0.072
+// at 256 and 0.037-0.039 / 0.040-0.041 at 128. So: always without a residual, with one up to 256 images of 28 x 28. KXC_B200_ROWSTACK128 = 0: never, 2: always (A/B runs); read at every
 // plan build.
 static bool rowstack128_wanted(bool has_residual, long long pixels) {
     const char* e = getenv("KXC_B200_ROWSTACK128");
     if (e != nullptr && e[0] == '0') return false;
     if (e != nullptr && e[0] == '2') return true;
-    return !has_residual || pixels <= 128ll * 28 * 28;
+    return !has_residual || pixels <= 256ll * 28 * 28;
 }
 
 static int32_t finalize_exact(kxc_b200_plan* pl);
